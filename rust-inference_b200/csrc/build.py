@@ -1,0 +1,192 @@
+"""Compiles the CUDA sources of this folder for sm_100a and loads them with ctypes.
+
+Each ``.cu`` file becomes one shared library of plain C entry points.  A
+library is compiled the first time something asks for it (``library(name)``),
+so a process compiles what its model needs and nothing else; the result is kept
+in ``_build/`` beside the sources under a name that carries a hash of the
+sources and flags, so a changed source is compiled again and an unchanged one
+never is.  While nvcc runs, a line is printed to stderr now and then.
+
+There is no fallback: if nvcc is missing or a compile fails, the caller gets a
+``KernelBuildError``.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from typing import Dict, Iterable, Optional, Tuple
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "--threads", "2"]
+
+# every kernel source of the package, with the headers it includes
+SOURCES: Dict[str, Tuple[str, ...]] = {
+    "elementwise": ("elementwise.cu", "common.cuh"),
+    "rope_kv": ("rope_kv.cu", "common.cuh"),
+    "attention_plain": ("attention_plain.cu", "common.cuh"),
+    "linear_f32": ("linear_f32.cu", "common.cuh"),
+    "sampling": ("sampling.cu", "common.cuh"),
+}
+
+
+class KernelBuildError(RuntimeError):
+    pass
+
+
+_lock = threading.Lock()
+_loaded: Dict[str, ctypes.CDLL] = {}
+
+
+def _log(msg: str) -> None:
+    print(f"[rust_inference_b200] {msg}", file=sys.stderr, flush=True)
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise KernelBuildError("nvcc was not found (PATH, $NVCC, /usr/local/cuda/bin): the CUDA kernels cannot be built")
+
+
+def build_dir() -> str:
+    """``_build/`` beside the sources if it can be written, else a per-user folder
+    under the temporary directory (a read-only installation)."""
+    override = os.environ.get("RUST_INFERENCE_B200_BUILD_DIR")
+    cands = [override] if override else []
+    cands.append(os.path.join(HERE, "_build"))
+    cands.append(os.path.join(tempfile.gettempdir(), f"rust_inference_b200_build_{os.getuid()}"))
+    for d in cands:
+        try:
+            os.makedirs(d, exist_ok=True)
+            if os.access(d, os.W_OK | os.X_OK):
+                return d
+        except OSError:
+            continue
+    raise KernelBuildError(f"no writable build folder among {cands}")
+
+
+def _variant_name(name: str, defines: Optional[Dict[str, object]]) -> str:
+    if not defines:
+        return name
+    return name + "".join(f"_{k.lower()}{v}" for k, v in sorted(defines.items()))
+
+
+def _fingerprint(name: str, defines: Optional[Dict[str, object]]) -> str:
+    h = hashlib.sha256()
+    for fn in SOURCES[name]:
+        with open(os.path.join(HERE, fn), "rb") as f:
+            h.update(fn.encode())
+            h.update(f.read())
+    h.update(repr(ARCH_FLAGS + BASE_FLAGS).encode())
+    h.update(repr(sorted((defines or {}).items())).encode())
+    return h.hexdigest()[:12]
+
+
+def library_path(name: str, defines: Optional[Dict[str, object]] = None, where: Optional[str] = None) -> str:
+    return os.path.join(where or build_dir(), f"{_variant_name(name, defines)}-{_fingerprint(name, defines)}.so")
+
+
+def find_built(name: str, defines: Optional[Dict[str, object]] = None) -> Optional[str]:
+    """An up-to-date library built earlier: in the in-tree folder even when that is
+    read-only now, else in the writable build folder."""
+    for d in (os.path.join(HERE, "_build"), None):
+        try:
+            p = library_path(name, defines, d)
+        except KernelBuildError:
+            continue
+        if os.path.exists(p):
+            return p
+    return None
+
+
+def compile_library(name: str, defines: Optional[Dict[str, object]] = None, verbose: bool = False) -> str:
+    """Compile one source (if its library is not there yet) and return the path."""
+    if name not in SOURCES:
+        raise KernelBuildError(f"unknown kernel library {name!r}")
+    have = find_built(name, defines)
+    if have:
+        return have
+    out = library_path(name, defines)
+    src = os.path.join(HERE, SOURCES[name][0])
+    tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
+    cmd = [_nvcc()] + ARCH_FLAGS + BASE_FLAGS + [f"-D{k}={v}" for k, v in sorted((defines or {}).items())]
+    if verbose:
+        cmd += ["-Xptxas", "-v"]
+    cmd += ["-I", HERE, "-o", tmp, src]
+    _log(f"compiling {_variant_name(name, defines)} for sm_100a ...")
+    t0 = time.time()
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, cwd=build_dir())
+    while True:
+        try:
+            log, _ = proc.communicate(timeout=15)
+            break
+        except subprocess.TimeoutExpired:
+            _log(f"still compiling {_variant_name(name, defines)} ({time.time() - t0:.0f} s)")
+    if proc.returncode != 0:
+        try:
+            os.unlink(tmp)
+        except OSError:
+            pass
+        raise KernelBuildError(f"nvcc failed for {SOURCES[name][0]}:\n{' '.join(cmd)}\n{log}")
+    os.replace(tmp, out)
+    _log(f"built {os.path.basename(out)} in {time.time() - t0:.1f} s")
+    if verbose and log:
+        print(log, file=sys.stderr)
+    return out
+
+
+def library(name: str, defines: Optional[Dict[str, object]] = None) -> ctypes.CDLL:
+    """The loaded library of ``name`` (compiled first if need be)."""
+    key = _variant_name(name, defines)
+    lib = _loaded.get(key)
+    if lib is not None:
+        return lib
+    with _lock:
+        lib = _loaded.get(key)
+        if lib is None:
+            path = compile_library(name, defines)
+            try:
+                lib = ctypes.CDLL(path)
+            except OSError as e:
+                raise KernelBuildError(f"cannot load {path}: {e}") from e
+            lib.ri_last_error.restype = ctypes.c_char_p
+            _loaded[key] = lib
+    return lib
+
+
+def prepare(requests: Iterable[Tuple[str, Optional[Dict[str, object]]]]) -> None:
+    """Compile several libraries side by side (each at most once)."""
+    todo = []
+    for name, defines in requests:
+        if _variant_name(name, defines) not in _loaded and not find_built(name, defines):
+            todo.append((name, defines))
+    if not todo:
+        return
+    errors = []
+
+    def work(item):
+        try:
+            compile_library(*item)
+        except Exception as e:  # noqa: BLE001 - reported below
+            errors.append(e)
+
+    threads = [threading.Thread(target=work, args=(item,)) for item in todo]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    if errors:
+        raise errors[0]
+
+
+def build_all(extra: Iterable[Tuple[str, Optional[Dict[str, object]]]] = ()) -> None:
+    """Compile every library (used by the repository's build check)."""
+    prepare([(n, None) for n in SOURCES if not n.endswith("_tmpl")] + list(extra))

@@ -1,0 +1,72 @@
+// Shared helpers of the sm_100a kernels: element types, reductions, error reporting.
+//
+// Every kernel file exports plain C functions that take device pointers, sizes
+// and a CUDA stream, launch on that stream and return 0 or a non-zero code;
+// `ri_last_error()` of the same library gives the message.  Nothing here
+// allocates or synchronises.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define RI_DTYPE_F32 0
+#define RI_DTYPE_BF16 1
+
+#ifndef RI_ERRBUF_DEFINED
+#define RI_ERRBUF_DEFINED
+static thread_local char ri_errbuf[512];
+extern "C" const char* ri_last_error() { return ri_errbuf; }
+#endif
+
+#define RI_FAIL(code, ...)                                  \
+    do {                                                    \
+        snprintf(ri_errbuf, sizeof(ri_errbuf), __VA_ARGS__); \
+        return (code);                                      \
+    } while (0)
+
+#define RI_REQUIRE(cond, ...)                 \
+    do {                                      \
+        if (!(cond)) RI_FAIL(-1, __VA_ARGS__); \
+    } while (0)
+
+// after a launch: report a launch error without synchronising
+#define RI_CHECK_LAUNCH(name)                                                              \
+    do {                                                                                   \
+        cudaError_t e_ = cudaGetLastError();                                               \
+        if (e_ != cudaSuccess) RI_FAIL((int)e_, "%s: %s", name, cudaGetErrorString(e_));   \
+    } while (0)
+
+__device__ __forceinline__ float ld_f(const float* p) { return *p; }
+__device__ __forceinline__ float ld_f(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void st_f(float* p, float v) { *p = v; }
+__device__ __forceinline__ void st_f(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block whose size is a multiple of 32 (at most 1024).  `red` holds 33 floats.
+// The order of the additions depends only on the block size, not on the data.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();                 // `red` may still be read from an earlier call
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    int nw = blockDim.x >> 5;
+    if (warp == 0) {
+        float t = (lane < nw) ? red[lane] : 0.0f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}

@@ -1,0 +1,142 @@
+// Embedding gather, RMSNorm (with the residual add fused in) and SiLU-gated product.
+//
+// The residual stream is float32 in every mode; the parts between two norms
+// work in the compute type T (float or bfloat16).  All sums of squares,
+// reciprocal roots and gains are float32.
+//
+// Formulas: thanhauco/rust-inference src/ops/embedding.rs:10-42,
+// src/ops/norm.rs:7-62, src/ops/elementwise.rs:10-52 (kernels.cu:89-148 there).
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// out[t, :] = float(table[ids[t], :])
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_rows_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
+                                  int dim, int vocab, int* __restrict__ bad) {
+    int id = ids[blockIdx.x];
+    if (id < 0 || id >= vocab) {          // checked on the host as well; never read out of range
+        if (threadIdx.x == 0) atomicExch(bad, 1);
+        return;
+    }
+    const T* src = table + (size_t)id * dim;
+    float* dst = out + (size_t)blockIdx.x * dim;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = ld_f(src + i);
+}
+
+extern "C" int ri_embed_rows(const int* ids, const void* table, float* out, int tokens, int dim, int vocab,
+                             int dtype, int* bad_flag, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    RI_REQUIRE(tokens > 0 && dim > 0 && vocab > 0, "embed_rows: bad sizes tokens=%d dim=%d vocab=%d", tokens, dim, vocab);
+    int threads = dim >= 1024 ? 256 : 128;
+    if (dtype == RI_DTYPE_F32)
+        embed_rows_kernel<float><<<tokens, threads, 0, stream>>>(ids, (const float*)table, out, dim, vocab, bad_flag);
+    else if (dtype == RI_DTYPE_BF16)
+        embed_rows_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, dim, vocab, bad_flag);
+    else
+        RI_FAIL(-1, "embed_rows: unknown dtype %d", dtype);
+    RI_CHECK_LAUNCH("embed_rows");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm of the residual stream.
+//   x = resid[r] (+ delta[r]);  if delta and write_back: resid[r] = x
+//   out[i] = T(x * (1 / sqrt(mean(x^2) + eps)) * gain)
+// r = rows ? rows[i] : i.  With `rows` nothing is written back.
+// One block per row, the row staged in shared memory (dim floats).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta, const int* __restrict__ rows,
+                               const float* __restrict__ gain, T* __restrict__ out, int dim, float eps,
+                               int write_back) {
+    extern __shared__ float row[];
+    __shared__ float red[33];
+    size_t r = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
+    float* rp = resid + r * dim;
+    const T* dp = delta ? delta + r * dim : nullptr;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        float v = rp[i];
+        if (dp) {
+            v += ld_f(dp + i);
+            if (write_back) rp[i] = v;
+        }
+        row[i] = v;
+        ss += v * v;
+    }
+    float total = block_sum(ss, red);
+    float inv = 1.0f / sqrtf(total / (float)dim + eps);
+    T* op = out + (size_t)blockIdx.x * dim;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) st_f(op + i, row[i] * inv * gain[i]);
+}
+
+extern "C" int ri_rmsnorm(float* resid, const void* delta, const int* rows, const float* gain, void* out, int n_rows,
+                          int dim, float eps, int write_back, int dtype, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    RI_REQUIRE(n_rows > 0 && dim > 0, "rmsnorm: bad sizes rows=%d dim=%d", n_rows, dim);
+    size_t smem = (size_t)dim * sizeof(float);
+    RI_REQUIRE(smem <= 200 * 1024, "rmsnorm: a row of %d elements does not fit in shared memory (limit 51200)", dim);
+    int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
+    if (rows) write_back = 0;
+    cudaError_t e = cudaSuccess;
+    if (dtype == RI_DTYPE_F32) {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) RI_FAIL((int)e, "rmsnorm: %s", cudaGetErrorString(e));
+        rmsnorm_kernel<float><<<n_rows, threads, smem, stream>>>(resid, (const float*)delta, rows, gain, (float*)out, dim, eps, write_back);
+    } else if (dtype == RI_DTYPE_BF16) {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) RI_FAIL((int)e, "rmsnorm: %s", cudaGetErrorString(e));
+        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, stream>>>(resid, (const __nv_bfloat16*)delta, rows, gain, (__nv_bfloat16*)out, dim, eps, write_back);
+    } else {
+        RI_FAIL(-1, "rmsnorm: unknown dtype %d", dtype);
+    }
+    RI_CHECK_LAUNCH("rmsnorm");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// resid[r] += delta[r] for whole rows (used when no norm follows an addition)
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void add_rows_kernel(float* __restrict__ resid, const T* __restrict__ delta, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) resid[i] += ld_f(delta + i);
+}
+
+extern "C" int ri_add_rows(float* resid, const void* delta, long long n, int dtype, cudaStream_t stream) {
+    if (n == 0) return 0;
+    unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == RI_DTYPE_F32) add_rows_kernel<float><<<blocks, 256, 0, stream>>>(resid, (const float*)delta, (size_t)n);
+    else if (dtype == RI_DTYPE_BF16) add_rows_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(resid, (const __nv_bfloat16*)delta, (size_t)n);
+    else RI_FAIL(-1, "add_rows: unknown dtype %d", dtype);
+    RI_CHECK_LAUNCH("add_rows");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// out[m, i] = silu(gu[m, i]) * gu[m, inter + i],  silu(t) = t / (1 + exp(-t))
+// `gu` holds the gate and the up projection side by side: [m, 2*inter].
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    size_t m = i / inter;
+    int c = (int)(i - m * inter);
+    float g = ld_f(gu + m * 2 * inter + c);
+    float u = ld_f(gu + m * 2 * inter + inter + c);
+    st_f(out + i, (g / (1.0f + expf(-g))) * u);
+}
+
+extern "C" int ri_silu_mul(const void* gu, void* out, int rows, int inter, int dtype, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    RI_REQUIRE(rows > 0 && inter > 0, "silu_mul: bad sizes rows=%d inter=%d", rows, inter);
+    size_t total = (size_t)rows * inter;
+    unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == RI_DTYPE_F32) silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, inter, total);
+    else if (dtype == RI_DTYPE_BF16) silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total);
+    else RI_FAIL(-1, "silu_mul: unknown dtype %d", dtype);
+    RI_CHECK_LAUNCH("silu_mul");
+    return 0;
+}

@@ -1,0 +1,119 @@
+// Per-head RMSNorm of queries and keys, rotary position encoding and the append
+// of keys and values to the paged cache, in one pass over the fused projection.
+//
+//   qkv  [tokens, (H + 2*KV) * Dh]   q heads, then k heads, then v heads
+//   q_out[tokens, H, Dh]
+//   k_pool, v_pool [pages, KV, page_size, Dh]  (one layer's pools)
+//
+// For a head vector x of q or k:  y = x * (1/sqrt(mean(x^2)+eps)) * gain  (if a
+// gain is given), then for d < rot/2 with (c, s) = table[pos][d]:
+//   z[d] = y[d]*c - y[d+rot/2]*s ;  z[d+rot/2] = y[d+rot/2]*c + y[d]*s
+// and elements from `rot` on are left as they are.  All of it in float32.
+// Formulas: thanhauco/rust-inference src/ops/norm.rs:14-32, src/ops/rope.rs:52-79,
+// src/kvcache.rs:145-189 (kernels.cu:97-142, 321-336 there).
+#include "common.cuh"
+
+#define RK_WARPS 4
+#define RK_MAX_DH 512
+
+template <typename T>
+__global__ void qk_norm_rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pool,
+                                           T* __restrict__ v_pool, const int* __restrict__ page_table,
+                                           const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                           const int* __restrict__ seq_slot, const float* __restrict__ q_gain,
+                                           const float* __restrict__ k_gain, float eps,
+                                           const float2* __restrict__ rope, int rope_rows, int rot, int H, int KV,
+                                           int Dh, int mpps, int page_size, int num_pages, int write_kv,
+                                           int* __restrict__ err) {
+    __shared__ float buf[RK_WARPS][RK_MAX_DH];
+    int t = blockIdx.x;
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int pos = tok_pos[t];
+    int slot = seq_slot[tok_seq[t]];
+    int page = -1;
+    if (write_kv) {
+        page = page_table[(size_t)slot * mpps + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicExch(err, 2);   // unmapped page: skip the write, report
+            page = -1;
+        }
+    }
+    if (rope && (pos < 0 || pos >= rope_rows)) {
+        if (threadIdx.x == 0) atomicExch(err, 3);
+        return;
+    }
+    int heads_total = H + 2 * KV;
+    int half = rot / 2;
+    const T* row = qkv + (size_t)t * heads_total * Dh;
+    float* x = buf[warp];
+    for (int h = warp; h < heads_total; h += RK_WARPS) {
+        const T* src = row + (size_t)h * Dh;
+        int which = h < H ? 0 : (h < H + KV ? 1 : 2);      // q, k, v
+        T* dst;
+        if (which == 0) {
+            dst = q_out + ((size_t)t * H + h) * Dh;
+        } else {
+            if (!write_kv || page < 0) continue;
+            int kvh = which == 1 ? h - H : h - H - KV;
+            T* pool = which == 1 ? k_pool : v_pool;
+            dst = pool + (((size_t)page * KV + kvh) * page_size + pos % page_size) * Dh;
+        }
+        if (which == 2) {
+            for (int d = lane; d < Dh; d += 32) dst[d] = src[d];
+            continue;
+        }
+        const float* gain = which == 0 ? q_gain : k_gain;
+        float ss = 0.0f;
+        for (int d = lane; d < Dh; d += 32) {
+            float v = ld_f(src + d);
+            x[d] = v;
+            ss += v * v;
+        }
+        if (gain) {
+            ss = warp_sum(ss);
+            float inv = 1.0f / sqrtf(ss / (float)Dh + eps);
+            for (int d = lane; d < Dh; d += 32) x[d] = x[d] * inv * gain[d];
+        }
+        __syncwarp();
+        if (rope) {
+            const float2* cs = rope + (size_t)pos * half;
+            for (int d = lane; d < half; d += 32) {
+                float a = x[d], b = x[d + half];
+                float2 c = cs[d];
+                st_f(dst + d, a * c.x - b * c.y);
+                st_f(dst + d + half, b * c.x + a * c.y);
+            }
+            for (int d = rot + lane; d < Dh; d += 32) st_f(dst + d, x[d]);
+        } else {
+            for (int d = lane; d < Dh; d += 32) st_f(dst + d, x[d]);
+        }
+        __syncwarp();
+    }
+}
+
+extern "C" int ri_qk_norm_rope_append(const void* qkv, void* q_out, void* k_pool, void* v_pool, const int* page_table,
+                                      const int* tok_seq, const int* tok_pos, const int* seq_slot, const float* q_gain,
+                                      const float* k_gain, float eps, const float* rope_table, int rope_rows, int rot,
+                                      int tokens, int H, int KV, int Dh, int mpps, int page_size, int num_pages,
+                                      int write_kv, int dtype, int* err_flag, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    RI_REQUIRE(tokens > 0 && H > 0 && KV > 0 && Dh > 0, "qk_norm_rope_append: bad sizes");
+    RI_REQUIRE(Dh <= RK_MAX_DH, "qk_norm_rope_append: head_dim %d exceeds the limit %d", Dh, RK_MAX_DH);
+    RI_REQUIRE(rot >= 0 && rot <= Dh && rot % 2 == 0, "qk_norm_rope_append: rotary_dim %d must be even and <= head_dim %d", rot, Dh);
+    RI_REQUIRE(!rope_table || rot > 0, "qk_norm_rope_append: a rope table needs rotary_dim > 0");
+    RI_REQUIRE(page_size > 0 && mpps > 0, "qk_norm_rope_append: bad page sizes");
+    if (dtype == RI_DTYPE_F32)
+        qk_norm_rope_append_kernel<float><<<tokens, 32 * RK_WARPS, 0, stream>>>(
+            (const float*)qkv, (float*)q_out, (float*)k_pool, (float*)v_pool, page_table, tok_seq, tok_pos, seq_slot,
+            q_gain, k_gain, eps, (const float2*)rope_table, rope_rows, rot, H, KV, Dh, mpps, page_size, num_pages,
+            write_kv, err_flag);
+    else if (dtype == RI_DTYPE_BF16)
+        qk_norm_rope_append_kernel<__nv_bfloat16><<<tokens, 32 * RK_WARPS, 0, stream>>>(
+            (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,
+            page_table, tok_seq, tok_pos, seq_slot, q_gain, k_gain, eps, (const float2*)rope_table, rope_rows, rot, H,
+            KV, Dh, mpps, page_size, num_pages, write_kv, err_flag);
+    else
+        RI_FAIL(-1, "qk_norm_rope_append: unknown dtype %d", dtype);
+    RI_CHECK_LAUNCH("qk_norm_rope_append");
+    return 0;
+}

@@ -1,0 +1,314 @@
+// Next-token selection on the device: greedy, temperature, top-k, top-p and
+// repetition penalty, with the meaning they have in thanhauco/rust-inference
+// src/sampling.rs:73-140:
+//
+//   x_i = logit_i, and for tokens already in the context x_i / penalty if
+//         x_i > 0 else x_i * penalty                                   (76-88)
+//   temperature <= 0: the first index of the maximum                   (89-91, 132-140)
+//   z_i = x_i / temperature; keep the top_k largest                    (93-98)
+//   order the kept ones by falling z, equal z by rising index          (99)
+//   p_i = exp(z_i - max) / sum                                         (101-104)
+//   top_p < 1: keep the shortest prefix whose sum reaches top_p        (105-117)
+//   draw: the first kept token, in that order, whose running sum of the
+//         renormalised p exceeds the uniform number u                  (119-127)
+//
+// Nothing is sorted.  Each token gets the key (ordered bits of z_i, V-1-i), so
+// that falling keys are exactly the reference's order, and a "prefix whose
+// weight reaches a target" is found by a radix search over the key, 12 bits a
+// pass, with weights summed as 64-bit integers (exp(z - max) * 2^32).  Integer
+// sums make the result independent of the order of the additions: the same
+// logits, options and u always give the same token.
+//
+// One block per row; rows are independent, so a sequence's draw does not depend
+// on what it is batched with.
+#include "common.cuh"
+#include <float.h>
+
+#define SP_THREADS 1024
+#define SP_DIGIT 12
+#define SP_BINS (1 << SP_DIGIT)
+#define SP_IDX_BITS 24
+#define SP_PASSES 5            // 5 * 12 = 60 >= 32 + 24 key bits
+
+typedef unsigned long long u64;
+
+__device__ __forceinline__ unsigned ordered_bits(float z) {
+    if (z != z) return 0u;                                   // NaN sorts last
+    unsigned u = __float_as_uint(z);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+struct RowView {
+    const float* logits;
+    const unsigned char* seen;     // may be null
+    float penalty;
+    float temperature;
+    int vocab;
+    __device__ __forceinline__ float x(int i) const {
+        float v = logits[i];
+        if (seen && seen[i]) v = v > 0.0f ? v / penalty : v * penalty;
+        return v;
+    }
+    __device__ __forceinline__ float z(int i) const { return x(i) / temperature; }
+    __device__ __forceinline__ u64 key(int i, float zi) const {
+        return ((u64)ordered_bits(zi) << SP_IDX_BITS) | (u64)((1u << SP_IDX_BITS) - 1u - (unsigned)i);
+    }
+};
+
+__device__ u64 block_sum_u64(u64 v, u64* red) {
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        u64 t = lane < (blockDim.x >> 5) ? red[lane] : 0;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+// weight of token i: 1 when counting, exp(z - zmax) * 2^32 as an integer otherwise
+__device__ __forceinline__ u64 weight_of(float zi, float zmax, int counting) {
+    if (counting) return 1ull;
+    return (u64)(expf(zi - zmax) * 4294967296.0f);
+}
+
+// The largest key K (among tokens with key >= floor_key) such that the weight of
+// all tokens with floor_key <= key and key >= K reaches `target`.  Returns 0 and
+// sets *found = 0 when even all of them together stay below the target.
+// `*reached` gets the weight of the tokens with key >= K.
+__device__ u64 radix_select(const RowView& r, float zmax, int counting, u64 floor_key, u64 target, u64* bins,
+                            u64* red, int* found, u64* reached) {
+    __shared__ u64 s_prefix, s_remaining, s_above;
+    __shared__ int s_found;
+    if (threadIdx.x == 0) { s_prefix = 0; s_remaining = target; s_above = 0; s_found = 1; }
+    __syncthreads();
+    for (int pass = SP_PASSES - 1; pass >= 0; pass--) {
+        int shift = pass * SP_DIGIT;
+        for (int b = threadIdx.x; b < SP_BINS; b += blockDim.x) bins[b] = 0;
+        __syncthreads();
+        u64 prefix = s_prefix;
+        for (int i = threadIdx.x; i < r.vocab; i += blockDim.x) {
+            float zi = r.z(i);
+            u64 k = r.key(i, zi);
+            if (k < floor_key) continue;
+            if (pass < SP_PASSES - 1 && (k >> (shift + SP_DIGIT)) != (prefix >> (shift + SP_DIGIT))) continue;
+            u64 w = weight_of(zi, zmax, counting);
+            if (w) atomicAdd(&bins[(unsigned)(k >> shift) & (SP_BINS - 1)], w);
+        }
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            // lane l owns bins [128 l, 128 l + 127]; walk from the top bin down
+            int lane = threadIdx.x;
+            const int per = SP_BINS / 32;
+            u64 mine = 0;
+            for (int b = 0; b < per; b++) mine += bins[lane * per + b];
+            // weight of all bins above this lane's range
+            u64 above = 0;
+            for (int l = 31; l > 0; l--) {
+                u64 v = __shfl_sync(0xffffffffu, mine, l);
+                if (lane < l) above += v;
+            }
+            u64 remaining = s_remaining;
+            int owner = (above < remaining && above + mine >= remaining) ? 1 : 0;
+            unsigned ballot = __ballot_sync(0xffffffffu, owner);
+            if (ballot == 0) {
+                if (lane == 0) s_found = 0;
+            } else if (owner) {
+                u64 acc = above;
+                int chosen = lane * per;
+                for (int b = per - 1; b >= 0; b--) {
+                    u64 w = bins[lane * per + b];
+                    if (acc + w >= remaining) { chosen = lane * per + b; break; }
+                    acc += w;
+                }
+                s_prefix = prefix | ((u64)chosen << shift);
+                s_remaining = remaining - acc;
+                s_above += acc;
+            }
+        }
+        __syncthreads();
+        if (!s_found) break;
+    }
+    __syncthreads();
+    int f = s_found;
+    u64 K = f ? s_prefix : 0;
+    __syncthreads();                 // every thread has its copies before the next call resets them
+    *found = f;
+    *reached = 0;
+    if (f) {
+        // exact weight of the tokens with floor_key <= key and key >= K
+        u64 part = 0;
+        for (int i = threadIdx.x; i < r.vocab; i += blockDim.x) {
+            float zi = r.z(i);
+            u64 k = r.key(i, zi);
+            if (k >= floor_key && k >= K) part += weight_of(zi, zmax, counting);
+        }
+        *reached = block_sum_u64(part, red);
+    }
+    return K;
+}
+
+__global__ void __launch_bounds__(SP_THREADS)
+sample_kernel(const float* __restrict__ logits, long long row_stride, const unsigned char* __restrict__ seen,
+              const int* __restrict__ seen_rows, long long seen_stride, int vocab, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ penalty,
+              const float* __restrict__ uniform, int* __restrict__ out) {
+    __shared__ u64 bins[SP_BINS];
+    __shared__ u64 red[33];
+    __shared__ float fred[33];
+    __shared__ int ired[33];
+    int row = blockIdx.x;
+    RowView r;
+    r.logits = logits + (size_t)row * row_stride;
+    r.penalty = penalty ? penalty[row] : 1.0f;
+    r.seen = (seen && r.penalty != 1.0f) ? seen + (size_t)(seen_rows ? seen_rows[row] : row) * seen_stride : nullptr;
+    r.temperature = temperature[row];
+    r.vocab = vocab;
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    // maximum of x and its first index (greedy answer; also the softmax shift)
+    float best = -FLT_MAX;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        float v = r.x(i);
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) { fred[warp] = best; ired[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++)
+            if (fred[w] > best || (fred[w] == best && ired[w] < bi)) { best = fred[w]; bi = ired[w]; }
+        if (bi == 0x7fffffff) bi = 0;          // a row of NaN: the reference's loop also ends at index 0
+        fred[32] = best;
+        ired[32] = bi;
+    }
+    __syncthreads();
+    best = fred[32];
+    bi = ired[32];
+    if (!(r.temperature > 0.0f)) {
+        if (threadIdx.x == 0) out[row] = bi;
+        return;
+    }
+    float zmax = best / r.temperature;
+
+    int found;
+    u64 reached;
+    u64 floor_key = 0;
+    int k = top_k ? top_k[row] : 0;
+    if (k > 0 && k < vocab) {
+        u64 K = radix_select(r, zmax, 1, 0, (u64)k, bins, red, &found, &reached);
+        if (found) floor_key = K;
+    }
+    // total weight of the kept tokens
+    u64 part = 0;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        float zi = r.z(i);
+        if (r.key(i, zi) >= floor_key) part += weight_of(zi, zmax, 0);
+    }
+    u64 total = block_sum_u64(part, red);
+    float tp = top_p ? top_p[row] : 1.0f;
+    if (tp < 1.0f) {
+        double want = (double)tp * (double)total;
+        u64 target = (u64)want;
+        if ((double)target < want) target += 1;           // ceil
+        if (target < 1) target = 1;
+        u64 K = radix_select(r, zmax, 0, floor_key, target, bins, red, &found, &reached);
+        if (found) { floor_key = K; total = reached; }
+    }
+    double ru = (double)uniform[row] * (double)total;
+    u64 target = (u64)ru + 1;                               // running sum > u * total
+    if (target > total) target = total;
+    u64 K = radix_select(r, zmax, 0, floor_key, target, bins, red, &found, &reached);
+    if (threadIdx.x == 0) {
+        int tok;
+        if (found) tok = (int)(((1u << SP_IDX_BITS) - 1u) - (unsigned)(K & ((1u << SP_IDX_BITS) - 1u)));
+        else tok = bi;                                      // cannot happen for total > 0; stay in range
+        if (total == 0) tok = bi;
+        out[row] = tok;
+    }
+}
+
+extern "C" int ri_sample(const float* logits, long long row_stride, int rows, int vocab, const unsigned char* seen,
+                         const int* seen_rows, long long seen_stride, const float* temperature, const int* top_k,
+                         const float* top_p, const float* penalty, const float* uniform, int* out,
+                         cudaStream_t stream) {
+    if (rows == 0) return 0;
+    RI_REQUIRE(rows > 0 && vocab > 0, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
+    RI_REQUIRE(vocab <= (1 << SP_IDX_BITS), "sample: vocabulary %d exceeds the limit %d", vocab, 1 << SP_IDX_BITS);
+    RI_REQUIRE(temperature && uniform && out, "sample: temperature, uniform and out are required");
+    sample_kernel<<<rows, SP_THREADS, 0, stream>>>(logits, row_stride, seen, seen_rows, seen_stride, vocab,
+                                                   temperature, top_k, top_p, penalty, uniform, out);
+    RI_CHECK_LAUNCH("sample");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// greedy only: first index of the row maximum (src/ops/reduce.rs:9-28)
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(SP_THREADS)
+argmax_kernel(const float* __restrict__ logits, long long row_stride, int vocab, int* __restrict__ out) {
+    __shared__ float fred[32];
+    __shared__ int ired[32];
+    const float* x = logits + (size_t)blockIdx.x * row_stride;
+    float best = -FLT_MAX;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        float v = x[i];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { fred[warp] = best; ired[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++)
+            if (fred[w] > best || (fred[w] == best && ired[w] < bi)) { best = fred[w]; bi = ired[w]; }
+        out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+
+extern "C" int ri_argmax(const float* logits, long long row_stride, int rows, int vocab, int* out,
+                         cudaStream_t stream) {
+    if (rows == 0) return 0;
+    RI_REQUIRE(rows > 0 && vocab > 0, "argmax: bad sizes rows=%d vocab=%d", rows, vocab);
+    argmax_kernel<<<rows, SP_THREADS, 0, stream>>>(logits, row_stride, vocab, out);
+    RI_CHECK_LAUNCH("argmax");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// seen[row, token] = 1 for the given (row, token) pairs: the context of the
+// repetition penalty, kept per sequence beside the cache.
+// ---------------------------------------------------------------------------
+__global__ void mark_seen_kernel(unsigned char* __restrict__ seen, long long seen_stride, const int* __restrict__ rows,
+                                 const int* __restrict__ tokens, int n, int vocab) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int t = tokens[i];
+    if (t >= 0 && t < vocab) seen[(size_t)rows[i] * seen_stride + t] = 1;
+}
+
+extern "C" int ri_mark_seen(unsigned char* seen, long long seen_stride, const int* rows, const int* tokens, int n,
+                            int vocab, cudaStream_t stream) {
+    if (n == 0) return 0;
+    mark_seen_kernel<<<(n + 255) / 256, 256, 0, stream>>>(seen, seen_stride, rows, tokens, n, vocab);
+    RI_CHECK_LAUNCH("mark_seen");
+    return 0;
+}

@@ -1,0 +1,217 @@
+"""The step function: a batch of sequences, each bringing its next tokens.
+
+``Engine.step`` takes, for every sequence of the batch, its cache slot and the
+tokens it brings (a whole prompt, a piece of one, or one decoded token), runs
+exactly those tokens as one packed batch against the cache that earlier steps
+left, and returns float32 logits at the wanted places.  Sequences may bring
+different numbers of tokens; nothing is padded, so padding cannot change a
+result.  Positions come from the cache lengths, so a caller cannot give
+positions that disagree with the cache (in the reference they are separate
+arguments, thanhauco/rust-inference src/models/mod.rs:36-44).
+
+Steps in which every sequence brings one token are replayed from a CUDA graph
+per batch size: the step's small tables are copied to fixed device buffers and
+the captured kernels read them from there.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Union
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache import Cache, CacheError, PAGE_SIZE
+from ..parts.base import StepContext
+from .model import Model
+
+
+@dataclass
+class Entry:
+    """One sequence's share of a step: ``want`` lists the places among ``tokens``
+    whose logits are asked for ("last", "all", or indices; may be empty)."""
+    slot: int
+    tokens: Sequence[int]
+    want: Union[str, Sequence[int]] = "last"
+
+
+class StepError(ValueError):
+    pass
+
+
+class _Tables:
+    """The int32 tables of a step in one device buffer (one copy from the host)."""
+
+    def __init__(self, T: int, B: int, W: int, device):
+        self.T, self.B, self.W = T, B, W
+        sizes = (T, T, T, W, B, B + 1, B)
+        self.offsets = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+        total = int(self.offsets[-1])
+        self.pinned = device.type == "cuda"
+        self.host = torch.empty(total, dtype=torch.int32, pin_memory=self.pinned)
+        self.host_np = self.host.numpy()
+        self.dev = torch.empty(total, dtype=torch.int32, device=device)
+        self.event = torch.cuda.Event() if self.pinned else None
+        self.used = False
+
+    def part(self, i: int, host: bool = False):
+        lo, hi = int(self.offsets[i]), int(self.offsets[i + 1])
+        return (self.host_np if host else self.dev)[lo:hi]
+
+    def upload(self) -> None:
+        self.dev.copy_(self.host, non_blocking=True)
+        if self.event is not None:
+            self.event.record()
+        self.used = True
+
+    def wait_host_free(self) -> None:
+        if self.used and self.event is not None:
+            self.event.synchronize()
+
+
+class Engine:
+    """A model with its cache.
+
+    ``max_tokens``: tokens the cache holds over all live sequences (rounded up
+    to whole pages per sequence); ``max_seqs``: slots; ``max_seq_len``: the
+    longest a single sequence may get (default: what the model allows, capped by
+    ``max_tokens``)."""
+
+    def __init__(self, model: Model, max_tokens: int, max_seqs: int, max_seq_len: Optional[int] = None,
+                 use_graphs: bool = True, page_size: int = PAGE_SIZE):
+        self.model = model
+        self.device = model.env.device
+        self.dtype = model.env.dtype
+        num_pages = max(1, -(-max_tokens // page_size))
+        limit = model.spec.max_positions
+        if max_seq_len is not None:
+            limit = min(limit, max_seq_len)
+        limit = min(limit, num_pages * page_size)
+        self.max_seq_len = limit
+        self.cache = Cache(model.cache_requests(), max(1, max_seqs), num_pages, max(1, -(-limit // page_size)),
+                           self.dtype, self.device, page_size)
+        model.prepare(self.cache.max_seq_len)
+        self.use_graphs = use_graphs and self.device.type == "cuda"
+        self._decode_tables = {}
+        self._graphs = {}
+        self._warm = set()
+        self.graph_replays = 0
+
+    # ---- sequences ------------------------------------------------------------------------
+    def new_sequence(self) -> int:
+        return self.cache.alloc_slot()
+
+    def release(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ---- one step --------------------------------------------------------------------------
+    def step(self, entries: Sequence[Entry]) -> torch.Tensor:
+        """Run the step; float32 logits [wanted places in entry order, vocab] on the device."""
+        if not entries:
+            raise StepError("a step needs at least one sequence")
+        V = self.model.spec.vocab_size
+        news, wants = [], []
+        for e in entries:
+            toks = np.asarray(e.tokens, dtype=np.int64).reshape(-1)
+            if toks.size == 0:
+                raise StepError(f"slot {e.slot} brings no token")
+            if toks.min() < 0 or toks.max() >= V:
+                raise StepError(f"slot {e.slot}: token id outside the vocabulary of {V}")
+            news.append(toks)
+            if isinstance(e.want, str):
+                if e.want == "last":
+                    w = [toks.size - 1]
+                elif e.want == "all":
+                    w = list(range(toks.size))
+                else:
+                    raise StepError(f"want must be 'last', 'all' or a list of places, got {e.want!r}")
+            else:
+                w = [int(i) for i in e.want]
+                if any(i < 0 or i >= toks.size for i in w):
+                    raise StepError(f"slot {e.slot}: wanted place outside its {toks.size} tokens")
+            wants.append(w)
+        slots = [int(e.slot) for e in entries]
+        before = self.cache.extend([(s, len(t)) for s, t in zip(slots, news)])
+        self.cache.upload()
+
+        B = len(entries)
+        T = sum(len(t) for t in news)
+        W = sum(len(w) for w in wants)
+        decode = all(len(t) == 1 for t in news)
+        graphable = self.use_graphs and decode and W == B and all(w == [0] for w in wants)
+        tables = self._tables_for(T, B, W, graphable)
+        tables.wait_host_free()
+        ids, tok_seq, tok_pos, want_rows = (tables.part(i, host=True) for i in range(4))
+        seq_slot, seq_start, seq_len = (tables.part(i, host=True) for i in range(4, 7))
+        t0 = w0 = 0
+        for b, (toks, w, s, L) in enumerate(zip(news, wants, slots, before)):
+            n = len(toks)
+            ids[t0:t0 + n] = toks
+            tok_seq[t0:t0 + n] = b
+            tok_pos[t0:t0 + n] = np.arange(L, L + n)
+            want_rows[w0:w0 + len(w)] = [t0 + i for i in w]
+            seq_slot[b], seq_start[b], seq_len[b] = s, t0, L + n
+            t0 += n
+            w0 += len(w)
+        seq_start[B] = T
+        tables.upload()
+        ctx = StepContext(
+            tok_seq=tables.part(1), tok_pos=tables.part(2), seq_slot=tables.part(4), seq_start=tables.part(5),
+            seq_len=tables.part(6), num_tokens=T, num_seqs=B, max_new=max(len(t) for t in news),
+            max_len=max(L + len(t) for L, t in zip(before, news)), host_seq_slot=tuple(slots),
+            host_new=tuple(len(t) for t in news), host_len=tuple(L + len(t) for L, t in zip(before, news)))
+        if W == 0:
+            want_dev = tables.part(2)[:0]
+        else:
+            want_dev = tables.part(3)
+        if graphable:
+            logits = self._decode_step(tables, ctx, want_dev)
+        else:
+            logits = self.model.forward(tables.part(0), ctx, self.cache, want_dev)
+        self.cache.after_step(slots)
+        return logits
+
+    # ---- graphs for one-token steps ------------------------------------------------------------
+    def _tables_for(self, T, B, W, graphable) -> _Tables:
+        if graphable:
+            t = self._decode_tables.get(B)
+            if t is None:
+                t = self._decode_tables[B] = _Tables(T, B, W, self.device)
+            return t
+        return _Tables(T, B, W, self.device)
+
+    def _graph_key(self, ctx) -> tuple:
+        return (ctx.num_seqs,)
+
+    def _decode_step(self, tables, ctx, want_dev):
+        key = self._graph_key(ctx)
+        rec = self._graphs.get(key)
+        if rec is not None:
+            rec[0].replay()
+            self.graph_replays += 1
+            return rec[1]
+        if key not in self._warm:
+            # the first step of this shape runs eagerly: libraries set themselves up
+            self._warm.add(key)
+            return self.model.forward(tables.part(0), ctx, self.cache, want_dev)
+        graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize(self.device)
+        with torch.cuda.graph(graph):
+            out = self.model.forward(tables.part(0), ctx, self.cache, want_dev)
+        self._graphs[key] = (graph, out)
+        graph.replay()
+        self.graph_replays += 1
+        return out
+
+    # ---- errors the kernels reported ------------------------------------------------------------
+    def check_device_errors(self) -> None:
+        if self.device.type != "cuda":
+            return
+        code = int(ops.error_flag(self.device).item())
+        if code:
+            ops.error_flag(self.device).zero_()
+            raise RuntimeError(f"a kernel refused an index: {ops.ERROR_TEXT.get(code, code)}")

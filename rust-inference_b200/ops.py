@@ -1,0 +1,288 @@
+"""The kernels of ``csrc/`` as Python functions on torch CUDA tensors.
+
+Each function checks shapes, dtypes and devices, allocates its output with
+torch and launches on torch's current stream.  There is no other
+implementation behind these names: on a machine without the compiled
+libraries (or without nvcc to make them) they raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc import build as _build
+
+F32, BF16 = 0, 1
+_P = ctypes.c_void_p
+_I = ctypes.c_int
+_L = ctypes.c_longlong
+_F = ctypes.c_float
+
+_SIGNATURES = {
+    ("elementwise", "ri_embed_rows"): [_P, _P, _P, _I, _I, _I, _I, _P, _P],
+    ("elementwise", "ri_rmsnorm"): [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _P],
+    ("elementwise", "ri_add_rows"): [_P, _P, _L, _I, _P],
+    ("elementwise", "ri_silu_mul"): [_P, _P, _I, _I, _I, _P],
+    ("rope_kv", "ri_qk_norm_rope_append"): [_P] * 10 + [_F, _P, _I, _I] + [_I] * 9 + [_P, _P],
+    ("attention_plain", "ri_attention_plain"): [_P] * 8 + [_I] * 7 + [_F, _I, _I, _P, _P],
+    ("linear_f32", "ri_linear_f32"): [_P, _P, _P, _I, _I, _I, _P],
+    ("sampling", "ri_sample"): [_P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P],
+    ("sampling", "ri_argmax"): [_P, _L, _I, _I, _P, _P],
+    ("sampling", "ri_mark_seen"): [_P, _L, _P, _P, _I, _I, _P],
+}
+_fn_cache = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _fn(lib_name: str, fn_name: str, defines=None):
+    key = (lib_name, fn_name, tuple(sorted((defines or {}).items())))
+    f = _fn_cache.get(key)
+    if f is None:
+        lib = _build.library(lib_name, defines)
+        f = getattr(lib, fn_name)
+        f.argtypes = _SIGNATURES[(lib_name, fn_name)]
+        f.restype = _I
+        _fn_cache[key] = f = (f, lib)
+    return f
+
+
+def _call(lib_name: str, fn_name: str, *args, defines=None):
+    f, lib = _fn(lib_name, fn_name, defines)
+    rc = f(*args)
+    if rc != 0:
+        raise KernelError(f"{fn_name}: {lib.ri_last_error().decode(errors='replace')} (code {rc})")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"the kernels work in float32 or bfloat16, not {dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise KernelError(f"{name} must have shape {tuple(shape)}, got {tuple(t.shape)}")
+
+
+_err_flags = {}
+
+
+def error_flag(device) -> torch.Tensor:
+    """One int32 per device that kernels set when they meet an index they must
+    not follow (an unmapped page, a token id or position out of range).  The
+    engine reads it whenever it synchronises anyway."""
+    dev = torch.device(device)
+    key = (dev.type, dev.index if dev.index is not None else torch.cuda.current_device())
+    f = _err_flags.get(key)
+    if f is None:
+        f = torch.zeros(1, dtype=torch.int32, device=dev)
+        _err_flags[key] = f
+    return f
+
+
+ERROR_TEXT = {1: "token id outside the vocabulary", 2: "cache write to an unmapped page",
+              3: "position beyond the rotary table", 4: "attention read from an unmapped page"}
+
+
+# ---------------------------------------------------------------------------------------
+def embed(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    """float32 rows ``table[ids]``: [tokens, dim]."""
+    _need(ids, "ids", torch.int32)
+    _need(table, "table")
+    tokens, (vocab, dim) = ids.numel(), table.shape
+    out = torch.empty((tokens, dim), dtype=torch.float32, device=table.device)
+    _call("elementwise", "ri_embed_rows", ids.data_ptr(), table.data_ptr(), out.data_ptr(), tokens, dim, vocab,
+          _code(table.dtype), error_flag(table.device).data_ptr(), _stream())
+    return out
+
+
+def rmsnorm(resid: torch.Tensor, gain: torch.Tensor, eps: float, out_dtype: torch.dtype,
+            delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """RMSNorm of the float32 residual stream ``resid`` [n, dim].
+
+    With ``delta`` (compute dtype, same shape) the sum resid + delta is normed,
+    and written back into ``resid`` unless ``rows`` is given.  With ``rows``
+    (int32 indices) only those rows are normed, in that order."""
+    _need(resid, "resid", torch.float32)
+    n, dim = resid.shape
+    _need(gain, "gain", torch.float32, (dim,))
+    if delta is not None:
+        _need(delta, "delta", out_dtype, (n, dim))
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    n_out = n if rows is None else rows.numel()
+    out = torch.empty((n_out, dim), dtype=out_dtype, device=resid.device)
+    _call("elementwise", "ri_rmsnorm", resid.data_ptr(), _ptr(delta), _ptr(rows), gain.data_ptr(), out.data_ptr(),
+          n_out, dim, float(eps), 1, _code(out_dtype), _stream())
+    return out
+
+
+def add_rows(resid: torch.Tensor, delta: torch.Tensor) -> None:
+    """resid += delta (float32 += compute dtype)."""
+    _need(resid, "resid", torch.float32)
+    _need(delta, "delta", None, resid.shape)
+    _call("elementwise", "ri_add_rows", resid.data_ptr(), delta.data_ptr(), resid.numel(), _code(delta.dtype), _stream())
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up for ``gate_up`` [rows, 2*inter] (gate first)."""
+    _need(gate_up, "gate_up")
+    rows, two = gate_up.shape
+    if two % 2:
+        raise KernelError("silu_mul: the last dimension must be even")
+    out = torch.empty((rows, two // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _call("elementwise", "ri_silu_mul", gate_up.data_ptr(), out.data_ptr(), rows, two // 2, _code(gate_up.dtype), _stream())
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """y = x w^T for x [M, K], w [N, K].
+
+    float32: this package's own FMA kernel (no tensor cores, no TF32).
+    bfloat16: the library GEMM (cuBLAS through torch), as the reference engine
+    uses cuBLAS for its linears (src/cuda/mod.rs:186-232 there); ``out_dtype``
+    float32 keeps the float32 accumulator (used for the logits)."""
+    _need(x, "x")
+    _need(w, "w", x.dtype)
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelError(f"linear: x has {K} columns, w has {K2}")
+    if x.dtype == torch.float32:
+        y = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        _call("linear_f32", "ri_linear_f32", x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K, _stream())
+        return y
+    if x.dtype != torch.bfloat16:
+        raise KernelError(f"linear: dtype {x.dtype}")
+    if out_dtype == torch.float32:
+        return torch.mm(x, w.t(), out_dtype=torch.float32)
+    return torch.mm(x, w.t())
+
+
+def qk_norm_rope_append(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                        q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], eps: float,
+                        rope_table: Optional[torch.Tensor], rotary_dim: int,
+                        k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
+                        tok_seq: torch.Tensor, tok_pos: torch.Tensor, seq_slot: torch.Tensor,
+                        write_kv: bool = True) -> torch.Tensor:
+    """Norm and rotate the q and k heads of ``qkv`` [tokens, (H+2KV)*Dh], append k
+    and v to the pools [pages, KV, page_size, Dh]; returns q [tokens, H, Dh]."""
+    _need(qkv, "qkv")
+    tokens = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise KernelError(f"qkv has {qkv.shape[1]} columns, expected {(num_heads + 2 * num_kv_heads) * head_dim}")
+    pages, kvh, page_size, dh = k_pool.shape
+    if (kvh, dh) != (num_kv_heads, head_dim) or v_pool.shape != k_pool.shape:
+        raise KernelError(f"cache pools {tuple(k_pool.shape)} / {tuple(v_pool.shape)} do not fit {num_kv_heads} kv heads of {head_dim}")
+    _need(k_pool, "k_pool", qkv.dtype)
+    _need(v_pool, "v_pool", qkv.dtype)
+    _need(page_table, "page_table", torch.int32)
+    for t, n in ((tok_seq, "tok_seq"), (tok_pos, "tok_pos"), (seq_slot, "seq_slot")):
+        _need(t, n, torch.int32)
+    for g, n in ((q_gain, "q_gain"), (k_gain, "k_gain")):
+        if g is not None:
+            _need(g, n, torch.float32, (head_dim,))
+    rope_rows = 0
+    if rope_table is not None:
+        _need(rope_table, "rope_table", torch.float32)
+        if rope_table.dim() != 3 or rope_table.shape[1] != rotary_dim // 2 or rope_table.shape[2] != 2:
+            raise KernelError(f"rope table must be [positions, {rotary_dim // 2}, 2], got {tuple(rope_table.shape)}")
+        rope_rows = rope_table.shape[0]
+    q = torch.empty((tokens, num_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+    _call("rope_kv", "ri_qk_norm_rope_append", qkv.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+          page_table.data_ptr(), tok_seq.data_ptr(), tok_pos.data_ptr(), seq_slot.data_ptr(), _ptr(q_gain),
+          _ptr(k_gain), float(eps), _ptr(rope_table), rope_rows, rotary_dim, tokens, num_heads, num_kv_heads,
+          head_dim, page_table.shape[1], page_size, pages, 1 if write_kv else 0, _code(qkv.dtype),
+          error_flag(qkv.device).data_ptr(), _stream())
+    return q
+
+
+def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
+              tok_seq: torch.Tensor, tok_pos: torch.Tensor, seq_slot: torch.Tensor, scale: float,
+              window: int = 0) -> torch.Tensor:
+    """Causal attention of q [tokens, H, Dh] over the paged cache; [tokens, H, Dh]."""
+    _need(q, "q")
+    tokens, H, Dh = q.shape
+    pages, KV, page_size, dh = k_pool.shape
+    if dh != Dh or v_pool.shape != k_pool.shape:
+        raise KernelError(f"attention: pools {tuple(k_pool.shape)} do not fit head_dim {Dh}")
+    _need(k_pool, "k_pool", q.dtype)
+    _need(v_pool, "v_pool", q.dtype)
+    _need(page_table, "page_table", torch.int32)
+    out = torch.empty_like(q)
+    _call("attention_plain", "ri_attention_plain", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
+          page_table.data_ptr(), tok_seq.data_ptr(), tok_pos.data_ptr(), seq_slot.data_ptr(), tokens, H, KV, Dh,
+          page_table.shape[1], page_size, pages, float(scale), int(window), _code(q.dtype),
+          error_flag(q.device).data_ptr(), _stream())
+    return out
+
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    """First index of each row's maximum: int32 [rows]."""
+    _need(logits, "logits", torch.float32)
+    rows, vocab = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _call("sampling", "ri_argmax", logits.data_ptr(), logits.stride(0), rows, vocab, out.data_ptr(), _stream())
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
+           top_k: Optional[torch.Tensor] = None, top_p: Optional[torch.Tensor] = None,
+           penalty: Optional[torch.Tensor] = None, seen: Optional[torch.Tensor] = None,
+           seen_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of float32 ``logits`` [rows, vocab]; the options are
+    per-row device tensors (temperature float32, top_k int32, top_p float32,
+    penalty float32), ``uniform`` the per-row number in [0, 1)."""
+    _need(logits, "logits", torch.float32)
+    rows, vocab = logits.shape
+    _need(temperature, "temperature", torch.float32, (rows,))
+    _need(uniform, "uniform", torch.float32, (rows,))
+    if top_k is not None:
+        _need(top_k, "top_k", torch.int32, (rows,))
+    if top_p is not None:
+        _need(top_p, "top_p", torch.float32, (rows,))
+    if penalty is not None:
+        _need(penalty, "penalty", torch.float32, (rows,))
+    seen_stride = 0
+    if seen is not None:
+        _need(seen, "seen", torch.uint8)
+        if seen.shape[1] != vocab:
+            raise KernelError("seen must be [rows, vocab]")
+        seen_stride = seen.stride(0)
+        if seen_rows is not None:
+            _need(seen_rows, "seen_rows", torch.int32, (rows,))
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _call("sampling", "ri_sample", logits.data_ptr(), logits.stride(0), rows, vocab, _ptr(seen), _ptr(seen_rows),
+          seen_stride, temperature.data_ptr(), _ptr(top_k), _ptr(top_p), _ptr(penalty), uniform.data_ptr(),
+          out.data_ptr(), _stream())
+    return out
+
+
+def mark_seen(seen: torch.Tensor, rows: torch.Tensor, tokens: torch.Tensor) -> None:
+    """seen[rows[i], tokens[i]] = 1."""
+    _need(seen, "seen", torch.uint8)
+    _need(rows, "rows", torch.int32)
+    _need(tokens, "tokens", torch.int32, rows.shape)
+    _call("sampling", "ri_mark_seen", seen.data_ptr(), seen.stride(0), rows.data_ptr(), tokens.data_ptr(),
+          rows.numel(), seen.shape[1], _stream())
