@@ -15,7 +15,7 @@
 // Nothing is sorted.  Each token gets the key (ordered bits of z_i, V-1-i), so
 // that falling keys are exactly the reference's order, and a "prefix whose
 // weight reaches a target" is found by a radix search over the key, 12 bits a
-// pass, with weights summed as 64-bit integers (exp(z - max) * 2^32).  Integer
+// pass, with weights summed as 64-bit integers (exp(z - max) * 2^40).  Integer
 // sums make the result independent of the order of the additions: the same
 // logits, options and u always give the same token.
 //
@@ -72,10 +72,10 @@ __device__ u64 block_sum_u64(u64 v, u64* red) {
     return red[32];
 }
 
-// weight of token i: 1 when counting, exp(z - zmax) * 2^32 as an integer otherwise
+// weight of token i: 1 when counting, exp(z - zmax) * 2^40 as an integer otherwise
 __device__ __forceinline__ u64 weight_of(float zi, float zmax, int counting) {
     if (counting) return 1ull;
-    return (u64)(expf(zi - zmax) * 4294967296.0f);
+    return (u64)(expf(zi - zmax) * 1099511627776.0f);      // 2^40: exact scaling, sums stay below 2^64
 }
 
 // The largest key K (among tokens with key >= floor_key) such that the weight of

@@ -1,0 +1,314 @@
+"""Each CUDA kernel alone against a plain float64 restatement, at sizes other than
+the engine's configurations (odd widths, head sizes in steps of 16, vocabularies
+that are no power of two)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+# elementwise kernels: one rounding of the output in bfloat16 (2^-8 relative)
+ETOL = {"float32": 2e-6, "bfloat16": 5e-3}
+
+
+def dev(a, dtype=torch.float32):
+    return torch.as_tensor(np.ascontiguousarray(a)).to("cuda", dtype=dtype).contiguous()
+
+
+def rnd(rng, *shape, scale=1.0, dtype="float32"):
+    x = (rng.standard_normal(shape) * scale).astype(np.float32)
+    return plain.bf16_round(x) if dtype == "bfloat16" else x
+
+
+def close(got, want, tol, what):
+    got = got.detach().float().cpu().numpy().astype(np.float64)
+    err = np.abs(got - want).max()
+    bound = tol * max(1e-6, np.abs(want).max())
+    assert err <= bound, f"{what}: max error {err:.3e} > {bound:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embed(dtype):
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(0)
+    table = rnd(rng, 1000, 72, dtype=dtype)
+    ids = rng.integers(0, 1000, size=37)
+    got = ops.embed(dev(ids, torch.int32), dev(table, DT[dtype]))
+    assert got.dtype == torch.float32
+    close(got, plain.embedding(ids, table), 0, "embed")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dim", [24, 72, 1000, 5120])
+def test_rmsnorm(dtype, dim):
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(dim)
+    resid = rnd(rng, 19, dim)
+    delta = rnd(rng, 19, dim, dtype=dtype)
+    gain = (1 + 0.1 * rng.standard_normal(dim)).astype(np.float32)
+    eps = 1e-5
+    r = dev(resid)
+    got = ops.rmsnorm(r, dev(gain), eps, DT[dtype])
+    close(got, plain.rms_norm(resid, gain, eps), ETOL[dtype], "rmsnorm")
+    close(r, resid.astype(np.float64), 0, "rmsnorm must not touch the stream without a delta")
+    got = ops.rmsnorm(r, dev(gain), eps, DT[dtype], delta=dev(delta, DT[dtype]))
+    total = resid.astype(np.float64) + delta
+    close(got, plain.rms_norm(total, gain, eps), ETOL[dtype], "add+rmsnorm")
+    close(r, total, 2e-7, "add+rmsnorm writes the sum back in float32")
+    rows = np.array([3, 3, 0, 18], dtype=np.int32)
+    r2 = dev(resid)
+    got = ops.rmsnorm(r2, dev(gain), eps, DT[dtype], delta=dev(delta, DT[dtype]), rows=dev(rows, torch.int32))
+    close(got, plain.rms_norm(total[rows], gain, eps), ETOL[dtype], "gathered add+rmsnorm")
+    close(r2, resid.astype(np.float64), 0, "gathered norm leaves the stream alone")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_silu_mul(dtype):
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(1)
+    gu = rnd(rng, 7, 2 * 88, scale=3.0, dtype=dtype)
+    got = ops.silu_mul(dev(gu, DT[dtype]))
+    g, u = gu[:, :88].astype(np.float64), gu[:, 88:].astype(np.float64)
+    close(got, plain.silu(g) * u, ETOL[dtype], "silu_mul")
+
+
+@pytest.mark.parametrize("shape", [(1, 64, 64), (5, 37, 70), (64, 192, 96), (130, 257, 1000), (3, 1000, 24)])
+def test_linear_f32(shape):
+    from rust_inference_b200 import ops
+    M, N, K = shape
+    rng = np.random.default_rng(M + N)
+    x, w = rnd(rng, M, K), rnd(rng, N, K)
+    got = ops.linear(dev(x), dev(w))
+    close(got, plain.linear(x, w), 3e-6, f"linear_f32 {shape}")
+    # a row's result does not depend on the rows around it
+    alone = ops.linear(dev(x[M - 1:M]), dev(w))
+    assert torch.equal(alone[0], got[M - 1])
+
+
+@pytest.mark.parametrize("shape", [(1, 64, 64), (5, 48, 80), (300, 264, 1000)])
+def test_linear_bf16(shape):
+    from rust_inference_b200 import ops
+    M, N, K = shape
+    rng = np.random.default_rng(M)
+    x, w = rnd(rng, M, K, dtype="bfloat16"), rnd(rng, N, K, dtype="bfloat16")
+    want = plain.linear(x, w)
+    close(ops.linear(dev(x, torch.bfloat16), dev(w, torch.bfloat16)), want, 5e-3, "linear bf16")
+    close(ops.linear(dev(x, torch.bfloat16), dev(w, torch.bfloat16), out_dtype=torch.float32), want, 2e-5,
+          "linear bf16 -> f32")
+
+
+def _paged(rng, lens, KV, Dh, P, dtype, extra_pages=3):
+    """Random pools with a shuffled page table for sequences of the given lengths."""
+    pages_per = [-(-n // P) for n in lens]
+    total = sum(pages_per) + extra_pages
+    order = rng.permutation(total)
+    mpps = max(pages_per) + 1
+    table = np.full((len(lens) + 2, mpps), -1, dtype=np.int32)
+    slots = rng.permutation(len(lens) + 2)[:len(lens)]
+    k = 0
+    for b, n in enumerate(pages_per):
+        table[slots[b], :n] = order[k:k + n]
+        k += n
+    return table, slots.astype(np.int32), total
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,KV,Dh,window", [(4, 2, 16, 0), (6, 1, 32, 0), (3, 3, 48, 0), (8, 2, 128, 0),
+                                            (5, 5, 80, 37), (4, 1, 256, 0), (2, 1, 64, 5)])
+def test_norm_rope_append_then_attention(dtype, H, KV, Dh, window):
+    """New tokens of several sequences against an existing cache: the appended keys and
+    values land in the right page rows and every query sees exactly its keys."""
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(H * 1000 + Dh)
+    P = 32
+    old = [0, 31, 64, 70]                     # cache lengths before the step
+    new = [40, 1, 3, 27]                      # tokens each sequence brings
+    lens = [a + b for a, b in zip(old, new)]
+    table, slots, total = _paged(rng, lens, KV, Dh, P, dtype)
+    tdt = DT[dtype]
+    eps, theta, rot = 1e-5, 10000.0, Dh - 16 if Dh > 32 else Dh
+    # full k/v history in plain form (already normed and rotated), then the new raw tokens
+    k_hist = [rnd(rng, n, KV, Dh, dtype=dtype) for n in old]
+    v_hist = [rnd(rng, n, KV, Dh, dtype=dtype) for n in old]
+    k_pool = np.zeros((total, KV, P, Dh), dtype=np.float32)
+    v_pool = np.zeros_like(k_pool)
+    for b, n in enumerate(old):
+        for j in range(n):
+            pg = table[slots[b], j // P]
+            k_pool[pg, :, j % P] = k_hist[b][j]
+            v_pool[pg, :, j % P] = v_hist[b][j]
+    T = sum(new)
+    qkv = rnd(rng, T, (H + 2 * KV) * Dh, dtype=dtype)
+    qg = (1 + 0.1 * rng.standard_normal(Dh)).astype(np.float32)
+    kg = (1 + 0.1 * rng.standard_normal(Dh)).astype(np.float32)
+    tok_seq = np.concatenate([np.full(n, b) for b, n in enumerate(new)]).astype(np.int32)
+    tok_pos = np.concatenate([np.arange(o, o + n) for o, n in zip(old, new)]).astype(np.int32)
+    # rope table as the position part builds it
+    from rust_inference_b200.config import RopeSpec
+    from rust_inference_b200.parts import BuildEnv, build_part
+    rope = build_part("position", RopeSpec(head_dim=Dh, theta=theta, rotary_dim=rot),
+                      BuildEnv(tdt, torch.device("cuda")))
+    rope.prepare(max(lens) + 1)
+    kp, vp = dev(k_pool, tdt), dev(v_pool, tdt)
+    args = (dev(table, torch.int32), dev(tok_seq, torch.int32), dev(tok_pos, torch.int32), dev(slots, torch.int32))
+    q = ops.qk_norm_rope_append(dev(qkv, tdt), H, KV, Dh, dev(qg), dev(kg), eps, rope.fused_table(), rot, kp, vp, *args)
+    out = ops.attention(q, kp, vp, *args, 1.0 / math.sqrt(Dh), window)
+    torch.cuda.synchronize()
+    assert int(ops.error_flag("cuda").item()) == 0
+
+    # plain: per sequence, norm + partial rope of the new q/k, then attention over history + new
+    x = qkv.reshape(T, H + 2 * KV, Dh).astype(np.float64)
+    t0 = 0
+    tol = {"float32": 1e-5, "bfloat16": 2e-2}[dtype]
+    for b, (o, n) in enumerate(zip(old, new)):
+        xs = x[t0:t0 + n]
+        cos, sin = plain.rope_cos_sin(np.arange(o, o + n), rot, theta)
+
+        def enc(t, gain):
+            t = plain.rms_norm(t, gain, eps)
+            return np.concatenate([plain.apply_rope(t[..., :rot], cos, sin), t[..., rot:]], axis=-1)
+        qn, kn, vn = enc(xs[:, :H], qg), enc(xs[:, H:H + KV], kg), xs[:, H + KV:]
+        if dtype == "bfloat16":      # what the cache holds is rounded
+            qn, kn = plain.bf16_round(qn.astype(np.float32)).astype(np.float64), plain.bf16_round(kn.astype(np.float32)).astype(np.float64)
+        kall = np.concatenate([k_hist[b].astype(np.float64), kn])
+        vall = np.concatenate([v_hist[b].astype(np.float64), vn])
+        qall = np.concatenate([np.zeros((o, H, Dh)), qn])
+        want = plain.causal_attention(qall, kall, vall, window=window)[o:]
+        close(q[t0:t0 + n], qn, {"float32": 2e-6, "bfloat16": 5e-3}[dtype], f"q of sequence {b}")
+        close(out[t0:t0 + n], want, tol, f"attention of sequence {b}")
+        # appended rows
+        for j in (o, o + n - 1):
+            pg = table[slots[b], j // P]
+            close(kp[pg, :, j % P], kn[j - o], {"float32": 2e-6, "bfloat16": 5e-3}[dtype], f"appended key {j} of sequence {b}")
+            close(vp[pg, :, j % P], vn[j - o], 0, f"appended value {j} of sequence {b}")
+        t0 += n
+
+
+def test_attention_far_key_stands_out():
+    """One key far back among hundreds gets nearly all the weight: a kernel that
+    skipped or misplaced it would return another value row."""
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(3)
+    for dtype in ("float32", "bfloat16"):
+        H, KV, Dh, P, n = 4, 2, 64, 32, 700
+        tdt = DT[dtype]
+        table, slots, total = _paged(rng, [n], KV, Dh, P, dtype)
+        k = rnd(rng, n, KV, Dh, scale=0.1, dtype=dtype)
+        v = rnd(rng, n, KV, Dh, dtype=dtype)
+        q = rnd(rng, 1, H, Dh, scale=0.1, dtype=dtype)
+        far = 37
+        k[far, 1] = q[0, 2] * 400.0           # head 2 reads kv head 1
+        k = plain.bf16_round(k) if dtype == "bfloat16" else k
+        k_pool = np.zeros((total, KV, P, Dh), dtype=np.float32)
+        v_pool = np.zeros_like(k_pool)
+        for j in range(n):
+            pg = table[slots[0], j // P]
+            k_pool[pg, :, j % P], v_pool[pg, :, j % P] = k[j], v[j]
+        out = ops.attention(dev(q, tdt), dev(k_pool, tdt), dev(v_pool, tdt), dev(table, torch.int32),
+                            dev(np.zeros(1), torch.int32), dev(np.array([n - 1]), torch.int32),
+                            dev(slots, torch.int32), 1.0 / math.sqrt(Dh), 0)
+        qall = np.concatenate([np.zeros((n - 1, H, Dh)), q.astype(np.float64)])
+        want = plain.causal_attention(qall, k.astype(np.float64), v.astype(np.float64))[n - 1:]
+        assert np.abs(want[0, 2] - v[far, 1]).max() < 1e-2     # the far key really dominates
+        close(out, want, {"float32": 1e-5, "bfloat16": 2e-2}[dtype], "far key")
+
+
+def test_argmax_first_maximum():
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((5, 151937)).astype(np.float32)
+    x[0, 777] = x[0, 150000] = 9.0            # a tie: the lower index wins
+    x[1, 151936] = 8.0                        # the very last element
+    x[2, 0] = 8.0
+    got = ops.argmax(dev(x)).cpu().numpy()
+    assert got.tolist() == [int(np.argmax(r)) for r in x]
+    assert got[0] == 777 and got[1] == 151936 and got[2] == 0
+
+
+@pytest.mark.parametrize("vocab", [50, 1000, 151936])
+def test_sample_matches_plain(vocab):
+    """The device sampler picks the plain sampler's token for the same uniform number."""
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(vocab)
+    rows = 12
+    logits = (rng.standard_normal((rows, vocab)) * 3).astype(np.float32)
+    logits[3, 10] = logits[3, 20] = logits[3].max() + 1.0      # equal logits at the top
+    cases = [dict(temperature=0.0), dict(temperature=0.8), dict(temperature=1.3, top_k=5),
+             dict(temperature=1.0, top_p=0.6), dict(temperature=0.7, top_k=40, top_p=0.9),
+             dict(temperature=0.9, repetition_penalty=1.5), dict(temperature=0.0, repetition_penalty=3.0),
+             dict(temperature=1.0, top_k=1)]
+    seen = np.zeros((rows, vocab), dtype=np.uint8)
+    hist = [list(rng.integers(0, vocab, size=20)) + [int(np.argmax(logits[r]))] for r in range(rows)]
+    for r in range(rows):
+        seen[r, hist[r]] = 1
+    for c in cases:
+        u = rng.random(rows).astype(np.float32)
+        got = ops.sample(dev(logits), dev(np.full(rows, c.get("temperature", 0.0), dtype=np.float32)), dev(u),
+                         top_k=dev(np.full(rows, c.get("top_k", 0)), torch.int32),
+                         top_p=dev(np.full(rows, c.get("top_p", 1.0), dtype=np.float32)),
+                         penalty=dev(np.full(rows, c.get("repetition_penalty", 1.0), dtype=np.float32)),
+                         seen=dev(seen, torch.uint8)).cpu().numpy()
+
+        # the plain sampler sums 150 000 probabilities one by one in float32, which moves the
+        # boundaries far out in the tail by about 1e-5; the device sums exactly.  So the device
+        # token is held against the same rule evaluated in float64, with u and top_p moved by
+        # what float32 exp can account for
+        for r in range(rows):
+            ok = {_ideal_sample(logits[r], hist[r], float(u[r]) + du, dp=dp, **c)
+                  for du in (0.0, -2e-6, 2e-6) for dp in (0.0, -2e-6, 2e-6)}
+            assert got[r] in ok, f"{c} row {r}: device {got[r]}, float64 rule {sorted(ok)}"
+        if vocab <= 1000:      # short sums: the plain sampler itself agrees
+
+            class Fixed:
+                def __init__(self, v):
+                    self.v = v
+
+                def next_f32(self):
+                    return np.float32(self.v)
+            want = [plain.plain_sample(logits[r], hist[r], Fixed(u[r]), **c) for r in range(rows)]
+            assert sum(int(g != w) for g, w in zip(got, want)) <= 1, f"{c}: device {got}, plain {want}"
+
+
+def _ideal_sample(logits, history, u, dp=0.0, temperature=0.0, top_k=0, top_p=1.0, repetition_penalty=1.0):
+    """The reference's rule (src/sampling.rs:73-128 there) with exact sums."""
+    x = np.array(logits, dtype=np.float32)
+    if repetition_penalty != 1.0:
+        pen = np.float32(repetition_penalty)
+        for t in set(int(t) for t in history):
+            x[t] = x[t] / pen if x[t] > 0 else x[t] * pen
+    if temperature <= 0:
+        return int(np.argmax(x))
+    z = (x / np.float32(temperature)).astype(np.float32)
+    order = np.lexsort((np.arange(len(z)), -z.astype(np.float64)))
+    if 0 < top_k < len(z):
+        order = order[:top_k]
+    p = np.exp(z[order].astype(np.float64) - float(z[order[0]]))
+    p /= p.sum()
+    if top_p < 1.0:
+        cum = np.cumsum(p)
+        keep = int(np.searchsorted(cum, top_p + dp, side="left")) + 1
+        p = p[:keep] / p[:keep].sum()
+    cum = np.cumsum(p)
+    j = int(np.searchsorted(cum, u, side="right"))
+    return int(order[min(j, len(p) - 1)])
+
+
+def test_sample_frequencies_and_top_p():
+    """p = [0.25, 0.75]: the share of token 1 over many draws (src/sampling.rs:166-177 there)."""
+    from rust_inference_b200 import ops
+    from rust_inference_b200.sampling import XorShiftRng
+    n = 4000
+    logits = np.tile(np.array([[0.0, math.log(3.0)]], dtype=np.float32), (n, 1))
+    rng = XorShiftRng(7)
+    u = np.array([rng.next_f32() for _ in range(n)], dtype=np.float32)
+    got = ops.sample(dev(logits), dev(np.ones(n, dtype=np.float32)), dev(u)).cpu().numpy()
+    assert abs(got.mean() - 0.75) < 0.03
+    # top_p 0.5: the first token alone has 0.84 of the mass
+    logits = np.tile(np.array([[3.0, 1.0, 0.5, 0.0]], dtype=np.float32), (50, 1))
+    got = ops.sample(dev(logits), dev(np.ones(50, dtype=np.float32)), dev(u[:50]),
+                     top_p=dev(np.full(50, 0.5, dtype=np.float32))).cpu().numpy()
+    assert (got == 0).all()
