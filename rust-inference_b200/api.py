@@ -25,7 +25,10 @@ class LLM:
 
     def __init__(self, model_dir: Optional[str] = None, dtype: str = "bfloat16", device: str = "cuda:0",
                  max_pages: int = 256, pages_per_seq: int = 128, max_seqs: int = 8, use_graphs: bool = True,
-                 model: Optional[Model] = None):
+                 model: Optional[Model] = None, engine: Optional[Engine] = None):
+        if engine is not None:
+            self.model, self.engine = engine.model, engine
+            return
         if model is None:
             if model_dir is None:
                 raise ValueError("give a model folder or a built model")

@@ -193,6 +193,7 @@ class Engine:
         if rec is not None:
             rec[0].replay()
             self.graph_replays += 1
+            ops.add_launches(rec[2])
             return rec[1]
         if key not in self._warm:
             # the first step of this shape runs eagerly: libraries set themselves up
@@ -200,11 +201,15 @@ class Engine:
             return self.model.forward(tables.part(0), ctx, self.cache, want_dev)
         graph = torch.cuda.CUDAGraph()
         torch.cuda.synchronize(self.device)
+        n0 = ops.launch_count()
         with torch.cuda.graph(graph):
             out = self.model.forward(tables.part(0), ctx, self.cache, want_dev)
-        self._graphs[key] = (graph, out)
+        captured = ops.launch_count() - n0          # recorded, not run: they count at each replay
+        ops.add_launches(-captured)
+        self._graphs[key] = (graph, out, captured)
         graph.replay()
         self.graph_replays += 1
+        ops.add_launches(captured)
         return out
 
     # ---- errors the kernels reported ------------------------------------------------------------

@@ -51,9 +51,22 @@ def _fn(lib_name: str, fn_name: str, defines=None):
     return f
 
 
+_launches = [0]
+
+
+def launch_count() -> int:
+    """Kernels of this package launched so far (graph replays count what they replay)."""
+    return _launches[0]
+
+
+def add_launches(n: int) -> None:
+    _launches[0] += n
+
+
 def _call(lib_name: str, fn_name: str, *args, defines=None):
     f, lib = _fn(lib_name, fn_name, defines)
     rc = f(*args)
+    _launches[0] += 1
     if rc != 0:
         raise KernelError(f"{fn_name}: {lib.ri_last_error().decode(errors='replace')} (code {rc})")
 
