@@ -34,6 +34,14 @@ SOURCES: Dict[str, Tuple[str, ...]] = {
     "attention_plain": ("attention_plain.cu", "common.cuh"),
     "linear_f32": ("linear_f32.cu", "common.cuh"),
     "sampling": ("sampling.cu", "common.cuh"),
+    "attention_decode": ("attention_decode.cu", "common.cuh"),
+}
+
+# sources that are compiled once per value of a macro (the model's head size);
+# the build check compiles these values, a model with another one compiles its own
+HEAD_DIMS = (16, 32, 48, 64, 80, 96, 128, 256)
+VARIANTS: Dict[str, Tuple[Dict[str, object], ...]] = {
+    "attention_decode": tuple({"RI_HEAD_DIM": d} for d in HEAD_DIMS),
 }
 
 
@@ -178,7 +186,13 @@ def prepare(requests: Iterable[Tuple[str, Optional[Dict[str, object]]]]) -> None
         except Exception as e:  # noqa: BLE001 - reported below
             errors.append(e)
 
-    threads = [threading.Thread(target=work, args=(item,)) for item in todo]
+    gate = threading.Semaphore(max(2, (os.cpu_count() or 4) // 2))
+
+    def gated(item):
+        with gate:
+            work(item)
+
+    threads = [threading.Thread(target=gated, args=(item,)) for item in todo]
     for t in threads:
         t.start()
     for t in threads:
@@ -189,4 +203,10 @@ def prepare(requests: Iterable[Tuple[str, Optional[Dict[str, object]]]]) -> None
 
 def build_all(extra: Iterable[Tuple[str, Optional[Dict[str, object]]]] = ()) -> None:
     """Compile every library (used by the repository's build check)."""
-    prepare([(n, None) for n in SOURCES if not n.endswith("_tmpl")] + list(extra))
+    reqs = []
+    for n in SOURCES:
+        if n in VARIANTS:
+            reqs.extend((n, d) for d in VARIANTS[n])
+        else:
+            reqs.append((n, None))
+    prepare(reqs + list(extra))

@@ -185,7 +185,7 @@ class Engine:
         return _Tables(T, B, W, self.device)
 
     def _graph_key(self, ctx) -> tuple:
-        return (ctx.num_seqs,)
+        return (ctx.num_seqs, ctx.len_bucket)
 
     def _decode_step(self, tables, ctx, want_dev):
         key = self._graph_key(ctx)

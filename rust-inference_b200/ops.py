@@ -31,7 +31,10 @@ _SIGNATURES = {
     ("sampling", "ri_sample"): [_P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P],
     ("sampling", "ri_argmax"): [_P, _L, _I, _I, _P, _P],
     ("sampling", "ri_mark_seen"): [_P, _L, _P, _P, _I, _I, _P],
+    ("attention_decode", "ri_attention_decode"): [_P] * 9 + [_I] * 8 + [_F, _I, _P, _P],
 }
+DECODE_CHUNK = 128          # keys per partial result of the decode attention kernel
+MAX_FAST_HEAD_DIM = 256
 _fn_cache = {}
 
 
@@ -248,6 +251,40 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
           page_table.data_ptr(), tok_seq.data_ptr(), tok_pos.data_ptr(), seq_slot.data_ptr(), tokens, H, KV, Dh,
           page_table.shape[1], page_size, pages, float(scale), int(window), _code(q.dtype),
           error_flag(q.device).data_ptr(), _stream())
+    return out
+
+
+def fast_attention_supported(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
+    """Whether the tensor-core attention kernels take this case (else the plain kernel does)."""
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= MAX_FAST_HEAD_DIM and page_size == 32
+
+
+def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
+                     seq_slot: torch.Tensor, seq_len: torch.Tensor, scale: float, window: int,
+                     max_len: int) -> torch.Tensor:
+    """Attention of one new token per sequence (q [seqs, H, Dh], bfloat16) over the
+    paged cache, keys split into chunks of ``DECODE_CHUNK``; ``max_len`` bounds the
+    sequences' lengths after this step and sizes the scratch memory."""
+    _need(q, "q", torch.bfloat16)
+    seqs, H, Dh = q.shape
+    pages, KV, page_size, dh = k_pool.shape
+    if dh != Dh or v_pool.shape != k_pool.shape:
+        raise KernelError(f"attention_decode: pools {tuple(k_pool.shape)} do not fit head_dim {Dh}")
+    if not fast_attention_supported(q.dtype, Dh, page_size):
+        raise KernelError(f"attention_decode: head_dim {Dh} with pages of {page_size} is not supported")
+    _need(k_pool, "k_pool", torch.bfloat16)
+    _need(v_pool, "v_pool", torch.bfloat16)
+    _need(page_table, "page_table", torch.int32)
+    _need(seq_slot, "seq_slot", torch.int32, (seqs,))
+    _need(seq_len, "seq_len", torch.int32, (seqs,))
+    chunks = max(1, -(-int(max_len) // DECODE_CHUNK))
+    o_part = torch.empty((seqs, H, chunks, Dh), dtype=torch.float32, device=q.device)
+    ml_part = torch.empty((seqs, H, chunks, 2), dtype=torch.float32, device=q.device)
+    out = torch.empty_like(q)
+    _call("attention_decode", "ri_attention_decode", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+          out.data_ptr(), o_part.data_ptr(), ml_part.data_ptr(), page_table.data_ptr(), seq_slot.data_ptr(),
+          seq_len.data_ptr(), seqs, H, KV, Dh, page_table.shape[1], page_size, pages, chunks, float(scale),
+          int(window), error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
     return out
 
 

@@ -65,6 +65,13 @@ class StepContext:
     def decode_only(self) -> bool:
         return self.max_new == 1
 
+    @property
+    def len_bucket(self) -> int:
+        """``max_len`` rounded up to a multiple of 1024: what kernels size their grids
+        and scratch memory by, so that a captured step stays valid while the
+        sequences grow inside the bucket."""
+        return -(-max(1, self.max_len) // 1024) * 1024
+
 
 @dataclass(frozen=True)
 class CacheRequest:

@@ -312,3 +312,62 @@ def test_sample_frequencies_and_top_p():
     got = ops.sample(dev(logits), dev(np.ones(50, dtype=np.float32)), dev(u[:50]),
                      top_p=dev(np.full(50, 0.5, dtype=np.float32))).cpu().numpy()
     assert (got == 0).all()
+
+
+def _fill_pools(rng, lens, KV, Dh, dtype, scale=1.0):
+    P = 32
+    table, slots, total = _paged(rng, lens, KV, Dh, P, dtype)
+    k = [rnd(rng, n, KV, Dh, scale=scale, dtype=dtype) for n in lens]
+    v = [rnd(rng, n, KV, Dh, dtype=dtype) for n in lens]
+    k_pool = (rng.standard_normal((total, KV, P, Dh)) * 50).astype(np.float32)     # junk where nothing is stored:
+    v_pool = (rng.standard_normal((total, KV, P, Dh)) * 50).astype(np.float32)     # a kernel that reads it is caught
+    for b, n in enumerate(lens):
+        for j in range(n):
+            pg = table[slots[b], j // P]
+            k_pool[pg, :, j % P], v_pool[pg, :, j % P] = k[b][j], v[b][j]
+    return table, slots, k, v, k_pool, v_pool
+
+
+@pytest.mark.parametrize("H,KV,Dh,window", [(4, 2, 16, 0), (6, 1, 32, 0), (3, 3, 48, 0), (32, 8, 128, 0), (5, 5, 80, 37),
+                                            (4, 1, 256, 0), (2, 1, 64, 200), (20, 1, 64, 0), (34, 2, 32, 129)])
+def test_attention_decode_kernel(H, KV, Dh, window):
+    """Split-KV decode attention: lengths around page and chunk edges, groups of 1 to 20
+    heads (more than the 16 rows of one pass), windows, a shuffled page table."""
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(H * 131 + Dh)
+    lens = [1, 31, 32, 33, 127, 128, 129, 300, 700, 1025]
+    table, slots, k, v, k_pool, v_pool = _fill_pools(rng, lens, KV, Dh, "bfloat16", scale=0.5)
+    q = rnd(rng, len(lens), H, Dh, dtype="bfloat16")
+    bt = torch.bfloat16
+    out = ops.attention_decode(dev(q, bt), dev(k_pool, bt), dev(v_pool, bt), dev(table, torch.int32),
+                               dev(slots, torch.int32), dev(np.array(lens), torch.int32), 1.0 / math.sqrt(Dh), window,
+                               max(lens))
+    torch.cuda.synchronize()
+    assert int(ops.error_flag("cuda").item()) == 0
+    for b, n in enumerate(lens):
+        qall = np.concatenate([np.zeros((n - 1, H, Dh)), q[b:b + 1].astype(np.float64)])
+        want = plain.causal_attention(qall, k[b].astype(np.float64), v[b].astype(np.float64), window=window)[n - 1:]
+        close(out[b:b + 1], want, 2e-2, f"decode attention, length {n}")
+    # the same sequence alone gives the same bits: nothing depends on the batch
+    one = ops.attention_decode(dev(q[8:9], bt), dev(k_pool, bt), dev(v_pool, bt), dev(table, torch.int32),
+                               dev(slots[8:9], torch.int32), dev(np.array(lens[8:9]), torch.int32),
+                               1.0 / math.sqrt(Dh), window, 2048)
+    assert torch.equal(one[0], out[8])
+
+
+def test_attention_decode_far_key():
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(9)
+    H, KV, Dh, n = 8, 2, 128, 3000
+    table, slots, k, v, k_pool, v_pool = _fill_pools(rng, [n], KV, Dh, "bfloat16", scale=0.1)
+    q = rnd(rng, 1, H, Dh, scale=0.1, dtype="bfloat16")
+    bt = torch.bfloat16
+    for far in (0, 31, 32, 1500, 2999):
+        kk = k[0].copy()
+        kk[far, 1] = plain.bf16_round(q[0, 5] * 300.0)          # head 5 reads kv head 1
+        kp = k_pool.copy()
+        kp[table[slots[0], far // 32], 1, far % 32] = kk[far, 1]
+        out = ops.attention_decode(dev(q, bt), dev(kp, bt), dev(v_pool, bt), dev(table, torch.int32),
+                                   dev(slots, torch.int32), dev(np.array([n]), torch.int32), 1.0 / math.sqrt(Dh), 0, n)
+        got = out[0, 5].float().cpu().numpy()
+        assert np.abs(got - v[0][far, 1]).max() < 2e-2, f"key {far} should take all the weight"
