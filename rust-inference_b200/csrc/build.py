@@ -34,7 +34,8 @@ SOURCES: Dict[str, Tuple[str, ...]] = {
     "attention_plain": ("attention_plain.cu", "common.cuh"),
     "linear_f32": ("linear_f32.cu", "common.cuh"),
     "sampling": ("sampling.cu", "common.cuh"),
-    "attention_decode": ("attention_decode.cu", "common.cuh"),
+    "attention_decode": ("attention_decode.cu", "common.cuh", "mma_helpers.cuh"),
+    "attention_prefill": ("attention_prefill.cu", "common.cuh", "mma_helpers.cuh"),
 }
 
 # sources that are compiled once per value of a macro (the model's head size);
@@ -42,6 +43,7 @@ SOURCES: Dict[str, Tuple[str, ...]] = {
 HEAD_DIMS = (16, 32, 48, 64, 80, 96, 128, 256)
 VARIANTS: Dict[str, Tuple[Dict[str, object], ...]] = {
     "attention_decode": tuple({"RI_HEAD_DIM": d} for d in HEAD_DIMS),
+    "attention_prefill": tuple({"RI_HEAD_DIM": d} for d in HEAD_DIMS),
 }
 
 

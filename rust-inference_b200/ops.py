@@ -32,6 +32,7 @@ _SIGNATURES = {
     ("sampling", "ri_argmax"): [_P, _L, _I, _I, _P, _P],
     ("sampling", "ri_mark_seen"): [_P, _L, _P, _P, _I, _I, _P],
     ("attention_decode", "ri_attention_decode"): [_P] * 9 + [_I] * 8 + [_F, _I, _P, _P],
+    ("attention_prefill", "ri_attention_prefill"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _P],
 }
 DECODE_CHUNK = 128          # keys per partial result of the decode attention kernel
 MAX_FAST_HEAD_DIM = 256
@@ -285,6 +286,34 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
           out.data_ptr(), o_part.data_ptr(), ml_part.data_ptr(), page_table.data_ptr(), seq_slot.data_ptr(),
           seq_len.data_ptr(), seqs, H, KV, Dh, page_table.shape[1], page_size, pages, chunks, float(scale),
           int(window), error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
+    return out
+
+
+def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
+                      seq_slot: torch.Tensor, seq_start: torch.Tensor, seq_len: torch.Tensor, max_new: int,
+                      scale: float, window: int) -> torch.Tensor:
+    """Attention of the step's new tokens (q [tokens, H, Dh], bfloat16, sequences back
+    to back as ``seq_start`` says) over the paged cache, which already holds their keys
+    and values; ``max_new`` is the most tokens one sequence brings."""
+    _need(q, "q", torch.bfloat16)
+    tokens, H, Dh = q.shape
+    pages, KV, page_size, dh = k_pool.shape
+    if dh != Dh or v_pool.shape != k_pool.shape:
+        raise KernelError(f"attention_prefill: pools {tuple(k_pool.shape)} do not fit head_dim {Dh}")
+    if not fast_attention_supported(q.dtype, Dh, page_size):
+        raise KernelError(f"attention_prefill: head_dim {Dh} with pages of {page_size} is not supported")
+    _need(k_pool, "k_pool", torch.bfloat16)
+    _need(v_pool, "v_pool", torch.bfloat16)
+    _need(page_table, "page_table", torch.int32)
+    seqs = seq_slot.numel()
+    _need(seq_slot, "seq_slot", torch.int32, (seqs,))
+    _need(seq_start, "seq_start", torch.int32, (seqs + 1,))
+    _need(seq_len, "seq_len", torch.int32, (seqs,))
+    out = torch.empty_like(q)
+    _call("attention_prefill", "ri_attention_prefill", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+          out.data_ptr(), page_table.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seq_len.data_ptr(),
+          seqs, int(max_new), H, KV, Dh, page_table.shape[1], page_size, pages, float(scale), int(window),
+          error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
     return out
 
 

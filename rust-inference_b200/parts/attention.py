@@ -65,9 +65,13 @@ class Attention(Mixer):
         q = ops.qk_norm_rope_append(qkv, s.num_heads, s.num_kv_heads, s.head_dim, self.q_gain, self.k_gain, eps,
                                     table, rot, cache.k_pool, cache.v_pool, cache.page_table,
                                     ctx.tok_seq, ctx.tok_pos, ctx.seq_slot, write_kv=cache.writes)
-        if ctx.decode_only and ops.fast_attention_supported(q.dtype, s.head_dim, cache.page_size):
+        fast = ops.fast_attention_supported(q.dtype, s.head_dim, cache.page_size)
+        if fast and ctx.decode_only:
             out = ops.attention_decode(q, cache.k_pool, cache.v_pool, cache.page_table, ctx.seq_slot, ctx.seq_len,
                                        self.scale, s.window, ctx.len_bucket)
+        elif fast:
+            out = ops.attention_prefill(q, cache.k_pool, cache.v_pool, cache.page_table, ctx.seq_slot,
+                                        ctx.seq_start, ctx.seq_len, ctx.max_new, self.scale, s.window)
         else:
             out = ops.attention(q, cache.k_pool, cache.v_pool, cache.page_table, ctx.tok_seq, ctx.tok_pos,
                                 ctx.seq_slot, self.scale, s.window)

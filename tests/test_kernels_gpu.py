@@ -371,3 +371,35 @@ def test_attention_decode_far_key():
                                    dev(slots, torch.int32), dev(np.array([n]), torch.int32), 1.0 / math.sqrt(Dh), 0, n)
         got = out[0, 5].float().cpu().numpy()
         assert np.abs(got - v[0][far, 1]).max() < 2e-2, f"key {far} should take all the weight"
+
+
+@pytest.mark.parametrize("H,KV,Dh,window", [(4, 2, 16, 0), (6, 1, 32, 0), (3, 3, 48, 0), (8, 2, 128, 0), (5, 5, 80, 37),
+                                            (4, 1, 256, 0), (2, 1, 64, 100), (4, 4, 96, 64)])
+def test_attention_prefill_kernel(H, KV, Dh, window):
+    """New tokens of several sequences against what their caches already hold: tiles that
+    start in the middle of a page, sequences shorter than a tile, several tiles, windows."""
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(H * 77 + Dh)
+    old = [0, 31, 64, 70, 0, 500, 0]
+    new = [40, 1, 3, 27, 200, 130, 64]
+    lens = [a + b for a, b in zip(old, new)]
+    table, slots, k, v, k_pool, v_pool = _fill_pools(rng, lens, KV, Dh, "bfloat16", scale=0.5)
+    T = sum(new)
+    q = rnd(rng, T, H, Dh, dtype="bfloat16")
+    starts = np.concatenate([[0], np.cumsum(new)]).astype(np.int32)
+    bt = torch.bfloat16
+    out = ops.attention_prefill(dev(q, bt), dev(k_pool, bt), dev(v_pool, bt), dev(table, torch.int32),
+                                dev(slots, torch.int32), dev(starts, torch.int32), dev(np.array(lens), torch.int32),
+                                max(new), 1.0 / math.sqrt(Dh), window)
+    torch.cuda.synchronize()
+    assert int(ops.error_flag("cuda").item()) == 0
+    for b, (o, n) in enumerate(zip(old, new)):
+        qall = np.concatenate([np.zeros((o, H, Dh)), q[starts[b]:starts[b + 1]].astype(np.float64)])
+        want = plain.causal_attention(qall, k[b].astype(np.float64), v[b].astype(np.float64), window=window)[o:]
+        close(out[starts[b]:starts[b + 1]], want, 2e-2, f"prefill attention, sequence {b}")
+    # sequence 4 alone: the same bits
+    one = ops.attention_prefill(dev(q[starts[4]:starts[5]], bt), dev(k_pool, bt), dev(v_pool, bt),
+                                dev(table, torch.int32), dev(slots[4:5], torch.int32),
+                                dev(np.array([0, new[4]]), torch.int32), dev(np.array(lens[4:5]), torch.int32), new[4],
+                                1.0 / math.sqrt(Dh), window)
+    assert torch.equal(one, out[starts[4]:starts[5]])
