@@ -36,6 +36,8 @@ SOURCES: Dict[str, Tuple[str, ...]] = {
     "sampling": ("sampling.cu", "common.cuh"),
     "attention_decode": ("attention_decode.cu", "common.cuh", "mma_helpers.cuh"),
     "attention_prefill": ("attention_prefill.cu", "common.cuh", "mma_helpers.cuh"),
+    "attention_decode_noalloc": ("attention_decode_noalloc.cu", "attention_decode_noalloc.h", "attention_decode.cu",
+                                 "common.cuh", "mma_helpers.cuh"),
 }
 
 # sources that are compiled once per value of a macro (the model's head size);
@@ -44,6 +46,7 @@ HEAD_DIMS = (16, 32, 48, 64, 80, 96, 128, 256)
 VARIANTS: Dict[str, Tuple[Dict[str, object], ...]] = {
     "attention_decode": tuple({"RI_HEAD_DIM": d} for d in HEAD_DIMS),
     "attention_prefill": tuple({"RI_HEAD_DIM": d} for d in HEAD_DIMS),
+    "attention_decode_noalloc": ({"RI_HEAD_DIM": 64}, {"RI_HEAD_DIM": 128}),
 }
 
 
