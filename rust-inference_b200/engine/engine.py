@@ -92,7 +92,7 @@ class Engine:
         self.cache = Cache(model.cache_requests(), max(1, max_seqs), num_pages, max(1, -(-limit // page_size)),
                            self.dtype, self.device, page_size)
         model.prepare(self.cache.max_seq_len)
-        self.use_graphs = use_graphs and self.device.type == "cuda"
+        self.use_graphs = use_graphs and self.device.type == "cuda" and model.graph_safe
         self._decode_tables = {}
         self._graphs = {}
         self._warm = set()

@@ -122,6 +122,13 @@ class Model:
     def cache_requests(self):
         return [self.blocks[layer].mixer.cache_request() for layer in self.cache_entry_layers]
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether one-token steps of this model may be replayed from a CUDA graph."""
+        parts = [p for b in self.blocks for _, p, _, _ in b.parts()] + [self.final_norm]
+        parts += [b.mixer.position for b in self.blocks if hasattr(b.mixer, "position")]
+        return all(getattr(p, "graph_safe", False) for p in parts)
+
     def prepare(self, max_positions: int) -> None:
         for b in self.blocks:
             b.mixer.prepare(max_positions)

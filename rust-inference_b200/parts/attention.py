@@ -21,6 +21,7 @@ from .registry import ParamInfo, build_part, register_mixer
 
 @register_mixer("attention")
 class Attention(Mixer):
+    graph_safe = True
     def __init__(self, spec, env):
         super().__init__(spec, env)
         if spec.num_heads % spec.num_kv_heads:

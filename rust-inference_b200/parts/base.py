@@ -89,8 +89,16 @@ class CacheRequest:
 
 
 class Part:
-    """Common base: parameters by local name."""
+    """Common base: parameters by local name.
+
+    ``graph_safe``: one-token steps are captured into CUDA graphs and replayed.  A
+    captured step repeats the same launches with the same host-side values, so a
+    part may only be replayed if everything that changes from step to step reaches
+    its kernels through device tensors (the context's int32 tables, the cache).  A
+    part that reads ``ctx.host_*`` values, branches on them or indexes with them
+    must leave this False; a model with such a part runs every step eagerly."""
     kind = "?"
+    graph_safe = False
 
     def __init__(self, spec, env: BuildEnv):
         self.spec = spec

@@ -12,6 +12,7 @@ from .registry import ParamInfo, register_ffn
 
 @register_ffn("swiglu")
 class SwiGLU(FeedForward):
+    graph_safe = True
     @classmethod
     def param_infos(cls, spec):
         D, I = spec.hidden_size, spec.intermediate_size

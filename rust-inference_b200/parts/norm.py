@@ -11,6 +11,7 @@ from .registry import ParamInfo, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
+    graph_safe = True
     @classmethod
     def param_infos(cls, spec):
         return {"weight": ParamInfo((spec.size,), "gain")}

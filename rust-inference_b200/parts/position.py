@@ -20,6 +20,7 @@ from .registry import register_position
 
 @register_position("rope")
 class Rope(PositionEncoding):
+    graph_safe = True
     def __init__(self, spec, env):
         super().__init__(spec, env)
         if spec.rot % 2 or spec.rot > spec.head_dim or spec.rot <= 0:
@@ -47,4 +48,4 @@ class Rope(PositionEncoding):
 
 @register_position("none")
 class NoPosition(PositionEncoding):
-    pass
+    graph_safe = True

@@ -1,0 +1,245 @@
+"""Each kind of part alone against its plain formula, and a toy architecture whose
+mixer keeps state of its own, defined in this file and registered without touching the
+package: one layer with the toy mixer, one with attention, the first layer scheduled
+twice (once more at the end, reading its own state on)."""
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+import plain_qwen3 as plain
+from rust_inference_b200.config import (AttentionSpec, LayerSpec, ModelSpec, RMSNormSpec, RopeSpec, ScheduleEntry,
+                                        SwiGLUSpec, register_architecture)
+from rust_inference_b200.parts import BuildEnv, CacheRequest, Mixer, ParamInfo, build_part, register_mixer
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def dev(a, dtype=torch.float32):
+    return torch.as_tensor(np.ascontiguousarray(a)).to("cuda", dtype=dtype).contiguous()
+
+
+def env(dtype):
+    return BuildEnv(DT[dtype], torch.device("cuda"))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_norm_part(dtype):
+    rng = np.random.default_rng(0)
+    part = build_part("norm", RMSNormSpec(size=88, eps=2e-5), env(dtype))
+    gain = (1 + 0.1 * rng.standard_normal(88)).astype(np.float32)
+    part.load({"weight": dev(gain)})
+    x = rng.standard_normal((5, 88)).astype(np.float32)
+    got = part(dev(x)).float().cpu().numpy()
+    want = plain.rms_norm(x, gain, 2e-5)
+    assert np.abs(got - want).max() <= (2e-6 if dtype == "float32" else 8e-3) * np.abs(want).max()
+
+
+def test_rope_part_table():
+    part = build_part("position", RopeSpec(head_dim=64, theta=1e6, rotary_dim=48, scaling=1.0), env("float32"))
+    part.prepare(300)
+    table = part.fused_table().cpu().numpy()
+    cos, sin = plain.rope_cos_sin(np.arange(300), 48, 1e6)
+    assert table.shape == (300, 24, 2)
+    assert np.abs(table[..., 0] - cos).max() < 1e-7 and np.abs(table[..., 1] - sin).max() < 1e-7
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_swiglu_part(dtype):
+    rng = np.random.default_rng(1)
+    part = build_part("ffn", SwiGLUSpec(hidden_size=72, intermediate_size=104), env(dtype))
+    W = {n: (rng.standard_normal(s) * 0.1).astype(np.float32) for n, s in
+         (("gate_proj.weight", (104, 72)), ("up_proj.weight", (104, 72)), ("down_proj.weight", (72, 104)))}
+    if dtype == "bfloat16":
+        W = {n: plain.bf16_round(w) for n, w in W.items()}
+    part.load({n: dev(w, DT[dtype]) for n, w in W.items()})
+    x = rng.standard_normal((9, 72)).astype(np.float32)
+    x = plain.bf16_round(x) if dtype == "bfloat16" else x
+    got = part(dev(x, DT[dtype]), None).float().cpu().numpy()
+    want = plain.swiglu_mlp(x, {"m." + n: w for n, w in W.items()}, "m.")
+    assert np.abs(got - want).max() <= (1e-5 if dtype == "float32" else 3e-2) * np.abs(want).max()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [0, 20])
+def test_attention_part_over_two_steps(dtype, window):
+    """The attention part with a cache of its own: a prompt step, then single tokens, against
+    the plain attention block on the whole sequence; with a window, pages behind it are freed."""
+    from rust_inference_b200.cache import Cache
+    from rust_inference_b200.parts.base import StepContext
+    rng = np.random.default_rng(2)
+    D, Hh, KV, Dh = 40, 4, 2, 16
+    spec = AttentionSpec(hidden_size=D, num_heads=Hh, num_kv_heads=KV, head_dim=Dh,
+                         position=RopeSpec(head_dim=Dh, theta=10000.0), qk_norm=RMSNormSpec(size=Dh, eps=1e-6), window=window)
+    part = build_part("mixer", spec, env(dtype))
+    W = {"q_proj.weight": (Hh * Dh, D), "k_proj.weight": (KV * Dh, D), "v_proj.weight": (KV * Dh, D), "o_proj.weight": (D, Hh * Dh)}
+    W = {n: (rng.standard_normal(s) * 0.2).astype(np.float32) for n, s in W.items()}
+    if dtype == "bfloat16":
+        W = {n: plain.bf16_round(w) for n, w in W.items()}
+    G = {"q_norm.weight": (1 + 0.1 * rng.standard_normal(Dh)).astype(np.float32),
+         "k_norm.weight": (1 + 0.1 * rng.standard_normal(Dh)).astype(np.float32)}
+    part.load({**{n: dev(w, DT[dtype]) for n, w in W.items()}, **{n: dev(g) for n, g in G.items()}})
+    part.prepare(256)
+    cache = Cache([part.cache_request()], num_slots=3, num_pages=8, max_pages_per_seq=8, dtype=DT[dtype], device="cuda")
+    cache.alloc_slot()
+    slot = cache.alloc_slot()
+    n, first = 90, 50
+    x = rng.standard_normal((n, D)).astype(np.float32)
+    x = plain.bf16_round(x) if dtype == "bfloat16" else x
+    outs = []
+    for lo, hi in [(0, first)] + [(i, i + 1) for i in range(first, n)]:
+        before = cache.extend([(slot, hi - lo)])[0]
+        cache.upload()
+        i32 = lambda a: dev(np.asarray(a), torch.int32)
+        ctx = StepContext(tok_seq=i32(np.zeros(hi - lo)), tok_pos=i32(np.arange(lo, hi)), seq_slot=i32([slot]),
+                          seq_start=i32([0, hi - lo]), seq_len=i32([hi]), num_tokens=hi - lo, num_seqs=1,
+                          max_new=hi - lo, max_len=hi)
+        assert before == lo
+        outs.append(part(dev(x[lo:hi], DT[dtype]), ctx, cache.layer(0)).float().cpu().numpy())
+        cache.after_step([slot])
+    got = np.concatenate(outs)
+    # plain: the block of plain_qwen3 with this window
+    cfg = {"num_attention_heads": Hh, "num_key_value_heads": KV, "head_dim": Dh, "hidden_size": D,
+           "rms_norm_eps": 1e-6, "rope_theta": 10000.0}
+    Wp = {"a." + k: v for k, v in {**W, **G}.items()}
+    q = plain.rms_norm(plain.linear(x, W["q_proj.weight"]).reshape(n, Hh, Dh), G["q_norm.weight"], 1e-6)
+    k = plain.rms_norm(plain.linear(x, W["k_proj.weight"]).reshape(n, KV, Dh), G["k_norm.weight"], 1e-6)
+    v = plain.linear(x, W["v_proj.weight"]).reshape(n, KV, Dh)
+    cos, sin = plain.rope_cos_sin(np.arange(n), Dh, 10000.0)
+    o = plain.causal_attention(plain.apply_rope(q, cos, sin), plain.apply_rope(k, cos, sin), v, window=window)
+    want = plain.linear(o.reshape(n, Hh * Dh), W["o_proj.weight"])
+    if window == 0:
+        assert np.allclose(want, plain.attention_block(x, Wp, "a.", cfg, np.arange(n)))
+    assert np.abs(got - want).max() <= (2e-5 if dtype == "float32" else 4e-2) * np.abs(want).max()
+    if window:
+        assert (cache.groups[0].pages.table[slot] >= 0).sum() <= 2        # pages behind the window went back
+    cache.check()
+
+
+# ---- a toy architecture with a stateful mixer, all of it defined here --------------------------------------
+
+@dataclass(frozen=True)
+class DecaySpec:
+    hidden_size: int
+    state_size: int
+    decay: float
+    kind: str = "toy_decay"
+
+
+@register_mixer("toy_decay")
+class DecayMixer(Mixer):
+    """s <- decay * s + x W_in ;  y = s W_out, token after token, s kept per sequence."""
+
+    @classmethod
+    def param_infos(cls, spec):
+        return {"in_proj.weight": ParamInfo((spec.state_size, spec.hidden_size)),
+                "out_proj.weight": ParamInfo((spec.hidden_size, spec.state_size))}
+
+    def load(self, tensors):
+        self.w_in, self.w_out = tensors["in_proj.weight"].float(), tensors["out_proj.weight"].float()
+
+    def cache_request(self):
+        return CacheRequest(state_shape=(self.spec.state_size,), state_dtype=torch.float32)
+
+    def __call__(self, x, ctx, cache):
+        u = x.float() @ self.w_in.t()
+        y = torch.empty_like(u)
+        t0 = 0
+        for slot, n in zip(ctx.host_seq_slot, ctx.host_new):
+            s = cache.state[slot]
+            for t in range(t0, t0 + n):
+                s = self.spec.decay * s + u[t]
+                y[t] = s
+            cache.state[slot] = s
+            t0 += n
+        return (y @ self.w_out.t()).to(x.dtype)
+
+
+@register_architecture("ToyStateLM")
+@dataclass(frozen=True)
+class ToyConfig:
+    vocab_size: int = 97
+    hidden_size: int = 48
+    state_size: int = 24
+    decay: float = 0.9
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(**{k: d[k] for k in ("vocab_size", "hidden_size", "state_size", "decay") if k in d})
+
+    def validate(self):
+        pass
+
+    def to_dict(self):
+        return {"architectures": ["ToyStateLM"], "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
+                "state_size": self.state_size, "decay": self.decay}
+
+    def to_spec(self):
+        D = self.hidden_size
+        norm = RMSNormSpec(size=D, eps=1e-5)
+        ffn = SwiGLUSpec(hidden_size=D, intermediate_size=2 * D)
+        attn = AttentionSpec(hidden_size=D, num_heads=3, num_kv_heads=1, head_dim=16,
+                             position=RopeSpec(head_dim=16, theta=1e4), qk_norm=None)
+
+        def layer(i, mixer):
+            return LayerSpec(mixer=mixer, ffn=ffn, mixer_norm=norm, ffn_norm=norm, names=(
+                ("mixer", f"layers.{i}.mixer."), ("ffn", f"layers.{i}.ffn."), ("mixer_norm", f"layers.{i}.norm1."),
+                ("ffn_norm", f"layers.{i}.norm2.")))
+        layers = (layer(0, DecaySpec(D, self.state_size, self.decay)), layer(1, attn))
+        # layer 0 runs twice; its second run has a state of its own (cache entry 2)
+        schedule = (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 2))
+        return ModelSpec(architecture="ToyStateLM", vocab_size=self.vocab_size, hidden_size=D, layers=layers,
+                         schedule=schedule, final_norm=norm, tie_embeddings=True, max_positions=512,
+                         embedding_name="embed.weight", head_name="head.weight", final_norm_prefix="norm.")
+
+
+def toy_plain(cfg, W, ids):
+    D = cfg.hidden_size
+    h = W["embed.weight"][np.asarray(ids)]
+    n = len(ids)
+
+    def ffn(x, p):
+        return plain.swiglu_mlp(x, W, p)
+
+    def decay(x):
+        u = x @ W["layers.0.mixer.in_proj.weight"].T
+        s, out = np.zeros(cfg.state_size), []
+        for t in range(n):
+            s = cfg.decay * s + u[t]
+            out.append(s)
+        return np.array(out) @ W["layers.0.mixer.out_proj.weight"].T
+
+    def attn(x):
+        q = plain.linear(x, W["layers.1.mixer.q_proj.weight"]).reshape(n, 3, 16)
+        k = plain.linear(x, W["layers.1.mixer.k_proj.weight"]).reshape(n, 1, 16)
+        v = plain.linear(x, W["layers.1.mixer.v_proj.weight"]).reshape(n, 1, 16)
+        cos, sin = plain.rope_cos_sin(np.arange(n), 16, 1e4)
+        o = plain.causal_attention(plain.apply_rope(q, cos, sin), plain.apply_rope(k, cos, sin), v)
+        return plain.linear(o.reshape(n, 48), W["layers.1.mixer.o_proj.weight"])
+    for i, mix in ((0, decay), (1, attn), (0, decay)):
+        p = f"layers.{i}."
+        h = h + mix(plain.rms_norm(h, W[p + "norm1.weight"], 1e-5))
+        h = h + ffn(plain.rms_norm(h, W[p + "norm2.weight"], 1e-5), p + "ffn.")
+    return plain.rms_norm(h, W["norm.weight"], 1e-5) @ W["embed.weight"].T
+
+
+def test_toy_architecture_registers_builds_and_steps(tmp_path):
+    cfg = ToyConfig()
+    d = H.make_model_dir(tmp_path, cfg.to_dict(), seed=3, stored="float32", name="toy")
+    W = plain.read_safetensors(d + "/model.safetensors")
+    rng = np.random.default_rng(0)
+    reqs = H.random_requests(rng, cfg.vocab_size, [7, 40, 3, 66, 21])
+    want = {rid: toy_plain(cfg, W, toks) for rid, toks in reqs.items()}
+    import os
+    env = dict(os.environ, PYTHONPATH=os.path.dirname(os.path.abspath(__file__)))
+    for label, steps in (("whole", H.trace_whole(reqs)), ("tail", H.trace_tail(reqs, tail=32)),
+                         ("batches", H.trace_batches(reqs, 2, [5, 0, 9]))):
+        out = str(tmp_path / f"toy_{label}")
+        # in this process: the toy parts are registered here, not in a fresh interpreter
+        H.replay_inprocess(d, "float32", steps, out, device="cuda")
+        rows = H.collect(steps, out, cfg.vocab_size)
+        H.assert_rows_close(rows, want, "float32", f"toy {label}")

@@ -25,7 +25,7 @@ TINY_C = {
     "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
     "num_hidden_layers": 2, "hidden_size": 120, "num_attention_heads": 6, "num_key_value_heads": 3,
     "head_dim": 48, "intermediate_size": 200, "vocab_size": 1000, "rope_theta": 50000.0,
-    "rms_norm_eps": 3e-6, "tie_word_embeddings": False, "max_position_embeddings": 1024,
+    "rms_norm_eps": 3e-6, "tie_word_embeddings": False, "max_position_embeddings": 2048,
 }
 TINY_C_STORED = "bfloat16"
 
