@@ -35,6 +35,8 @@ static_assert(RI_HEAD_DIM % 16 == 0 && RI_HEAD_DIM >= 16 && RI_HEAD_DIM <= 256, 
 #define AD_CHUNK (AD_PAGE * AD_WARPS)
 #define AD_PITCH (AD_DH + 8)                 // bf16 elements per shared row: 16 bytes of padding, no bank conflicts
 #define AD_ROWS 16                           // query heads per pass (rows of the MMA)
+#define AD_MERGE_THREADS 128
+#define AD_MERGE_TILE 128                    // chunks whose weights are staged at a time
 
 struct __align__(16) DecodeSmem {
     bf16 k[AD_CHUNK][AD_PITCH];
@@ -230,17 +232,46 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ o_part, 
     const int c_lo = first_key / AD_CHUNK, c_hi = (len + AD_CHUNK - 1) / AD_CHUNK;     // [c_lo, c_hi)
     const float* ml = ml_part + ((size_t)b * H + h) * max_chunks * 2;
     const float* op = o_part + ((size_t)b * H + h) * max_chunks * AD_DH;
+    __shared__ float s_w[AD_MERGE_TILE], s_lw[AD_MERGE_TILE], s_red[32];
+    // the maximum over the visible chunks
     float M = -FLT_MAX;
-    for (int c = c_lo; c < c_hi; c++) M = fmaxf(M, ml[c * 2]);
+    for (int c = c_lo + (int)threadIdx.x; c < c_hi; c += blockDim.x) M = fmaxf(M, ml[c * 2]);
+    M = warp_max(M);
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = M;
+    __syncthreads();
+    M = s_red[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); w++) M = fmaxf(M, s_red[w]);
+    // weights of a tile of chunks into shared memory, then sums in rising chunk order
     float L = 0.0f;
-    for (int c = c_lo; c < c_hi; c++) L += ml[c * 2] == -FLT_MAX ? 0.0f : ml[c * 2 + 1] * exp2f(ml[c * 2] - M);
-    for (int d = threadIdx.x; d < AD_DH; d += blockDim.x) {
-        float acc = 0.0f;
-        for (int c = c_lo; c < c_hi; c++) {
-            float w = ml[c * 2] == -FLT_MAX ? 0.0f : exp2f(ml[c * 2] - M);
-            acc += op[(size_t)c * AD_DH + d] * w;
+    float acc[(AD_DH + AD_MERGE_THREADS - 1) / AD_MERGE_THREADS];
+#pragma unroll
+    for (int j = 0; j < (AD_DH + AD_MERGE_THREADS - 1) / AD_MERGE_THREADS; j++) acc[j] = 0.0f;
+    for (int t0 = c_lo; t0 < c_hi; t0 += AD_MERGE_TILE) {
+        const int n = min(AD_MERGE_TILE, c_hi - t0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            float m = ml[(t0 + i) * 2];
+            float w = m == -FLT_MAX ? 0.0f : exp2f(m - M);
+            s_w[i] = w;
+            s_lw[i] = ml[(t0 + i) * 2 + 1] * w;
         }
-        out[((size_t)b * H + h) * AD_DH + d] = __float2bfloat16_rn(acc / L);
+        __syncthreads();
+        for (int i = 0; i < n; i++) L += s_lw[i];
+#pragma unroll
+        for (int j = 0; j < (AD_DH + AD_MERGE_THREADS - 1) / AD_MERGE_THREADS; j++) {
+            int d = threadIdx.x + j * AD_MERGE_THREADS;
+            if (d < AD_DH) {
+                float a = acc[j];
+#pragma unroll 8
+                for (int i = 0; i < n; i++) a += op[(size_t)(t0 + i) * AD_DH + d] * s_w[i];
+                acc[j] = a;
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < (AD_DH + AD_MERGE_THREADS - 1) / AD_MERGE_THREADS; j++) {
+        int d = threadIdx.x + j * AD_MERGE_THREADS;
+        if (d < AD_DH) out[((size_t)b * H + h) * AD_DH + d] = __float2bfloat16_rn(acc[j] / L);
     }
 }
 
@@ -271,7 +302,7 @@ extern "C" int ri_attention_decode(const void* q, const void* k_pool, const void
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, o_part, ml_part, page_table, seq_slot, seq_len, H, KV,
         mpps, num_pages, max_chunks, scale * 1.4426950408889634f, window, err_flag);
     RI_CHECK_LAUNCH("attention_decode");
-    attention_decode_merge_kernel<<<dim3(H, seqs), AD_DH >= 128 ? 128 : 64, 0, stream>>>(
+    attention_decode_merge_kernel<<<dim3(H, seqs), AD_MERGE_THREADS, 0, stream>>>(
         o_part, ml_part, (bf16*)out, seq_len, H, max_chunks, window);
     RI_CHECK_LAUNCH("attention_decode_merge");
     return 0;

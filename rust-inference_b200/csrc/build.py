@@ -36,6 +36,7 @@ SOURCES: Dict[str, Tuple[str, ...]] = {
     "sampling": ("sampling.cu", "common.cuh"),
     "attention_decode": ("attention_decode.cu", "common.cuh", "mma_helpers.cuh"),
     "attention_prefill": ("attention_prefill.cu", "common.cuh", "mma_helpers.cuh"),
+    "linear_skinny": ("linear_skinny.cu", "common.cuh", "mma_helpers.cuh"),
     "attention_decode_noalloc": ("attention_decode_noalloc.cu", "attention_decode_noalloc.h", "attention_decode.cu",
                                  "common.cuh", "mma_helpers.cuh"),
 }

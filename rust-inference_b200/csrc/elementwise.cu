@@ -71,10 +71,97 @@ __global__ void rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ 
     for (int i = threadIdx.x; i < dim; i += blockDim.x) st_f(op + i, row[i] * inv * gain[i]);
 }
 
+// The same for rows whose length is a multiple of 4 and at most 4 * NV * blockDim: the row
+// stays in registers (NV float4 per thread), loads and stores are 16 / 8 bytes wide.  The
+// order of the additions (a thread's elements in rising order, then the block's tree) is
+// fixed by the row length alone.
+__device__ __forceinline__ float4 ld4(const float* p) { return *(const float4*)p; }
+__device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
+    uint2 u = *(const uint2*)p;
+    __nv_bfloat162 a = *(__nv_bfloat162*)&u.x, b = *(__nv_bfloat162*)&u.y;
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *(float4*)p = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *(unsigned*)&a;
+    u.y = *(unsigned*)&b;
+    *(uint2*)p = u;
+}
+
+template <typename T, int NV>
+__global__ void rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta, const int* __restrict__ rows,
+                                   const float* __restrict__ gain, T* __restrict__ out, int dim, float eps,
+                                   int write_back) {
+    __shared__ float red[33];
+    size_t r = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
+    float* rp = resid + r * dim;
+    const T* dp = delta ? delta + r * dim : nullptr;
+    const int nvec = dim >> 2;
+    float4 v[NV];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        int i = threadIdx.x + j * blockDim.x;
+        if (i < nvec) {
+            float4 a = ld4(rp + 4 * i);
+            if (dp) {
+                float4 d = ld4(dp + 4 * i);
+                a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+                if (write_back) st4(rp + 4 * i, a);
+            }
+            v[j] = a;
+            ss += a.x * a.x;
+            ss += a.y * a.y;
+            ss += a.z * a.z;
+            ss += a.w * a.w;
+        }
+    }
+    float total = block_sum(ss, red);
+    float inv = 1.0f / sqrtf(total / (float)dim + eps);
+    T* op = out + (size_t)blockIdx.x * dim;
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        int i = threadIdx.x + j * blockDim.x;
+        if (i < nvec) {
+            float4 g = ld4(gain + 4 * i);
+            st4(op + 4 * i, make_float4(v[j].x * inv * g.x, v[j].y * inv * g.y, v[j].z * inv * g.z, v[j].w * inv * g.w));
+        }
+    }
+}
+
+template <typename T>
+static bool launch_rmsnorm_vec(float* resid, const void* delta, const int* rows, const float* gain, void* out,
+                               int n_rows, int dim, float eps, int write_back, cudaStream_t stream) {
+    if (dim % 4) return false;
+    uintptr_t al = (uintptr_t)resid | (uintptr_t)gain | (uintptr_t)out | (uintptr_t)delta;
+    if (al & 15) return false;
+    int nvec = dim / 4;
+    int threads = nvec >= 1024 ? 1024 : ((nvec + 31) / 32) * 32;
+    int nv = (nvec + threads - 1) / threads;
+    const T* d = (const T*)delta;
+    T* o = (T*)out;
+    if (nv == 1) rmsnorm_vec_kernel<T, 1><<<n_rows, threads, 0, stream>>>(resid, d, rows, gain, o, dim, eps, write_back);
+    else if (nv == 2) rmsnorm_vec_kernel<T, 2><<<n_rows, threads, 0, stream>>>(resid, d, rows, gain, o, dim, eps, write_back);
+    else if (nv <= 4) rmsnorm_vec_kernel<T, 4><<<n_rows, threads, 0, stream>>>(resid, d, rows, gain, o, dim, eps, write_back);
+    else return false;
+    return true;
+}
+
 extern "C" int ri_rmsnorm(float* resid, const void* delta, const int* rows, const float* gain, void* out, int n_rows,
                           int dim, float eps, int write_back, int dtype, cudaStream_t stream) {
     if (n_rows == 0) return 0;
     RI_REQUIRE(n_rows > 0 && dim > 0, "rmsnorm: bad sizes rows=%d dim=%d", n_rows, dim);
+    if (rows) write_back = 0;
+    if (dtype == RI_DTYPE_F32 && launch_rmsnorm_vec<float>(resid, delta, rows, gain, out, n_rows, dim, eps, write_back, stream)) {
+        RI_CHECK_LAUNCH("rmsnorm");
+        return 0;
+    }
+    if (dtype == RI_DTYPE_BF16 && launch_rmsnorm_vec<__nv_bfloat16>(resid, delta, rows, gain, out, n_rows, dim, eps, write_back, stream)) {
+        RI_CHECK_LAUNCH("rmsnorm");
+        return 0;
+    }
     size_t smem = (size_t)dim * sizeof(float);
     RI_REQUIRE(smem <= 200 * 1024, "rmsnorm: a row of %d elements does not fit in shared memory (limit 51200)", dim);
     int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);

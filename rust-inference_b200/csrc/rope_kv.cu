@@ -46,7 +46,7 @@ __global__ void qk_norm_rope_append_kernel(const T* __restrict__ qkv, T* __restr
     int half = rot / 2;
     const T* row = qkv + (size_t)t * heads_total * Dh;
     float* x = buf[warp];
-    for (int h = warp; h < heads_total; h += RK_WARPS) {
+    for (int h = blockIdx.y * RK_WARPS + warp; h < heads_total; h += RK_WARPS * gridDim.y) {
         const T* src = row + (size_t)h * Dh;
         int which = h < H ? 0 : (h < H + KV ? 1 : 2);      // q, k, v
         T* dst;
@@ -102,13 +102,18 @@ extern "C" int ri_qk_norm_rope_append(const void* qkv, void* q_out, void* k_pool
     RI_REQUIRE(rot >= 0 && rot <= Dh && rot % 2 == 0, "qk_norm_rope_append: rotary_dim %d must be even and <= head_dim %d", rot, Dh);
     RI_REQUIRE(!rope_table || rot > 0, "qk_norm_rope_append: a rope table needs rotary_dim > 0");
     RI_REQUIRE(page_size > 0 && mpps > 0, "qk_norm_rope_append: bad page sizes");
+    // few tokens: spread the heads of a token over several blocks (one head per warp)
+    int head_blocks = (H + 2 * KV + RK_WARPS - 1) / RK_WARPS;
+    if ((long long)tokens * head_blocks > 4096) head_blocks = 1 > 4096 / tokens ? 1 : 4096 / tokens;
+    RI_REQUIRE(tokens <= 2147483647 && head_blocks <= 65535, "qk_norm_rope_append: bad grid");
+    dim3 grid(tokens, head_blocks);
     if (dtype == RI_DTYPE_F32)
-        qk_norm_rope_append_kernel<float><<<tokens, 32 * RK_WARPS, 0, stream>>>(
+        qk_norm_rope_append_kernel<float><<<grid, 32 * RK_WARPS, 0, stream>>>(
             (const float*)qkv, (float*)q_out, (float*)k_pool, (float*)v_pool, page_table, tok_seq, tok_pos, seq_slot,
             q_gain, k_gain, eps, (const float2*)rope_table, rope_rows, rot, H, KV, Dh, mpps, page_size, num_pages,
             write_kv, err_flag);
     else if (dtype == RI_DTYPE_BF16)
-        qk_norm_rope_append_kernel<__nv_bfloat16><<<tokens, 32 * RK_WARPS, 0, stream>>>(
+        qk_norm_rope_append_kernel<__nv_bfloat16><<<grid, 32 * RK_WARPS, 0, stream>>>(
             (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,
             page_table, tok_seq, tok_pos, seq_slot, q_gain, k_gain, eps, (const float2*)rope_table, rope_rows, rot, H,
             KV, Dh, mpps, page_size, num_pages, write_kv, err_flag);

@@ -284,12 +284,81 @@ argmax_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
     }
 }
 
-extern "C" int ri_argmax(const float* logits, long long row_stride, int rows, int vocab, int* out,
-                         cudaStream_t stream) {
+// Two stages for long rows: `slices` blocks per row each find the first maximum of their
+// slice, a second kernel picks among the slices (lowest index on ties, so the result is the
+// first maximum of the whole row).  part_val / part_idx: [rows, slices] scratch.
+__global__ void __launch_bounds__(256)
+argmax_slice_kernel(const float* __restrict__ logits, long long row_stride, int vocab, int per_slice,
+                    float* __restrict__ part_val, int* __restrict__ part_idx) {
+    __shared__ float fred[8];
+    __shared__ int ired[8];
+    const float* x = logits + (size_t)blockIdx.y * row_stride;
+    int lo = blockIdx.x * per_slice, hi = min(vocab, lo + per_slice);
+    float best = -FLT_MAX;
+    int bi = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        float v = x[i];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { fred[warp] = best; ired[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++)
+            if (fred[w] > best || (fred[w] == best && ired[w] < bi)) { best = fred[w]; bi = ired[w]; }
+        part_val[(size_t)blockIdx.y * gridDim.x + blockIdx.x] = best;
+        part_idx[(size_t)blockIdx.y * gridDim.x + blockIdx.x] = bi;
+    }
+}
+
+__global__ void argmax_pick_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int slices,
+                                   int* __restrict__ out) {
+    // one warp per row
+    int row = blockIdx.x, lane = threadIdx.x;
+    float best = -FLT_MAX;
+    int bi = 0x7fffffff;
+    for (int s = lane; s < slices; s += 32) {
+        float v = part_val[(size_t)row * slices + s];
+        int i = part_idx[(size_t)row * slices + s];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
+}
+
+extern "C" int ri_argmax_slices(int vocab) {
+    int s = (vocab + 2047) / 2048;
+    return s < 1 ? 1 : (s > 128 ? 128 : s);
+}
+
+// part_val, part_idx: [rows, ri_argmax_slices(vocab)] scratch (may be null when that is 1)
+extern "C" int ri_argmax(const float* logits, long long row_stride, int rows, int vocab, int* out, float* part_val,
+                         int* part_idx, cudaStream_t stream) {
     if (rows == 0) return 0;
     RI_REQUIRE(rows > 0 && vocab > 0, "argmax: bad sizes rows=%d vocab=%d", rows, vocab);
-    argmax_kernel<<<rows, SP_THREADS, 0, stream>>>(logits, row_stride, vocab, out);
-    RI_CHECK_LAUNCH("argmax");
+    int slices = ri_argmax_slices(vocab);
+    if (slices == 1 || !part_val || !part_idx) {
+        argmax_kernel<<<rows, SP_THREADS, 0, stream>>>(logits, row_stride, vocab, out);
+        RI_CHECK_LAUNCH("argmax");
+        return 0;
+    }
+    RI_REQUIRE(rows <= 65535, "argmax: at most 65535 rows");
+    int per_slice = (vocab + slices - 1) / slices;
+    argmax_slice_kernel<<<dim3(slices, rows), 256, 0, stream>>>(logits, row_stride, vocab, per_slice, part_val, part_idx);
+    RI_CHECK_LAUNCH("argmax (slices)");
+    argmax_pick_kernel<<<rows, 32, 0, stream>>>(part_val, part_idx, slices, out);
+    RI_CHECK_LAUNCH("argmax (pick)");
     return 0;
 }
 

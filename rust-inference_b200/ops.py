@@ -29,13 +29,15 @@ _SIGNATURES = {
     ("attention_plain", "ri_attention_plain"): [_P] * 8 + [_I] * 7 + [_F, _I, _I, _P, _P],
     ("linear_f32", "ri_linear_f32"): [_P, _P, _P, _I, _I, _I, _P],
     ("sampling", "ri_sample"): [_P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P],
-    ("sampling", "ri_argmax"): [_P, _L, _I, _I, _P, _P],
+    ("sampling", "ri_argmax"): [_P, _L, _I, _I, _P, _P, _P, _P],
     ("sampling", "ri_mark_seen"): [_P, _L, _P, _P, _I, _I, _P],
     ("attention_decode", "ri_attention_decode"): [_P] * 9 + [_I] * 8 + [_F, _I, _P, _P],
+    ("linear_skinny", "ri_linear_skinny"): [_P, _P, _P, _I, _I, _I, _I, _P],
     ("attention_prefill", "ri_attention_prefill"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _P],
 }
 DECODE_CHUNK = 128          # keys per partial result of the decode attention kernel
 MAX_FAST_HEAD_DIM = 256
+SKINNY_MAX_TOKENS = 16      # up to here the bfloat16 linear is this package's weight-streaming kernel
 _fn_cache = {}
 
 
@@ -177,9 +179,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     """y = x w^T for x [M, K], w [N, K].
 
     float32: this package's own FMA kernel (no tensor cores, no TF32).
-    bfloat16: the library GEMM (cuBLAS through torch), as the reference engine
-    uses cuBLAS for its linears (src/cuda/mod.rs:186-232 there); ``out_dtype``
-    float32 keeps the float32 accumulator (used for the logits)."""
+    bfloat16, up to 16 tokens: this package's weight-streaming tensor-core kernel.
+    bfloat16, more tokens: the library GEMM (cuBLAS through torch), as the
+    reference engine uses cuBLAS for its linears (src/cuda/mod.rs:186-232 there).
+    ``out_dtype`` float32 keeps the float32 accumulator (used for the logits)."""
     _need(x, "x")
     _need(w, "w", x.dtype)
     M, K = x.shape
@@ -192,6 +195,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         return y
     if x.dtype != torch.bfloat16:
         raise KernelError(f"linear: dtype {x.dtype}")
+    if M <= SKINNY_MAX_TOKENS and K % 8 == 0:
+        # a handful of tokens: the weight-streaming kernel of this package
+        y = torch.empty((M, N), dtype=torch.float32 if out_dtype == torch.float32 else torch.bfloat16, device=x.device)
+        _call("linear_skinny", "ri_linear_skinny", x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K,
+              1 if out_dtype == torch.float32 else 0, _stream())
+        return y
     if out_dtype == torch.float32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
     return torch.mm(x, w.t())
@@ -322,7 +331,13 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     _need(logits, "logits", torch.float32)
     rows, vocab = logits.shape
     out = torch.empty(rows, dtype=torch.int32, device=logits.device)
-    _call("sampling", "ri_argmax", logits.data_ptr(), logits.stride(0), rows, vocab, out.data_ptr(), _stream())
+    slices = min(128, max(1, -(-vocab // 2048)))           # ri_argmax_slices of the library
+    part_val = part_idx = None
+    if slices > 1:
+        part_val = torch.empty((rows, slices), dtype=torch.float32, device=logits.device)
+        part_idx = torch.empty((rows, slices), dtype=torch.int32, device=logits.device)
+    _call("sampling", "ri_argmax", logits.data_ptr(), logits.stride(0), rows, vocab, out.data_ptr(), _ptr(part_val),
+          _ptr(part_idx), _stream())
     return out
 
 
