@@ -26,7 +26,8 @@ static int noalloc_setup(int device) {
     void* p = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&p, ri_noalloc_scratch);
     if (e != cudaSuccess) RI_FAIL((int)e, "attention_decode_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-    e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DecodeSmem));
+    e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)decode_smem_bytes(AD_ROWS));       // the most any group size needs
     if (e != cudaSuccess) RI_FAIL((int)e, "attention_decode_noalloc: shared memory limit: %s", cudaGetErrorString(e));
     g_scratch_addr[device] = (float*)p;
     return 0;
@@ -58,7 +59,8 @@ extern "C" int ri_attention_decode_noalloc(const void* q, const void* k_pool, co
     float* o_part = g_scratch_addr[device];
     float* ml_part = (float*)((unsigned char*)o_part + round256((size_t)seqs * H * max_chunks * Dh * sizeof(float)));
     dim3 grid(max_chunks, KV, seqs);
-    attention_decode_kernel<<<grid, 32 * AD_WARPS, sizeof(DecodeSmem), stream>>>(
+    const int G = H / KV;
+    attention_decode_kernel<<<grid, 32 * AD_WARPS, decode_smem_bytes(G < AD_ROWS ? G : AD_ROWS), stream>>>(
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, o_part, ml_part, page_table, seq_slot, seq_len, H, KV,
         mpps, num_pages, max_chunks, scale * 1.4426950408889634f, window, err_flag);
     RI_CHECK_LAUNCH("attention_decode_noalloc");
