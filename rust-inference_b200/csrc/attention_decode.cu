@@ -107,6 +107,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int quad = lane >> 2, qc = lane & 3;
     const int slot = seq_slot[b];
+    pdl_trigger_early();
 
     const int key0 = c0 + warp * AD_PAGE;
     const bool page_live = key0 < len && key0 + AD_PAGE > first_key;
@@ -120,6 +121,12 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     }
     const size_t page_base = (((size_t)(page < 0 ? 0 : page) * KV + kvh) * AD_PAGE) * AD_DH;
     const int valid_rows = page < 0 ? 0 : min(AD_PAGE, len - key0);   // rows of the page that hold keys
+    // The kernel before this one wrote the newest key and value (position len-1) and the
+    // queries.  A warp whose page holds that position waits for it before it reads the
+    // page; the other warps read keys and values of earlier steps and wait only before
+    // they read the queries.
+    const bool newest_page = key0 + AD_PAGE >= len;
+    if (newest_page) pdl_wait();
 
     // ---- values: one bulk copy per row into padded shared memory; rows without a key are zeroed ----
     if (lane == 0) {
@@ -139,6 +146,19 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     for (int g0 = 0; g0 < G; g0 += AD_ROWS) {
         // ---- query fragments of this pass: rows quad and quad+8 of the group (zero past its end) ----
         uint4 qa[AD_GROUPS], qb[AD_GROUPS];
+        uint4 kf[4][AD_GROUPS];
+#pragma unroll
+        for (int t = 0; t < 4; t++) {                              // keys straight from global memory
+            const int r = t * 8 + quad;                            // row of the page = key key0 + r
+            const bool okr = r < valid_rows;
+            const bf16* pk = k_pool + page_base + (size_t)(okr ? r : 0) * AD_DH;
+#pragma unroll
+            for (int g = 0; g < AD_GROUPS; g++) {
+                int d = g * 32 + qc * 8;
+                kf[t][g] = (okr && d < AD_DH) ? ldg_nc16(pk + d) : make_uint4(0, 0, 0, 0);
+            }
+        }
+        if (g0 == 0 && !newest_page) pdl_wait();                   // the queries come from the kernel before
         {
             const bool okA = g0 + quad < G, okB = g0 + quad + 8 < G;
             const bf16* pa = q + ((size_t)b * H + kvh * G + g0 + (okA ? quad : 0)) * AD_DH;
@@ -151,21 +171,9 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
                 qb[g] = (in && okB) ? *(const uint4*)(pb + d) : make_uint4(0, 0, 0, 0);
             }
         }
-        // ---- S[16 rows, 32 keys] = Q K^T, keys straight from global memory -------------------------
+        // ---- S[16 rows, 32 keys] = Q K^T ------------------------------------------------------------
         float s[4][4];
         {
-            uint4 kf[4][AD_GROUPS];
-#pragma unroll
-            for (int t = 0; t < 4; t++) {
-                const int r = t * 8 + quad;                        // row of the page = key key0 + r
-                const bool okr = r < valid_rows;
-                const bf16* pk = k_pool + page_base + (size_t)(okr ? r : 0) * AD_DH;
-#pragma unroll
-                for (int g = 0; g < AD_GROUPS; g++) {
-                    int d = g * 32 + qc * 8;
-                    kf[t][g] = (okr && d < AD_DH) ? ldg_nc16(pk + d) : make_uint4(0, 0, 0, 0);
-                }
-            }
 #pragma unroll
             for (int t = 0; t < 4; t++) {
 #pragma unroll
@@ -232,6 +240,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
             }
         }
         // ---- combine the four warps in warp order (only the rows that are heads) ---------------------
+        if (g0 + AD_ROWS >= G) pdl_trigger_late();
         if (g0 > 0) __syncthreads();          // the pass before has finished reading the combine area
         if (qc == 0) {
             sm.wm[warp][quad] = mx[0];
@@ -286,6 +295,8 @@ attention_decode_merge_kernel(const float* __restrict__ o_part, const float* __r
                               bf16* __restrict__ out, const int* __restrict__ seq_len, int H, int max_chunks,
                               int window) {
     const int h = blockIdx.x, b = blockIdx.y;
+    pdl_trigger();
+    pdl_wait();
     const int len = seq_len[b];
     const int first_key = (window > 0 && len - window > 0) ? len - window : 0;
     const int c_lo = first_key / AD_CHUNK, c_hi = (len + AD_CHUNK - 1) / AD_CHUNK;     // [c_lo, c_hi)
@@ -368,12 +379,12 @@ extern "C" int ri_attention_decode(const void* q, const void* k_pool, const void
     int rc = decode_configure(H / KV, &smem);
     if (rc) return rc;
     dim3 grid(max_chunks, KV, seqs);
-    attention_decode_kernel<<<grid, 32 * AD_WARPS, smem, stream>>>(
-        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, o_part, ml_part, page_table, seq_slot, seq_len, H, KV,
-        mpps, num_pages, max_chunks, scale * 1.4426950408889634f, window, err_flag);
+    ri_launch_pdl(attention_decode_kernel, grid, dim3(32 * AD_WARPS), smem, stream,
+                  (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, o_part, ml_part, page_table, seq_slot, seq_len,
+                  H, KV, mpps, num_pages, max_chunks, scale * 1.4426950408889634f, window, err_flag);
     RI_CHECK_LAUNCH("attention_decode");
-    attention_decode_merge_kernel<<<dim3(H, seqs), AD_MERGE_THREADS, 0, stream>>>(
-        o_part, ml_part, (bf16*)out, seq_len, H, max_chunks, window);
+    ri_launch_pdl(attention_decode_merge_kernel, dim3(H, seqs), dim3(AD_MERGE_THREADS), 0, stream,
+                  (const float*)o_part, (const float*)ml_part, (bf16*)out, seq_len, H, max_chunks, window);
     RI_CHECK_LAUNCH("attention_decode_merge");
     return 0;
 }

@@ -87,6 +87,19 @@ def build_dir() -> str:
     raise KernelBuildError(f"no writable build folder among {cands}")
 
 
+def _with_env_defines(defines: Optional[Dict[str, object]]) -> Optional[Dict[str, object]]:
+    """Extra -D flags for every compile from RUST_INFERENCE_B200_DEFINES="A=1,B=2" (for experiments)."""
+    extra = os.environ.get("RUST_INFERENCE_B200_DEFINES", "")
+    if not extra:
+        return defines
+    out = dict(defines or {})
+    for item in extra.split(","):
+        if item.strip():
+            k, _, v = item.partition("=")
+            out[k.strip()] = v.strip() or "1"
+    return out
+
+
 def _variant_name(name: str, defines: Optional[Dict[str, object]]) -> str:
     if not defines:
         return name
@@ -123,6 +136,7 @@ def find_built(name: str, defines: Optional[Dict[str, object]] = None) -> Option
 
 def compile_library(name: str, defines: Optional[Dict[str, object]] = None, verbose: bool = False) -> str:
     """Compile one source (if its library is not there yet) and return the path."""
+    defines = _with_env_defines(defines)
     if name not in SOURCES:
         raise KernelBuildError(f"unknown kernel library {name!r}")
     have = find_built(name, defines)
@@ -159,6 +173,7 @@ def compile_library(name: str, defines: Optional[Dict[str, object]] = None, verb
 
 def library(name: str, defines: Optional[Dict[str, object]] = None) -> ctypes.CDLL:
     """The loaded library of ``name`` (compiled first if need be)."""
+    defines = _with_env_defines(defines)
     key = _variant_name(name, defines)
     lib = _loaded.get(key)
     if lib is not None:

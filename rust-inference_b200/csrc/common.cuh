@@ -37,6 +37,50 @@ extern "C" const char* ri_last_error() { return ri_errbuf; }
         if (e_ != cudaSuccess) RI_FAIL((int)e_, "%s: %s", name, cudaGetErrorString(e_));   \
     } while (0)
 
+// ---- programmatic dependent launch ---------------------------------------------------------
+// A kernel launched with ri_launch_pdl may start while the kernel before it in the stream is
+// still running.  It must call pdl_wait() before it reads anything that kernel (or any
+// earlier one) wrote and before its first write to global memory; what it does before that
+// (index arithmetic, loads of what no kernel of the step writes) overlaps the predecessor's
+// tail.  pdl_trigger() lets the blocks of the kernel after this one start in the same way.
+// Both are no-ops for a kernel that was launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+// Where a kernel lets its successor start: early (at its top) the successor's blocks take
+// places on the SMs while this kernel still has blocks waiting for one; late (after its main
+// loop) they only overlap its tail.
+#ifndef RI_PDL_EARLY_TRIGGER
+#define RI_PDL_EARLY_TRIGGER 0
+#endif
+__device__ __forceinline__ void pdl_trigger_early() { if (RI_PDL_EARLY_TRIGGER) pdl_trigger(); }
+__device__ __forceinline__ void pdl_trigger_late() { if (!RI_PDL_EARLY_TRIGGER) pdl_trigger(); }
+
+#include <stdlib.h>
+static inline int ri_pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("RUST_INFERENCE_B200_NO_PDL");
+        v = (e && e[0] == '1') ? 0 : 1;
+    }
+    return v;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t ri_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                        cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = ri_pdl_enabled();
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 __device__ __forceinline__ float ld_f(const float* p) { return *p; }
 __device__ __forceinline__ float ld_f(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 __device__ __forceinline__ void st_f(float* p, float v) { *p = v; }

@@ -14,6 +14,8 @@
 template <typename T>
 __global__ void embed_rows_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
                                   int dim, int vocab, int* __restrict__ bad) {
+    pdl_trigger();
+    pdl_wait();
     int id = ids[blockIdx.x];
     if (id < 0 || id >= vocab) {          // checked on the host as well; never read out of range
         if (threadIdx.x == 0) atomicExch(bad, 1);
@@ -30,9 +32,9 @@ extern "C" int ri_embed_rows(const int* ids, const void* table, float* out, int 
     RI_REQUIRE(tokens > 0 && dim > 0 && vocab > 0, "embed_rows: bad sizes tokens=%d dim=%d vocab=%d", tokens, dim, vocab);
     int threads = dim >= 1024 ? 256 : 128;
     if (dtype == RI_DTYPE_F32)
-        embed_rows_kernel<float><<<tokens, threads, 0, stream>>>(ids, (const float*)table, out, dim, vocab, bad_flag);
+        ri_launch_pdl(embed_rows_kernel<float>, dim3(tokens), dim3(threads), 0, stream, ids, (const float*)table, out, dim, vocab, bad_flag);
     else if (dtype == RI_DTYPE_BF16)
-        embed_rows_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, dim, vocab, bad_flag);
+        ri_launch_pdl(embed_rows_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, ids, (const __nv_bfloat16*)table, out, dim, vocab, bad_flag);
     else
         RI_FAIL(-1, "embed_rows: unknown dtype %d", dtype);
     RI_CHECK_LAUNCH("embed_rows");
@@ -95,6 +97,8 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restric
                                    const float* __restrict__ gain, T* __restrict__ out, int dim, float eps,
                                    int write_back) {
     __shared__ float red[33];
+    pdl_trigger();
+    pdl_wait();
     size_t r = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
     float* rp = resid + r * dim;
     const T* dp = delta ? delta + r * dim : nullptr;
@@ -142,9 +146,9 @@ static bool launch_rmsnorm_vec(float* resid, const void* delta, const int* rows,
     int nv = (nvec + threads - 1) / threads;
     const T* d = (const T*)delta;
     T* o = (T*)out;
-    if (nv == 1) rmsnorm_vec_kernel<T, 1><<<n_rows, threads, 0, stream>>>(resid, d, rows, gain, o, dim, eps, write_back);
-    else if (nv == 2) rmsnorm_vec_kernel<T, 2><<<n_rows, threads, 0, stream>>>(resid, d, rows, gain, o, dim, eps, write_back);
-    else if (nv <= 4) rmsnorm_vec_kernel<T, 4><<<n_rows, threads, 0, stream>>>(resid, d, rows, gain, o, dim, eps, write_back);
+    if (nv == 1) ri_launch_pdl(rmsnorm_vec_kernel<T, 1>, dim3(n_rows), dim3(threads), 0, stream, resid, d, rows, gain, o, dim, eps, write_back);
+    else if (nv == 2) ri_launch_pdl(rmsnorm_vec_kernel<T, 2>, dim3(n_rows), dim3(threads), 0, stream, resid, d, rows, gain, o, dim, eps, write_back);
+    else if (nv <= 4) ri_launch_pdl(rmsnorm_vec_kernel<T, 4>, dim3(n_rows), dim3(threads), 0, stream, resid, d, rows, gain, o, dim, eps, write_back);
     else return false;
     return true;
 }
@@ -207,6 +211,8 @@ extern "C" int ri_add_rows(float* resid, const void* delta, long long n, int dty
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total) {
+    pdl_trigger();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     size_t m = i / inter;
@@ -221,8 +227,8 @@ extern "C" int ri_silu_mul(const void* gu, void* out, int rows, int inter, int d
     RI_REQUIRE(rows > 0 && inter > 0, "silu_mul: bad sizes rows=%d inter=%d", rows, inter);
     size_t total = (size_t)rows * inter;
     unsigned blocks = (unsigned)((total + 255) / 256);
-    if (dtype == RI_DTYPE_F32) silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, inter, total);
-    else if (dtype == RI_DTYPE_BF16) silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total);
+    if (dtype == RI_DTYPE_F32) ri_launch_pdl(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)out, inter, total);
+    else if (dtype == RI_DTYPE_BF16) ri_launch_pdl(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total);
     else RI_FAIL(-1, "silu_mul: unknown dtype %d", dtype);
     RI_CHECK_LAUNCH("silu_mul");
     return 0;

@@ -34,6 +34,8 @@ linear_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, Out
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int quad = lane >> 2, qc = lane & 3;
     const int n0 = blockIdx.x * SK_ROWS;
+    pdl_trigger_early();
+    pdl_wait();
     const int steps = (K + 31) / 32;                        // groups of 32 k
     const int s_lo = (int)((long long)steps * warp / SK_WARPS), s_hi = (int)((long long)steps * (warp + 1) / SK_WARPS);
     // rows past N and tokens past M are computed on row 0 / token 0 and never written
@@ -83,6 +85,7 @@ linear_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, Out
             mma_bf16(acc[t], a.z, b.z, a.w, b.w, xv.z, xv.w);
         }
     }
+    pdl_trigger_late();
     // acc[t][0,1]: (row quad, tokens t*8 + 2qc, +1); acc[t][2,3]: (row quad+8, same tokens)
 #pragma unroll
     for (int t = 0; t < NT; t++)
@@ -102,7 +105,7 @@ linear_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, Out
 template <int NT, int U, typename OutT>
 static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, cudaStream_t stream) {
     dim3 grid((N + SK_ROWS - 1) / SK_ROWS);
-    linear_skinny_kernel<NT, U, OutT><<<grid, 32 * SK_WARPS, 0, stream>>>((const bf16*)x, (const bf16*)w, (OutT*)y, M, N, K);
+    ri_launch_pdl(linear_skinny_kernel<NT, U, OutT>, grid, dim3(32 * SK_WARPS), 0, stream, (const bf16*)x, (const bf16*)w, (OutT*)y, M, N, K);
     return 0;
 }
 

@@ -26,6 +26,8 @@ __global__ void qk_norm_rope_append_kernel(const T* __restrict__ qkv, T* __restr
                                            int Dh, int mpps, int page_size, int num_pages, int write_kv,
                                            int* __restrict__ err) {
     __shared__ float buf[RK_WARPS][RK_MAX_DH];
+    pdl_trigger();
+    pdl_wait();
     int t = blockIdx.x;
     int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int pos = tok_pos[t];
@@ -108,12 +110,12 @@ extern "C" int ri_qk_norm_rope_append(const void* qkv, void* q_out, void* k_pool
     RI_REQUIRE(tokens <= 2147483647 && head_blocks <= 65535, "qk_norm_rope_append: bad grid");
     dim3 grid(tokens, head_blocks);
     if (dtype == RI_DTYPE_F32)
-        qk_norm_rope_append_kernel<float><<<grid, 32 * RK_WARPS, 0, stream>>>(
+        ri_launch_pdl(qk_norm_rope_append_kernel<float>, grid, dim3(32 * RK_WARPS), 0, stream,
             (const float*)qkv, (float*)q_out, (float*)k_pool, (float*)v_pool, page_table, tok_seq, tok_pos, seq_slot,
             q_gain, k_gain, eps, (const float2*)rope_table, rope_rows, rot, H, KV, Dh, mpps, page_size, num_pages,
             write_kv, err_flag);
     else if (dtype == RI_DTYPE_BF16)
-        qk_norm_rope_append_kernel<__nv_bfloat16><<<grid, 32 * RK_WARPS, 0, stream>>>(
+        ri_launch_pdl(qk_norm_rope_append_kernel<__nv_bfloat16>, grid, dim3(32 * RK_WARPS), 0, stream,
             (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,
             page_table, tok_seq, tok_pos, seq_slot, q_gain, k_gain, eps, (const float2*)rope_table, rope_rows, rot, H,
             KV, Dh, mpps, page_size, num_pages, write_kv, err_flag);

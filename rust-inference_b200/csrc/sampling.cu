@@ -292,6 +292,8 @@ argmax_slice_kernel(const float* __restrict__ logits, long long row_stride, int 
                     float* __restrict__ part_val, int* __restrict__ part_idx) {
     __shared__ float fred[8];
     __shared__ int ired[8];
+    pdl_trigger();
+    pdl_wait();
     const float* x = logits + (size_t)blockIdx.y * row_stride;
     int lo = blockIdx.x * per_slice, hi = min(vocab, lo + per_slice);
     float best = -FLT_MAX;
@@ -320,6 +322,8 @@ argmax_slice_kernel(const float* __restrict__ logits, long long row_stride, int 
 __global__ void argmax_pick_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int slices,
                                    int* __restrict__ out) {
     // one warp per row
+    pdl_trigger();
+    pdl_wait();
     int row = blockIdx.x, lane = threadIdx.x;
     float best = -FLT_MAX;
     int bi = 0x7fffffff;
@@ -355,9 +359,9 @@ extern "C" int ri_argmax(const float* logits, long long row_stride, int rows, in
     }
     RI_REQUIRE(rows <= 65535, "argmax: at most 65535 rows");
     int per_slice = (vocab + slices - 1) / slices;
-    argmax_slice_kernel<<<dim3(slices, rows), 256, 0, stream>>>(logits, row_stride, vocab, per_slice, part_val, part_idx);
+    ri_launch_pdl(argmax_slice_kernel, dim3(slices, rows), dim3(256), 0, stream, logits, row_stride, vocab, per_slice, part_val, part_idx);
     RI_CHECK_LAUNCH("argmax (slices)");
-    argmax_pick_kernel<<<rows, 32, 0, stream>>>(part_val, part_idx, slices, out);
+    ri_launch_pdl(argmax_pick_kernel, dim3(rows), dim3(32), 0, stream, (const float*)part_val, (const int*)part_idx, slices, out);
     RI_CHECK_LAUNCH("argmax (pick)");
     return 0;
 }
