@@ -93,6 +93,108 @@ __global__ void qk_norm_rope_append_kernel(const T* __restrict__ qkv, T* __restr
     }
 }
 
+// The same for head sizes of 64, 128 or 256 with the whole head rotated: a lane holds VEC
+// consecutive elements (Dh = 32 * VEC), loads and stores are VEC elements wide, and the
+// rotation partner of an element (half a head away) sits in lane ^ 16.
+template <typename T, int V>
+struct alignas(sizeof(T) * V) VecOf {
+    T v[V];
+};
+
+template <typename T, int VEC>
+__global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pool,
+                                               T* __restrict__ v_pool, const int* __restrict__ page_table,
+                                               const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                               const int* __restrict__ seq_slot, const float* __restrict__ q_gain,
+                                               const float* __restrict__ k_gain, float eps,
+                                               const float2* __restrict__ rope, int rope_rows, int H, int KV, int mpps,
+                                               int page_size, int num_pages, int write_kv, int* __restrict__ err) {
+    constexpr int Dh = 32 * VEC;
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int pos = tok_pos[t];
+    const int slot = seq_slot[tok_seq[t]];
+    int page = -1;
+    if (write_kv) {
+        page = page_table[(size_t)slot * mpps + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicExch(err, 2);
+            page = -1;
+        }
+    }
+    if (rope && (pos < 0 || pos >= rope_rows)) {
+        if (threadIdx.x == 0) atomicExch(err, 3);
+        return;
+    }
+    const int heads_total = H + 2 * KV;
+    const T* row = qkv + (size_t)t * heads_total * Dh;
+    const int d0 = lane * VEC;                                   // this lane's first element
+    float cs_c[VEC], cs_s[VEC];
+    if (rope) {
+        const float2* cs = rope + (size_t)pos * (Dh / 2) + (lane & 15) * VEC;
+#pragma unroll
+        for (int j = 0; j < VEC; j++) {
+            float2 c = cs[j];
+            cs_c[j] = c.x;
+            cs_s[j] = (lane < 16) ? -c.y : c.y;                  // low half: a*c - b*s; high half: b*c + a*s
+        }
+    }
+    for (int h = blockIdx.y * RK_WARPS + warp; h < heads_total; h += RK_WARPS * gridDim.y) {
+        const int which = h < H ? 0 : (h < H + KV ? 1 : 2);
+        T* dst;
+        if (which == 0) {
+            dst = q_out + ((size_t)t * H + h) * Dh;
+        } else {
+            if (!write_kv || page < 0) continue;
+            const int kvh = which == 1 ? h - H : h - H - KV;
+            T* pool = which == 1 ? k_pool : v_pool;
+            dst = pool + (((size_t)page * KV + kvh) * page_size + pos % page_size) * Dh;
+        }
+        VecOf<T, VEC> in = *(const VecOf<T, VEC>*)(row + (size_t)h * Dh + d0);
+        if (which == 2) {
+            *(VecOf<T, VEC>*)(dst + d0) = in;
+            continue;
+        }
+        float x[VEC];
+        float ss = 0.0f;
+#pragma unroll
+        for (int j = 0; j < VEC; j++) {
+            x[j] = ld_f(&in.v[j]);
+            ss += x[j] * x[j];
+        }
+        const float* gain = which == 0 ? q_gain : k_gain;
+        if (gain) {
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / (float)Dh + eps);
+#pragma unroll
+            for (int j = 0; j < VEC; j++) x[j] = x[j] * inv * gain[d0 + j];
+        }
+        VecOf<T, VEC> o;
+#pragma unroll
+        for (int j = 0; j < VEC; j++) {
+            float v = x[j];
+            if (rope) {
+                float other = __shfl_xor_sync(0xffffffffu, x[j], 16);
+                v = x[j] * cs_c[j] + other * cs_s[j];
+            }
+            st_f(&o.v[j], v);
+        }
+        *(VecOf<T, VEC>*)(dst + d0) = o;
+    }
+}
+
+template <typename T, int VEC>
+static void launch_rope_vec(dim3 grid, cudaStream_t stream, const void* qkv, void* q_out, void* k_pool, void* v_pool,
+                            const int* page_table, const int* tok_seq, const int* tok_pos, const int* seq_slot,
+                            const float* q_gain, const float* k_gain, float eps, const float* rope_table, int rope_rows,
+                            int H, int KV, int mpps, int page_size, int num_pages, int write_kv, int* err_flag) {
+    ri_launch_pdl(qk_norm_rope_append_vec_kernel<T, VEC>, grid, dim3(32 * RK_WARPS), 0, stream, (const T*)qkv, (T*)q_out,
+                  (T*)k_pool, (T*)v_pool, page_table, tok_seq, tok_pos, seq_slot, q_gain, k_gain, eps,
+                  (const float2*)rope_table, rope_rows, H, KV, mpps, page_size, num_pages, write_kv, err_flag);
+}
+
 extern "C" int ri_qk_norm_rope_append(const void* qkv, void* q_out, void* k_pool, void* v_pool, const int* page_table,
                                       const int* tok_seq, const int* tok_pos, const int* seq_slot, const float* q_gain,
                                       const float* k_gain, float eps, const float* rope_table, int rope_rows, int rot,
@@ -109,6 +211,21 @@ extern "C" int ri_qk_norm_rope_append(const void* qkv, void* q_out, void* k_pool
     if ((long long)tokens * head_blocks > 4096) head_blocks = 1 > 4096 / tokens ? 1 : 4096 / tokens;
     RI_REQUIRE(tokens <= 2147483647 && head_blocks <= 65535, "qk_norm_rope_append: bad grid");
     dim3 grid(tokens, head_blocks);
+    const bool whole = !rope_table || rot == Dh;
+    const bool aligned = ((((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool) & 31) == 0);
+    if (whole && aligned && (Dh == 64 || Dh == 128 || Dh == 256) && (dtype == RI_DTYPE_F32 || dtype == RI_DTYPE_BF16)) {
+#define RI_ROPE_VEC(T, V) launch_rope_vec<T, V>(grid, stream, qkv, q_out, k_pool, v_pool, page_table, tok_seq, tok_pos, \
+                                                seq_slot, q_gain, k_gain, eps, rope_table, rope_rows, H, KV, mpps,      \
+                                                page_size, num_pages, write_kv, err_flag)
+        if (dtype == RI_DTYPE_F32) {
+            if (Dh == 64) RI_ROPE_VEC(float, 2); else if (Dh == 128) RI_ROPE_VEC(float, 4); else RI_ROPE_VEC(float, 8);
+        } else {
+            if (Dh == 64) RI_ROPE_VEC(__nv_bfloat16, 2); else if (Dh == 128) RI_ROPE_VEC(__nv_bfloat16, 4); else RI_ROPE_VEC(__nv_bfloat16, 8);
+        }
+#undef RI_ROPE_VEC
+        RI_CHECK_LAUNCH("qk_norm_rope_append");
+        return 0;
+    }
     if (dtype == RI_DTYPE_F32)
         ri_launch_pdl(qk_norm_rope_append_kernel<float>, grid, dim3(32 * RK_WARPS), 0, stream,
             (const float*)qkv, (float*)q_out, (float*)k_pool, (float*)v_pool, page_table, tok_seq, tok_pos, seq_slot,

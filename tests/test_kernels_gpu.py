@@ -121,9 +121,11 @@ def _paged(rng, lens, KV, Dh, P, dtype, extra_pages=3):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,KV,Dh,window", [(4, 2, 16, 0), (6, 1, 32, 0), (3, 3, 48, 0), (8, 2, 128, 0),
-                                            (5, 5, 80, 37), (4, 1, 256, 0), (2, 1, 64, 5)])
-def test_norm_rope_append_then_attention(dtype, H, KV, Dh, window):
+@pytest.mark.parametrize("H,KV,Dh,window,full", [(4, 2, 16, 0, True), (6, 1, 32, 0, True), (3, 3, 48, 0, False),
+                                                 (8, 2, 128, 0, False), (5, 5, 80, 37, False), (4, 1, 256, 0, False),
+                                                 (2, 1, 64, 5, False), (6, 2, 64, 0, True), (8, 2, 128, 0, True),
+                                                 (3, 1, 256, 0, True)])
+def test_norm_rope_append_then_attention(dtype, H, KV, Dh, window, full):
     """New tokens of several sequences against an existing cache: the appended keys and
     values land in the right page rows and every query sees exactly its keys."""
     from rust_inference_b200 import ops
@@ -134,7 +136,7 @@ def test_norm_rope_append_then_attention(dtype, H, KV, Dh, window):
     lens = [a + b for a, b in zip(old, new)]
     table, slots, total = _paged(rng, lens, KV, Dh, P, dtype)
     tdt = DT[dtype]
-    eps, theta, rot = 1e-5, 10000.0, Dh - 16 if Dh > 32 else Dh
+    eps, theta, rot = 1e-5, 10000.0, Dh if full else Dh - 16     # whole head rotated, or all but the last 16
     # full k/v history in plain form (already normed and rotated), then the new raw tokens
     k_hist = [rnd(rng, n, KV, Dh, dtype=dtype) for n in old]
     v_hist = [rnd(rng, n, KV, Dh, dtype=dtype) for n in old]
