@@ -37,6 +37,7 @@ SOURCES: Dict[str, Tuple[str, ...]] = {
     "attention_decode": ("attention_decode.cu", "common.cuh", "mma_helpers.cuh"),
     "attention_prefill": ("attention_prefill.cu", "common.cuh", "mma_helpers.cuh"),
     "linear_skinny": ("linear_skinny.cu", "common.cuh", "mma_helpers.cuh"),
+    "attention_prefill_tc": ("attention_prefill_tc.cu", "common.cuh", "mma_helpers.cuh"),
     "attention_decode_noalloc": ("attention_decode_noalloc.cu", "attention_decode_noalloc.h", "attention_decode.cu",
                                  "common.cuh", "mma_helpers.cuh"),
 }
@@ -48,6 +49,7 @@ VARIANTS: Dict[str, Tuple[Dict[str, object], ...]] = {
     "attention_decode": tuple({"RI_HEAD_DIM": d} for d in HEAD_DIMS),
     "attention_prefill": tuple({"RI_HEAD_DIM": d} for d in HEAD_DIMS),
     "attention_decode_noalloc": ({"RI_HEAD_DIM": 64}, {"RI_HEAD_DIM": 128}),
+    "attention_prefill_tc": ({"RI_HEAD_DIM": 64}, {"RI_HEAD_DIM": 128}),
 }
 
 

@@ -33,10 +33,13 @@ _SIGNATURES = {
     ("sampling", "ri_mark_seen"): [_P, _L, _P, _P, _I, _I, _P],
     ("attention_decode", "ri_attention_decode"): [_P] * 9 + [_I] * 8 + [_F, _I, _P, _P],
     ("linear_skinny", "ri_linear_skinny"): [_P, _P, _P, _I, _I, _I, _I, _P],
+    ("attention_prefill_tc", "ri_attention_prefill_tc"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _P],
     ("attention_prefill", "ri_attention_prefill"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _P],
 }
 DECODE_CHUNK = 128          # keys per partial result of the decode attention kernel
 MAX_FAST_HEAD_DIM = 256
+TCGEN05_HEAD_DIMS = (64, 128)   # head sizes the tcgen05 prefill attention kernel is built for
+_NO_TCGEN05 = __import__("os").environ.get("RUST_INFERENCE_B200_NO_TCGEN05") == "1"   # for comparisons
 SKINNY_MAX_TOKENS = 16      # up to here the bfloat16 linear is this package's weight-streaming kernel
 _fn_cache = {}
 
@@ -121,7 +124,8 @@ def error_flag(device) -> torch.Tensor:
 
 
 ERROR_TEXT = {1: "token id outside the vocabulary", 2: "cache write to an unmapped page",
-              3: "position beyond the rotary table", 4: "attention read from an unmapped page"}
+              3: "position beyond the rotary table", 4: "attention read from an unmapped page",
+              5: "a bounded wait inside a kernel ran out (copy or tensor-core completion never arrived)"}
 
 
 # ---------------------------------------------------------------------------------------
@@ -319,6 +323,13 @@ def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     _need(seq_start, "seq_start", torch.int32, (seqs + 1,))
     _need(seq_len, "seq_len", torch.int32, (seqs,))
     out = torch.empty_like(q)
+    if Dh in TCGEN05_HEAD_DIMS and not _NO_TCGEN05:
+        # head sizes of 64 and 128: the tcgen05 / tensor-memory kernel
+        _call("attention_prefill_tc", "ri_attention_prefill_tc", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+              out.data_ptr(), page_table.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seq_len.data_ptr(),
+              seqs, int(max_new), H, KV, Dh, page_table.shape[1], page_size, pages, float(scale), int(window),
+              error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
+        return out
     _call("attention_prefill", "ri_attention_prefill", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
           out.data_ptr(), page_table.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seq_len.data_ptr(),
           seqs, int(max_new), H, KV, Dh, page_table.shape[1], page_size, pages, float(scale), int(window),
