@@ -1,16 +1,17 @@
 // Prefill attention on the 5th-generation tensor cores (tcgen05) for bfloat16, head size 64 or 128.
 //
-// Grid (query tile, head, sequence); a tile is 128 consecutive new tokens of one
-// sequence, two threads per token (8 warps).  For every block of 128 keys the block
+// Grid (head, query tile, sequence); a tile is 128 consecutive new tokens of one
+// sequence, two threads per token (8 warps).  For every block of 64 keys the block
 //   1. brings the keys and values from the paged cache into shared memory in the
-//      128-byte-swizzled layout the tensor core reads (cp.async, double buffered);
-//   2. S = Q K^T: one thread issues tcgen05.mma (M 128 queries, N 128 keys), the
-//      accumulator lives in tensor memory (TMEM columns 0..127);
+//      128-byte-swizzled layout the tensor core reads (cp.async; the next block's keys
+//      are asked for as soon as S is done, its values as soon as O_blk is done);
+//   2. S = Q K^T: one thread issues tcgen05.mma (M 128 queries, N 64 keys), the
+//      accumulator lives in tensor memory (TMEM columns 0..63);
 //   3. every thread reads its own row of S from TMEM (tcgen05.ld), takes the online
 //      softmax in float32 (maximum, then exp2 and sum), and writes its row of P as
 //      bfloat16 into shared memory, again in the swizzled operand layout;
 //   4. O_blk = P V: tcgen05.mma with V read as an MN-major operand straight from the
-//      [key][element] tile (TMEM columns 128..), read back and added to the thread's
+//      [key][element] tile (TMEM columns 64..), read back and added to the thread's
 //      running output, rescaled by exp2(old maximum - new maximum).
 // Completion of the MMAs is signalled through tcgen05.commit on an mbarrier; every
 // wait is bounded and ends in an error code, not a hang.
@@ -34,16 +35,18 @@ static_assert(RI_HEAD_DIM == 64 || RI_HEAD_DIM == 128, "tcgen05 prefill attentio
 #define TC_PAGE 32
 #define TC_BM 128                       // queries per block
 #define TC_THREADS 256                  // two threads per query row
-#define TC_BN 128                       // keys per step
+#define TC_BN 64                        // keys per step
 #define TC_SLABS (TC_DH / 64)           // 64-element (128-byte) slabs along the head
-#define TC_SLAB_BYTES (128 * 128)       // 128 rows of 128 bytes
-#define TC_TILE_BYTES (TC_SLABS * TC_SLAB_BYTES)   // a [128 x Dh] operand tile
-#define TC_P_BYTES (2 * TC_SLAB_BYTES)             // P [128 x 128 keys]: two slabs
-#define TC_TMEM_COLS 256                // S: columns 0..127, O_blk: columns 128..128+Dh-1
+#define TC_Q_SLAB (TC_BM * 128)         // a slab of the query tile: 128 rows of 128 bytes
+#define TC_KV_SLAB (TC_BN * 128)        // a slab of a key or value tile: 64 rows of 128 bytes
+#define TC_Q_BYTES (TC_SLABS * TC_Q_SLAB)
+#define TC_KV_BYTES (TC_SLABS * TC_KV_SLAB)
+#define TC_P_BYTES (TC_BM * 128)        // P [128 x 64 keys]: one slab
+#define TC_TMEM_COLS 256                // S: columns 0..63, O_blk: columns 64..64+Dh-1
 #define TC_WAIT_LIMIT (1 << 20)
 
 // dynamic shared memory, 1024-byte aligned (swizzle atoms):
-//   q | k[2] | v[2] | p      then the small things
+//   q | k | v | p      then the small things
 struct TcTail {
     unsigned long long mma_bar;
     unsigned tmem_base;
@@ -51,19 +54,15 @@ struct TcTail {
     float rowmax[2][128];             // exchange between the two threads of a row
 };
 #define TC_OFF_Q 0
-#define TC_OFF_K (TC_OFF_Q + TC_TILE_BYTES)
-#define TC_OFF_V (TC_OFF_K + 2 * TC_TILE_BYTES)
-#define TC_OFF_P (TC_OFF_V + 2 * TC_TILE_BYTES)
+#define TC_OFF_K (TC_OFF_Q + TC_Q_BYTES)
+#define TC_OFF_V (TC_OFF_K + TC_KV_BYTES)
+#define TC_OFF_P (TC_OFF_V + TC_KV_BYTES)
 #define TC_OFF_TAIL (TC_OFF_P + TC_P_BYTES)
 #define TC_SMEM_BYTES (TC_OFF_TAIL + 1088 + 1024)   // + slack to align the base to 1024
 
-// byte offset of element (row, col) of a [128 x 64*slabs] bf16 tile in the swizzled layout:
-// slab = col / 64; inside a slab rows are 128 bytes apart and the 16-byte chunk c of a row
-// sits at chunk position c ^ (row % 8)
-__device__ __forceinline__ unsigned swz_off(int row, int col) {
-    int slab = col >> 6, c = (col & 63) >> 3;
-    return (unsigned)(slab * TC_SLAB_BYTES + row * 128 + ((c ^ (row & 7)) << 4) + ((col & 7) << 1));
-}
+// The swizzled operand layout: a tile is cut into slabs of 64 elements (128 bytes) along its rows;
+// inside a slab rows are 128 bytes apart and the 16-byte chunk c of a row sits at chunk position
+// c ^ (row % 8).  Tiles start on 1024-byte boundaries.
 
 // shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1
 __device__ __forceinline__ unsigned long long smem_desc(unsigned addr, unsigned lbo_bytes, unsigned sbo_bytes) {
@@ -119,23 +118,24 @@ __device__ __forceinline__ bool tc_mbar_wait(unsigned long long* bar, unsigned p
     return false;
 }
 
-// One row of a [128 x Dh] tile: thread t copies half a row (row t/2, half t%2) of keys or values from
-// the paged pool, or of the queries, into the swizzled layout; rows that are not `ok` are zero-filled.
-__device__ __forceinline__ void copy_half_row(unsigned char* tile, const bf16* src_row, bool ok) {
-    constexpr int HALF = TC_DH / 16;                    // 16-byte chunks in half a row
-    const int r = threadIdx.x >> 1, h = threadIdx.x & 1;
+// A piece of a row of a [rows x Dh] tile from global memory into the swizzled layout: `chunks`
+// 16-byte chunks starting at chunk `c0` of row `r`; `ok` false writes zeros.  `slab_bytes` is the
+// size of one 64-element slab of the tile (rows * 128).
+__device__ __forceinline__ void copy_row_piece(unsigned char* tile, int slab_bytes, int r, int c0, int chunks,
+                                               const bf16* src_row, bool ok) {
     unsigned char* dst_row = tile + r * 128;
-#pragma unroll
-    for (int j = 0; j < HALF; j++) {
-        int c = h * HALF + j;                           // chunk of the row, 0 .. Dh/8 - 1
-        int slab = c >> 3, cc = c & 7;
-        cp_async16(dst_row + slab * TC_SLAB_BYTES + ((cc ^ (r & 7)) << 4), src_row + c * 8, ok);
+    for (int j = 0; j < chunks; j++) {
+        int c = c0 + j;                                 // chunk of the row, 0 .. Dh/8 - 1
+        cp_async16(dst_row + (c >> 3) * slab_bytes + (((c & 7) ^ (r & 7)) << 4), src_row + c * 8, ok);
     }
 }
+// keys [key0, key0+64) of one kv head: thread t copies a quarter of row t/4
 __device__ __forceinline__ void load_kv_tile(unsigned char* tile, const bf16* __restrict__ pool,
                                              const int* __restrict__ table, int kvh, int KV, int num_pages, int key0,
                                              int len, int* err) {
-    const int key = key0 + (threadIdx.x >> 1);
+    constexpr int Q4 = TC_DH / 32;                      // chunks in a quarter row
+    const int r = threadIdx.x >> 2;
+    const int key = key0 + r;
     bool ok = key < len;
     size_t off = 0;
     if (ok) {
@@ -147,7 +147,7 @@ __device__ __forceinline__ void load_kv_tile(unsigned char* tile, const bf16* __
             off = (((size_t)page * KV + kvh) * TC_PAGE + key % TC_PAGE) * TC_DH;
         }
     }
-    copy_half_row(tile, pool + off, ok);
+    copy_row_piece(tile, TC_KV_SLAB, r, (threadIdx.x & 3) * Q4, Q4, pool + off, ok);
 }
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
@@ -156,8 +156,9 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 // 256 threads: thread t works on query row t % 128; threads t and t + 128 share a row, the first
-// takes keys 0..63 of a block and the first half of the output elements, the second the rest.
-__global__ void __launch_bounds__(TC_THREADS, 1)
+// takes keys 0..31 of a block and the first half of the output elements, the second the rest.
+// Two blocks fit on an SM: while one waits for the tensor core the other does its softmax.
+__global__ void __launch_bounds__(TC_THREADS, 2)
 attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool,
                             const bf16* __restrict__ v_pool, bf16* __restrict__ out,
                             const int* __restrict__ page_table, const int* __restrict__ seq_slot,
@@ -166,10 +167,12 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
     TcTail& tail = *reinterpret_cast<TcTail*>(smem + TC_OFF_TAIL);
-    const int b = blockIdx.z, h = blockIdx.y;
+    // blocks start in the order of blockIdx.x, then y: heads vary fastest, so the late tiles of all
+    // heads, which see the most keys, start first
+    const int b = blockIdx.z, h = blockIdx.x;
     const int t_begin = seq_start[b], n_new = seq_start[b + 1] - t_begin;
     const int tiles = (n_new + TC_BM - 1) / TC_BM;
-    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;        // late tiles see the most keys: start them first
+    const int tile = (int)gridDim.y - 1 - (int)blockIdx.y;
     if (tile >= tiles) return;
     const int len = seq_len[b];
     const int r_base = tile * TC_BM;
@@ -182,6 +185,8 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     const int tid = threadIdx.x, warp = tid >> 5;
     const int row = tid & (TC_BM - 1), half = tid >> 7;            // my query row, my half of keys / elements
     const int my_pos = pos_first + row;
+    unsigned char* k_tile = smem + TC_OFF_K;
+    unsigned char* v_tile = smem + TC_OFF_V;
 
     // ---- set-up: tensor memory, the MMA barrier --------------------------------------------------
     if (warp == 0) {
@@ -194,14 +199,16 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         tail.dead = 0;
     }
-    // ---- the tile's queries and the first key block -----------------------------------------------
+    // ---- copies in flight: group 1 = queries and the first keys, group 2 = the first values --------
     {
         const int r = tid >> 1;
         const bool ok = r < rows;
-        copy_half_row(smem + TC_OFF_Q, q + ((size_t)(t_begin + r_base + (ok ? r : 0)) * H + h) * TC_DH, ok);
+        copy_row_piece(smem + TC_OFF_Q, TC_Q_SLAB, r, (tid & 1) * (TC_DH / 16), TC_DH / 16,
+                       q + ((size_t)(t_begin + r_base + (ok ? r : 0)) * H + h) * TC_DH, ok);
     }
-    load_kv_tile(smem + TC_OFF_K, k_pool, table, kvh, KV, num_pages, kb_lo * TC_BN, len, err);
-    load_kv_tile(smem + TC_OFF_V, v_pool, table, kvh, KV, num_pages, kb_lo * TC_BN, len, err);
+    load_kv_tile(k_tile, k_pool, table, kvh, KV, num_pages, kb_lo * TC_BN, len, err);
+    cp_async_commit();
+    load_kv_tile(v_tile, v_pool, table, kvh, KV, num_pages, kb_lo * TC_BN, len, err);
     cp_async_commit();
     tc_fence_before();
     __syncthreads();
@@ -209,9 +216,11 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     const unsigned tmem = tail.tmem_base;
     const unsigned tmem_row = tmem + ((unsigned)((warp & 3) * 32) << 16);      // this warp's 32 lanes
     const unsigned q_addr = smem_u32(smem + TC_OFF_Q), p_addr = smem_u32(smem + TC_OFF_P);
+    const unsigned k_addr = smem_u32(k_tile), v_addr = smem_u32(v_tile);
     constexpr unsigned IDESC_QK = instr_desc(TC_BM, TC_BN, 0);
     constexpr unsigned IDESC_PV = instr_desc(TC_BM, TC_DH, 1);
     constexpr int OW = TC_DH / 2;                                  // output elements per thread
+    constexpr int SW = TC_BN / 2;                                  // scores per thread (32)
 
     float o[OW];
 #pragma unroll
@@ -221,42 +230,38 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     bool dead = false;
 
     for (int kb = kb_lo; kb <= kb_hi && !dead; kb++) {
-        const int buf = (kb - kb_lo) & 1;
-        unsigned char* k_tile = smem + TC_OFF_K + buf * TC_TILE_BYTES;
-        unsigned char* v_tile = smem + TC_OFF_V + buf * TC_TILE_BYTES;
-        if (kb < kb_hi) {
-            load_kv_tile(smem + TC_OFF_K + (buf ^ 1) * TC_TILE_BYTES, k_pool, table, kvh, KV, num_pages, (kb + 1) * TC_BN, len, err);
-            load_kv_tile(smem + TC_OFF_V + (buf ^ 1) * TC_TILE_BYTES, v_pool, table, kvh, KV, num_pages, (kb + 1) * TC_BN, len, err);
-        }
-        cp_async_commit();
-        cp_async_wait<1>();              // everything but the block just asked for has arrived
-        fence_async_smem();              // ... and is visible to the tensor core's reads
+        // the keys of this block have arrived (the values may still be on their way)
+        cp_async_wait<1>();
+        fence_async_smem();
         tc_fence_before();
         __syncthreads();
         // ---- S = Q K^T ---------------------------------------------------------------------------------
         if (tid == 0) {
             tc_fence_after();
-            const unsigned k_addr = smem_u32(k_tile);
 #pragma unroll
             for (int j = 0; j < TC_DH / 16; j++) {
-                unsigned off = (unsigned)((j >> 2) * TC_SLAB_BYTES + (j & 3) * 32);
-                umma_bf16(tmem, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + off, 16, 1024), IDESC_QK, j > 0);
+                unsigned qo = (unsigned)((j >> 2) * TC_Q_SLAB + (j & 3) * 32), ko = (unsigned)((j >> 2) * TC_KV_SLAB + (j & 3) * 32);
+                umma_bf16(tmem, smem_desc(q_addr + qo, 16, 1024), smem_desc(k_addr + ko, 16, 1024), IDESC_QK, j > 0);
             }
             umma_commit(&tail.mma_bar);
         }
         if (!tc_mbar_wait(&tail.mma_bar, phase)) { atomicExch(err, 5); tail.dead = 1; }
         phase ^= 1;
         tc_fence_after();
-        // ---- my 64 scores of the row: mask, maximum (shared with the row's other thread) --------------
-        const int k0 = kb * TC_BN + half * 64;                     // my first key
+        // the key tile is free: ask for the next block's keys (an empty group after the last block)
+#ifndef TC_DBG_NO_LOADS
+        if (kb < kb_hi) load_kv_tile(k_tile, k_pool, table, kvh, KV, num_pages, (kb + 1) * TC_BN, len, err);
+#endif
+        cp_async_commit();
+        // ---- my 32 scores of the row: mask, maximum (shared with the row's other thread) --------------
+        const int k0 = kb * TC_BN + half * SW;                     // my first key
         const bool edge = (kb * TC_BN + TC_BN - 1 > pos_first) || (window > 0 && kb * TC_BN < pos_last - window + 1);
-        float s[64];
-        tmem_ld32(tmem_row + half * 64, *reinterpret_cast<float(*)[32]>(&s[0]));
-        tmem_ld32(tmem_row + half * 64 + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+        float s[SW];
+        tmem_ld32(tmem_row + half * SW, s);
         float mx = -FLT_MAX;
         if (edge) {
 #pragma unroll
-            for (int i = 0; i < 64; i++) {
+            for (int i = 0; i < SW; i++) {
                 int key = k0 + i;
                 bool vis = key <= my_pos && (window <= 0 || key > my_pos - window);
                 s[i] = vis ? s[i] : -FLT_MAX;
@@ -264,7 +269,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < 64; i++) mx = fmaxf(mx, s[i]);
+            for (int i = 0; i < SW; i++) mx = fmaxf(mx, s[i]);
         }
         tail.rowmax[half][row] = mx;
         __syncthreads();
@@ -277,52 +282,64 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         // ---- P = exp2(S * scale - m) as bfloat16 into the operand layout; sum --------------------------
         {
             const float neg_m = (m == -FLT_MAX) ? 0.0f : -m;
-            unsigned char* p_row = smem + TC_OFF_P + half * TC_SLAB_BYTES + row * 128;
+            unsigned char* p_row = smem + TC_OFF_P + row * 128;
 #pragma unroll
-            for (int c = 0; c < 8; c++) {
+            for (int c = 0; c < SW / 8; c++) {
                 float p[8];
 #pragma unroll
                 for (int e = 0; e < 8; e++) {
                     float x = s[c * 8 + e];
+#ifdef TC_DBG_NO_EXP
+                    p[e] = (x == -FLT_MAX) ? 0.0f : fmaf(x, scale_log2, neg_m);
+#else
                     p[e] = (x == -FLT_MAX) ? 0.0f : ex2_approx(fmaf(x, scale_log2, neg_m));
+#endif
                     l += p[e];
                 }
-                *(uint4*)(p_row + ((c ^ (row & 7)) << 4)) =
+                const int chunk = half * (SW / 8) + c;             // 16-byte chunk of the 64-key row
+                *(uint4*)(p_row + ((chunk ^ (row & 7)) << 4)) =
                     make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
             }
         }
+        cp_async_wait<1>();              // the values of this block have arrived (the next keys may be on their way)
         fence_async_smem();
         tc_fence_before();
         __syncthreads();
         // ---- O_blk = P V --------------------------------------------------------------------------------
+#ifndef TC_DBG_NO_PV
         if (tid == 0) {
             tc_fence_after();
-            const unsigned v_addr = smem_u32(v_tile);
 #pragma unroll
             for (int j = 0; j < TC_BN / 16; j++) {
-                unsigned a_off = (unsigned)((j >> 2) * TC_SLAB_BYTES + (j & 3) * 32);     // 16 keys along P's K dim
-                unsigned b_off = (unsigned)(j * 16 * 128);                               // 16 key rows of V
-                umma_bf16(tmem + 128, smem_desc(p_addr + a_off, 16, 1024),
-                          smem_desc(v_addr + b_off, TC_SLAB_BYTES, 1024), IDESC_PV, j > 0);
+                umma_bf16(tmem + TC_BN, smem_desc(p_addr + j * 32, 16, 1024),
+                          smem_desc(v_addr + j * 16 * 128, TC_KV_SLAB, 1024), IDESC_PV, j > 0);
             }
             umma_commit(&tail.mma_bar);
         }
         if (!tc_mbar_wait(&tail.mma_bar, phase)) { atomicExch(err, 5); tail.dead = 1; }
         phase ^= 1;
         tc_fence_after();
+        // the value tile is free: ask for the next block's values
+#ifndef TC_DBG_NO_LOADS
+        if (kb < kb_hi) load_kv_tile(v_tile, v_pool, table, kvh, KV, num_pages, (kb + 1) * TC_BN, len, err);
+#endif
+        cp_async_commit();
 #pragma unroll
         for (int c = 0; c < OW / 32; c++) {
             float ob[32];
-            tmem_ld32(tmem_row + 128 + half * OW + c * 32, ob);
+            tmem_ld32(tmem_row + TC_BN + half * OW + c * 32, ob);
 #pragma unroll
             for (int i = 0; i < 32; i++) o[c * 32 + i] = fmaf(o[c * 32 + i], corr, ob[i]);
         }
-        tc_fence_before();
-        __syncthreads();                 // S, O_blk, P and this K/V buffer may be overwritten
+#else
+        cp_async_commit();
+#endif
         dead = tail.dead != 0;
+        // the next iteration's first barrier comes before anything of S, O_blk or P is overwritten
     }
     cp_async_wait<0>();
     // ---- out = O / l (l: both halves of the row) ---------------------------------------------------------
+    __syncthreads();
     tail.rowmax[half][row] = l;
     __syncthreads();
     l += tail.rowmax[half ^ 1][row];
@@ -369,7 +386,8 @@ extern "C" int ri_attention_prefill_tc(const void* q, const void* k_pool, const 
         if (e != cudaSuccess) RI_FAIL((int)e, "attention_prefill_tc: %s", cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid((max_new + TC_BM - 1) / TC_BM, H, seqs);
+    dim3 grid(H, (max_new + TC_BM - 1) / TC_BM, seqs);
+    RI_REQUIRE(grid.y <= 65535, "attention_prefill_tc: too many tokens in one sequence of a step");
     attention_prefill_tc_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, page_table, seq_slot, seq_start, seq_len,
         H, KV, mpps, num_pages, scale * 1.4426950408889634f, window, err_flag);
