@@ -233,3 +233,13 @@ def build_all(extra: Iterable[Tuple[str, Optional[Dict[str, object]]]] = ()) -> 
         else:
             reqs.append((n, None))
     prepare(reqs + list(extra))
+    # libraries of sources that have changed since are of no use to anyone: remove them
+    keep = {os.path.basename(library_path(n, _with_env_defines(d), os.path.join(HERE, "_build"))) for n, d in reqs}
+    built = os.path.join(HERE, "_build")
+    if os.path.isdir(built) and not os.environ.get("RUST_INFERENCE_B200_DEFINES"):
+        for fn in os.listdir(built):
+            if fn.endswith(".so") and fn not in keep:
+                try:
+                    os.unlink(os.path.join(built, fn))
+                except OSError:
+                    pass

@@ -201,7 +201,9 @@ extern "C" int ri_qk_norm_rope_append(const void* qkv, void* q_out, void* k_pool
                                       int tokens, int H, int KV, int Dh, int mpps, int page_size, int num_pages,
                                       int write_kv, int dtype, int* err_flag, cudaStream_t stream) {
     if (tokens == 0) return 0;
-    RI_REQUIRE(tokens > 0 && H > 0 && KV > 0 && Dh > 0, "qk_norm_rope_append: bad sizes");
+    // H or KV may be 0 (only queries, or only keys and values); without kv heads nothing is appended
+    RI_REQUIRE(tokens > 0 && H >= 0 && KV >= 0 && H + KV > 0 && Dh > 0, "qk_norm_rope_append: bad sizes");
+    if (KV == 0) write_kv = 0;
     RI_REQUIRE(Dh <= RK_MAX_DH, "qk_norm_rope_append: head_dim %d exceeds the limit %d", Dh, RK_MAX_DH);
     RI_REQUIRE(rot >= 0 && rot <= Dh && rot % 2 == 0, "qk_norm_rope_append: rotary_dim %d must be even and <= head_dim %d", rot, Dh);
     RI_REQUIRE(!rope_table || rot > 0, "qk_norm_rope_append: a rope table needs rotary_dim > 0");

@@ -222,11 +222,18 @@ def qk_norm_rope_append(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, he
     tokens = qkv.shape[0]
     if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
         raise KernelError(f"qkv has {qkv.shape[1]} columns, expected {(num_heads + 2 * num_kv_heads) * head_dim}")
-    pages, kvh, page_size, dh = k_pool.shape
-    if (kvh, dh) != (num_kv_heads, head_dim) or v_pool.shape != k_pool.shape:
-        raise KernelError(f"cache pools {tuple(k_pool.shape)} / {tuple(v_pool.shape)} do not fit {num_kv_heads} kv heads of {head_dim}")
-    _need(k_pool, "k_pool", qkv.dtype)
-    _need(v_pool, "v_pool", qkv.dtype)
+    if k_pool is None:                 # nothing is appended (write_kv False): any valid pointers will do
+        if write_kv:
+            raise KernelError("qk_norm_rope_append: appending needs the cache pools")
+        pages, page_size = 1, 1
+        k_pool = v_pool = qkv
+        page_table = tok_seq.view(1, -1) if page_table is None else page_table
+    else:
+        pages, kvh, page_size, dh = k_pool.shape
+        if (kvh, dh) != (num_kv_heads, head_dim) or v_pool.shape != k_pool.shape:
+            raise KernelError(f"cache pools {tuple(k_pool.shape)} / {tuple(v_pool.shape)} do not fit {num_kv_heads} kv heads of {head_dim}")
+        _need(k_pool, "k_pool", qkv.dtype)
+        _need(v_pool, "v_pool", qkv.dtype)
     _need(page_table, "page_table", torch.int32)
     for t, n in ((tok_seq, "tok_seq"), (tok_pos, "tok_pos"), (seq_slot, "seq_slot")):
         _need(t, n, torch.int32)

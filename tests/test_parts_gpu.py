@@ -243,3 +243,63 @@ def test_toy_architecture_registers_builds_and_steps(tmp_path):
         H.replay_inprocess(d, "float32", steps, out, device="cuda")
         rows = H.collect(steps, out, cfg.vocab_size)
         H.assert_rows_close(rows, want, "float32", f"toy {label}")
+
+
+# ---- a toy position encoding with a rule of its own (no cos/sin table), defined here -----------------------
+
+@dataclass(frozen=True)
+class GrowSpec:
+    rate: float
+    kind: str = "toy_grow"
+
+
+from rust_inference_b200.parts import PositionEncoding, register_position  # noqa: E402
+
+
+@register_position("toy_grow")
+class GrowPosition(PositionEncoding):
+    """q <- q * (1 + rate*pos), k <- k / (1 + rate*pos): scores then depend on both positions."""
+    graph_safe = True            # everything it uses reaches it through device tensors
+
+    def apply(self, q, k, ctx):
+        f = (1.0 + self.spec.rate * ctx.tok_pos.float())[:, None, None]
+        return (q.float() * f).to(q.dtype), (k.float() / f).to(k.dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_part_with_a_position_encoding_of_its_own(dtype):
+    from rust_inference_b200.cache import Cache
+    from rust_inference_b200.parts.base import StepContext
+    rng = np.random.default_rng(4)
+    D, Hh, KV, Dh, n, first = 48, 4, 2, 16, 70, 40
+    spec = AttentionSpec(hidden_size=D, num_heads=Hh, num_kv_heads=KV, head_dim=Dh, position=GrowSpec(rate=0.01),
+                         qk_norm=RMSNormSpec(size=Dh, eps=1e-6))
+    part = build_part("mixer", spec, env(dtype))
+    W = {"q_proj.weight": (Hh * Dh, D), "k_proj.weight": (KV * Dh, D), "v_proj.weight": (KV * Dh, D), "o_proj.weight": (D, Hh * Dh)}
+    W = {k: (rng.standard_normal(s) * 0.2).astype(np.float32) for k, s in W.items()}
+    if dtype == "bfloat16":
+        W = {k: plain.bf16_round(w) for k, w in W.items()}
+    G = {"q_norm.weight": (1 + 0.1 * rng.standard_normal(Dh)).astype(np.float32),
+         "k_norm.weight": (1 + 0.1 * rng.standard_normal(Dh)).astype(np.float32)}
+    part.load({**{k: dev(w, DT[dtype]) for k, w in W.items()}, **{k: dev(g) for k, g in G.items()}})
+    part.prepare(128)
+    cache = Cache([part.cache_request()], num_slots=2, num_pages=4, max_pages_per_seq=4, dtype=DT[dtype], device="cuda")
+    slot = cache.alloc_slot()
+    x = rng.standard_normal((n, D)).astype(np.float32)
+    x = plain.bf16_round(x) if dtype == "bfloat16" else x
+    outs = []
+    i32 = lambda a: dev(np.asarray(a), torch.int32)
+    for lo, hi in [(0, first)] + [(i, i + 1) for i in range(first, n)]:
+        cache.extend([(slot, hi - lo)])
+        cache.upload()
+        ctx = StepContext(tok_seq=i32(np.zeros(hi - lo)), tok_pos=i32(np.arange(lo, hi)), seq_slot=i32([slot]),
+                          seq_start=i32([0, hi - lo]), seq_len=i32([hi]), num_tokens=hi - lo, num_seqs=1,
+                          max_new=hi - lo, max_len=hi)
+        outs.append(part(dev(x[lo:hi], DT[dtype]), ctx, cache.layer(0)).float().cpu().numpy())
+    got = np.concatenate(outs)
+    f = (1.0 + 0.01 * np.arange(n))[:, None, None]
+    q = plain.rms_norm(plain.linear(x, W["q_proj.weight"]).reshape(n, Hh, Dh), G["q_norm.weight"], 1e-6) * f
+    k = plain.rms_norm(plain.linear(x, W["k_proj.weight"]).reshape(n, KV, Dh), G["k_norm.weight"], 1e-6) / f
+    v = plain.linear(x, W["v_proj.weight"]).reshape(n, KV, Dh)
+    want = plain.linear(plain.causal_attention(q, k, v).reshape(n, Hh * Dh), W["o_proj.weight"])
+    assert np.abs(got - want).max() <= (2e-5 if dtype == "float32" else 4e-2) * np.abs(want).max()
