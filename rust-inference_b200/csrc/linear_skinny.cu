@@ -1,52 +1,131 @@
 // y[M, N] = x[M, K] . W[N, K]^T in bfloat16 for a handful of tokens (M <= 16): the
 // decode-time linear, bound by reading W once from memory.
 //
-// A block owns 16 rows of W (16 outputs) and all of K; its eight warps each take an
-// eighth of K and stream their part of the 16 rows straight from global memory into
-// registers, 16 bytes per lane per load, several loads in flight.  The products run
-// on the tensor cores (mma.sync m16n8k16, W rows as the 16 MMA rows, tokens as the 8
-// columns).  No shared-memory staging of W is needed: within a group of 32 k the
-// order of the k index is permuted the same way for W and for x, which a dot product
-// does not notice, so that what a lane loads (8 consecutive k of one row) is exactly
-// its MMA fragment.  The eight partial sums are added in warp order in shared memory.
+// A block owns 16 rows of W (16 outputs) and all of K; its four warps each take a
+// quarter of K.  A warp streams its part of the 16 rows through a ring of two stages
+// in shared memory: per stage each of 16 lanes starts one bulk copy (cp.async.bulk,
+// 512 bytes of one row, completion counted on the stage's mbarrier), so 16 KB per
+// warp are in flight without holding a register, and three blocks share an SM.  The copies of the first stages are
+// started before the kernel waits for its predecessor (programmatic dependent
+// launch): W is never written, so they overlap the predecessor's tail.
 //
-// A token's result does not depend on M or on the other tokens.
-// Output is bfloat16 or float32 (the float32 accumulator, for the logits).
+// The products run on the tensor cores (mma.sync m16n8k16, W rows as the 16 MMA rows,
+// tokens as the 8 columns).  Within a group of 32 k the order of the k index is
+// permuted the same way for W and for x, which a dot product does not notice, so
+// that the 16 bytes a lane reads (8 consecutive k of one row) are exactly its MMA
+// fragment; rows sit 576 bytes apart in shared memory, which makes those reads free
+// of bank conflicts.  The warps' partial sums are added in warp order.
+//
+// A token's result does not depend on M or on the other tokens.  Output is bfloat16
+// or float32 (the float32 accumulator, for the logits).  Waits are bounded: if one
+// runs out the kernel sets the error word (5) and finishes.
 #include "common.cuh"
 #include "mma_helpers.cuh"
 
-#define SK_WARPS 8
+#ifndef SK_WARPS
+#define SK_WARPS 4
+#endif
 #define SK_ROWS 16
+#ifndef SK_STAGE_K
+#define SK_STAGE_K 256                       // k per stage
+#endif
+#define SK_GROUPS (SK_STAGE_K / 32)          // groups of 32 k in a stage
+#define SK_STAGE_BYTES (SK_STAGE_K * 2)      // bytes of a row in a stage
+#define SK_PITCH (SK_STAGE_BYTES + 64)       // rows 64 bytes apart modulo 128: no bank conflicts
+#ifndef SK_STAGES
+#define SK_STAGES 2
+#endif
+#ifndef SK_MIN_BLOCKS
+#define SK_MIN_BLOCKS 3
+#endif
+#define SK_WAIT_LIMIT (1 << 20)
 
-__device__ __forceinline__ uint4 ld_nc16(const void* p) {
+__device__ __forceinline__ uint4 ld_ca16(const void* p) { return __ldg((const uint4*)p); }
+__device__ __forceinline__ uint4 lds16(const void* p) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_u32(p)));
     return v;
 }
-__device__ __forceinline__ uint4 ld_ca16(const void* p) { return __ldg((const uint4*)p); }
+__device__ __forceinline__ void sk_mbar_init(unsigned long long* bar) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(bar)));
+}
+__device__ __forceinline__ void sk_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void sk_bulk_g2s(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool sk_wait(unsigned long long* bar, unsigned parity) {
+    unsigned a = smem_u32(bar);
+    for (int i = 0; i < SK_WAIT_LIMIT; i++) {
+        unsigned ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
 
-// NT: token tiles of 8 (1 or 2); U: groups of 32 k in flight per warp
-template <int NT, int U, typename OutT>
-__global__ void __launch_bounds__(32 * SK_WARPS)
-linear_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ y, int M, int N, int K) {
-    __shared__ float part[SK_WARPS][SK_ROWS][NT * 8 + 1];
+struct __align__(16) SkinnyWarpSmem {
+    unsigned char w[SK_STAGES][SK_ROWS][SK_PITCH];
+};
+struct __align__(16) SkinnySmem {
+    SkinnyWarpSmem warp[SK_WARPS];
+    unsigned long long bar[SK_WARPS][SK_STAGES];
+    float part[SK_WARPS][SK_ROWS][17];
+};
+
+// NT: token tiles of 8 (1 or 2)
+template <int NT, typename OutT>
+__global__ void __launch_bounds__(32 * SK_WARPS, SK_MIN_BLOCKS)
+linear_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ y, int M, int N, int K,
+                     int* __restrict__ err) {
+    extern __shared__ __align__(16) unsigned char sk_raw[];
+    SkinnySmem& sm = *reinterpret_cast<SkinnySmem*>(sk_raw);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int quad = lane >> 2, qc = lane & 3;
     const int n0 = blockIdx.x * SK_ROWS;
-    pdl_trigger_early();
-    pdl_wait();
-    const int steps = (K + 31) / 32;                        // groups of 32 k
-    const int s_lo = (int)((long long)steps * warp / SK_WARPS), s_hi = (int)((long long)steps * (warp + 1) / SK_WARPS);
-    // rows past N and tokens past M are computed on row 0 / token 0 and never written
-    const int rowA = n0 + quad, rowB = n0 + quad + 8;
-    const bf16* wA = w + (size_t)(rowA < N ? rowA : 0) * K + qc * 8;
-    const bf16* wB = w + (size_t)(rowB < N ? rowB : 0) * K + qc * 8;
+    const int rows_here = min(SK_ROWS, N - n0);
+    // this warp's share of K, in stages of 128 k
+    const int stages_total = (K + SK_STAGE_K - 1) / SK_STAGE_K;
+    const int st_lo = (int)((long long)stages_total * warp / SK_WARPS), st_hi = (int)((long long)stages_total * (warp + 1) / SK_WARPS);
+    const int my_stages = st_hi - st_lo;
+    SkinnyWarpSmem& ws = sm.warp[warp];
+    unsigned long long* bar = sm.bar[warp];
+
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < SK_STAGES; s++) sk_mbar_init(&bar[s]);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncwarp();
+
+    // start the copy of stage `i` (counted from this warp's first) into ring slot i % SK_STAGES
+    auto issue = [&](int i) {
+        const int slot = i % SK_STAGES;
+        const int k0 = (st_lo + i) * SK_STAGE_K;
+        const int kbytes = min(SK_STAGE_K, K - k0) * 2;                 // K is a multiple of 8: a multiple of 16 bytes
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // earlier reads and writes of the slot come first
+        if (lane == 0) sk_expect_tx(&bar[slot], (unsigned)(rows_here * kbytes));
+        __syncwarp();
+        if (lane < rows_here) {
+            sk_bulk_g2s(&ws.w[slot][lane][0], w + (size_t)(n0 + lane) * K + k0, (unsigned)kbytes, &bar[slot]);
+            // the tail of a partial stage is read as zeros
+            for (int bofs = kbytes; bofs < SK_STAGE_BYTES; bofs += 16) *(uint4*)&ws.w[slot][lane][bofs] = make_uint4(0, 0, 0, 0);
+        } else if (lane < SK_ROWS) {
+            for (int bofs = 0; bofs < SK_STAGE_BYTES; bofs += 16) *(uint4*)&ws.w[slot][lane][bofs] = make_uint4(0, 0, 0, 0);
+        }
+    };
+    const int prefill = my_stages < SK_STAGES ? my_stages : SK_STAGES;
+    for (int i = 0; i < prefill; i++) issue(i);       // W is read-only for every kernel: no need to wait first
+    pdl_wait();                                        // x comes from the kernel before
+
     const bf16* xr[NT];
 #pragma unroll
     for (int t = 0; t < NT; t++) {
         int tok = t * 8 + quad;
-        xr[t] = x + (size_t)(tok < M ? tok : 0) * K + qc * 8;
+        xr[t] = x + (size_t)(tok < M ? tok : 0) * K + qc * 8;          // tokens past M: token 0, never written
     }
     float acc[NT][4];
 #pragma unroll
@@ -54,78 +133,82 @@ linear_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, Out
 #pragma unroll
         for (int e = 0; e < 4; e++) acc[t][e] = 0.0f;
 
-    const int full = K / 32;                                 // groups in which every lane has its 8 k
-    const int s_full = s_hi < full ? s_hi : full;
-    int s = s_lo;
-    for (; s + U <= s_full; s += U) {                        // U groups in flight, no conditions
-        uint4 a[U], b[U], xv[U][NT];
+    bool dead = false;
+    for (int i = 0; i < my_stages; i++) {
+        const int slot = i % SK_STAGES;
+        const int k0 = (st_lo + i) * SK_STAGE_K;
+        // x for this stage (L1/L2), asked for before the wait
+        uint4 xv[SK_GROUPS][NT];
 #pragma unroll
-        for (int u = 0; u < U; u++) {
-            a[u] = ld_nc16(wA + (s + u) * 32);
-            b[u] = ld_nc16(wB + (s + u) * 32);
-#pragma unroll
-            for (int t = 0; t < NT; t++) xv[u][t] = ld_ca16(xr[t] + (s + u) * 32);
-        }
-#pragma unroll
-        for (int u = 0; u < U; u++)
+        for (int g = 0; g < SK_GROUPS; g++)
 #pragma unroll
             for (int t = 0; t < NT; t++) {
-                mma_bf16(acc[t], a[u].x, b[u].x, a[u].y, b[u].y, xv[u][t].x, xv[u][t].y);
-                mma_bf16(acc[t], a[u].z, b[u].z, a[u].w, b[u].w, xv[u][t].z, xv[u][t].w);
+                int k = k0 + g * 32 + qc * 8;
+                xv[g][t] = k < K ? ld_ca16(xr[t] + k0 + g * 32) : make_uint4(0, 0, 0, 0);
             }
-    }
-    for (; s < s_hi; s++) {                                  // what is left, one group at a time
-        const bool in = s * 32 + qc * 8 < K;                 // K is a multiple of 8: a lane's 8 k are whole or absent
-        const uint4 zero = make_uint4(0, 0, 0, 0);
-        uint4 a = in ? ld_nc16(wA + s * 32) : zero, b = in ? ld_nc16(wB + s * 32) : zero;
-#pragma unroll
-        for (int t = 0; t < NT; t++) {
-            uint4 xv = in ? ld_ca16(xr[t] + s * 32) : zero;
-            mma_bf16(acc[t], a.x, b.x, a.y, b.y, xv.x, xv.y);
-            mma_bf16(acc[t], a.z, b.z, a.w, b.w, xv.z, xv.w);
+        if (!dead && !sk_wait(&bar[slot], (unsigned)((i / SK_STAGES) & 1))) {
+            if (lane == 0) atomicExch(err, 5);
+            dead = true;
         }
+        __syncwarp();                                   // zero tails written by other lanes
+#pragma unroll
+        for (int g = 0; g < SK_GROUPS; g++) {
+            uint4 a = lds16(&ws.w[slot][quad][g * 64 + qc * 16]);
+            uint4 b = lds16(&ws.w[slot][quad + 8][g * 64 + qc * 16]);
+#pragma unroll
+            for (int t = 0; t < NT; t++) {
+                mma_bf16(acc[t], a.x, b.x, a.y, b.y, xv[g][t].x, xv[g][t].y);
+                mma_bf16(acc[t], a.z, b.z, a.w, b.w, xv[g][t].z, xv[g][t].w);
+            }
+        }
+        __syncwarp();                                   // every lane has read the slot
+        if (i + SK_STAGES < my_stages) issue(i + SK_STAGES);
     }
     pdl_trigger_late();
     // acc[t][0,1]: (row quad, tokens t*8 + 2qc, +1); acc[t][2,3]: (row quad+8, same tokens)
 #pragma unroll
     for (int t = 0; t < NT; t++)
 #pragma unroll
-        for (int e = 0; e < 4; e++) part[warp][quad + (e >> 1) * 8][t * 8 + qc * 2 + (e & 1)] = acc[t][e];
+        for (int e = 0; e < 4; e++) sm.part[warp][quad + (e >> 1) * 8][t * 8 + qc * 2 + (e & 1)] = acc[t][e];
     __syncthreads();
     for (int i = threadIdx.x; i < SK_ROWS * NT * 8; i += blockDim.x) {
         int tok = i / SK_ROWS, row = i % SK_ROWS;              // consecutive threads: consecutive outputs of one token
         if (tok >= M || n0 + row >= N) continue;
         float v = 0.0f;
 #pragma unroll
-        for (int wi = 0; wi < SK_WARPS; wi++) v += part[wi][row][tok];
+        for (int wi = 0; wi < SK_WARPS; wi++) v += sm.part[wi][row][tok];
         st_f(y + (size_t)tok * N + n0 + row, v);
     }
 }
 
-template <int NT, int U, typename OutT>
-static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, cudaStream_t stream) {
+template <int NT, typename OutT>
+static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, int* err, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<NT, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SkinnySmem));
+        if (e != cudaSuccess) RI_FAIL((int)e, "linear_skinny: %s", cudaGetErrorString(e));
+        configured = true;
+    }
     dim3 grid((N + SK_ROWS - 1) / SK_ROWS);
-    ri_launch_pdl(linear_skinny_kernel<NT, U, OutT>, grid, dim3(32 * SK_WARPS), 0, stream, (const bf16*)x, (const bf16*)w, (OutT*)y, M, N, K);
+    ri_launch_pdl(linear_skinny_kernel<NT, OutT>, grid, dim3(32 * SK_WARPS), sizeof(SkinnySmem), stream, (const bf16*)x,
+                  (const bf16*)w, (OutT*)y, M, N, K, err);
     return 0;
 }
 
 extern "C" int ri_linear_skinny_max_tokens() { return 16; }
 
 // out_f32: 0 = bfloat16 output, 1 = float32 output
-extern "C" int ri_linear_skinny(const void* x, const void* w, void* y, int M, int N, int K, int out_f32,
+extern "C" int ri_linear_skinny(const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int* err_flag,
                                 cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
     RI_REQUIRE(M > 0 && N > 0 && K > 0, "linear_skinny: bad sizes M=%d N=%d K=%d", M, N, K);
     RI_REQUIRE(M <= 16, "linear_skinny: at most 16 tokens, got %d", M);
     RI_REQUIRE(K % 8 == 0, "linear_skinny: K=%d must be a multiple of 8", K);
     RI_REQUIRE((((uintptr_t)x | (uintptr_t)w) & 15) == 0, "linear_skinny: x and w must be 16-byte aligned");
-    if (M <= 8) {
-        if (out_f32) launch_skinny<1, 8, float>(x, w, y, M, N, K, stream);
-        else launch_skinny<1, 8, bf16>(x, w, y, M, N, K, stream);
-    } else {
-        if (out_f32) launch_skinny<2, 4, float>(x, w, y, M, N, K, stream);
-        else launch_skinny<2, 4, bf16>(x, w, y, M, N, K, stream);
-    }
+    int rc;
+    if (M <= 8) rc = out_f32 ? launch_skinny<1, float>(x, w, y, M, N, K, err_flag, stream) : launch_skinny<1, bf16>(x, w, y, M, N, K, err_flag, stream);
+    else rc = out_f32 ? launch_skinny<2, float>(x, w, y, M, N, K, err_flag, stream) : launch_skinny<2, bf16>(x, w, y, M, N, K, err_flag, stream);
+    if (rc) return rc;
     RI_CHECK_LAUNCH("linear_skinny");
     return 0;
 }

@@ -32,7 +32,7 @@ _SIGNATURES = {
     ("sampling", "ri_argmax"): [_P, _L, _I, _I, _P, _P, _P, _P],
     ("sampling", "ri_mark_seen"): [_P, _L, _P, _P, _I, _I, _P],
     ("attention_decode", "ri_attention_decode"): [_P] * 9 + [_I] * 8 + [_F, _I, _P, _P],
-    ("linear_skinny", "ri_linear_skinny"): [_P, _P, _P, _I, _I, _I, _I, _P],
+    ("linear_skinny", "ri_linear_skinny"): [_P, _P, _P, _I, _I, _I, _I, _P, _P],
     ("attention_prefill_tc", "ri_attention_prefill_tc"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _P],
     ("attention_prefill", "ri_attention_prefill"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _P],
 }
@@ -203,7 +203,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         # a handful of tokens: the weight-streaming kernel of this package
         y = torch.empty((M, N), dtype=torch.float32 if out_dtype == torch.float32 else torch.bfloat16, device=x.device)
         _call("linear_skinny", "ri_linear_skinny", x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K,
-              1 if out_dtype == torch.float32 else 0, _stream())
+              1 if out_dtype == torch.float32 else 0, error_flag(x.device).data_ptr(), _stream())
         return y
     if out_dtype == torch.float32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
