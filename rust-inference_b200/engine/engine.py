@@ -54,6 +54,7 @@ class _Tables:
         self.dev = torch.empty(total, dtype=torch.int32, device=device)
         self.event = torch.cuda.Event() if self.pinned else None
         self.used = False
+        self.decode_constants = False
 
     def part(self, i: int, host: bool = False):
         lo, hi = int(self.offsets[i]), int(self.offsets[i + 1])
@@ -94,6 +95,7 @@ class Engine:
         model.prepare(self.cache.max_seq_len)
         self.use_graphs = use_graphs and self.device.type == "cuda" and model.graph_safe
         self._decode_tables = {}
+        self._other_tables = {}
         self._graphs = {}
         self._warm = set()
         self.graph_replays = 0
@@ -114,6 +116,9 @@ class Engine:
         if not entries:
             raise StepError("a step needs at least one sequence")
         V = self.model.spec.vocab_size
+        if all(len(e.tokens) == 1 and (e.want == "last" or (not isinstance(e.want, str) and list(e.want) == [0]))
+               for e in entries):
+            return self._step_one_token_each(entries, V)
         news, wants = [], []
         for e in entries:
             toks = np.asarray(e.tokens, dtype=np.int64).reshape(-1)
@@ -175,14 +180,71 @@ class Engine:
         self.cache.after_step(slots)
         return logits
 
+    def step_device_ids(self, slots: Sequence[int], ids: torch.Tensor) -> torch.Tensor:
+        """A decode step whose token ids are on the device already (int32 [len(slots)], as the
+        sampler left them): the host need not have seen them, so this step can be launched
+        while the ids of the step before are still on their way to the host."""
+        if ids.dtype != torch.int32 or ids.numel() != len(slots) or ids.device != self.device:
+            raise StepError("step_device_ids: ids must be int32 on the engine's device, one per slot")
+        return self._step_one_token_each(None, self.model.spec.vocab_size, slots=[int(s) for s in slots], ids_dev=ids)
+
+    def _step_one_token_each(self, entries, V, slots=None, ids_dev=None) -> torch.Tensor:
+        """The decode step: every sequence brings one token and wants its logits.  Same
+        result as the general path, with the host work cut to a few array writes."""
+        if ids_dev is None:
+            toks = [int(e.tokens[0]) for e in entries]
+            if min(toks) < 0 or max(toks) >= V:
+                raise StepError(f"token id outside the vocabulary of {V}")
+            slots = [int(e.slot) for e in entries]
+        else:
+            toks = 0                                      # filled in on the device below
+        B = len(slots)
+        before = self.cache.extend([(s, 1) for s in slots])
+        self.cache.upload()
+        tables = self._tables_for(B, B, B, self.use_graphs)
+        tables.wait_host_free()
+        h = tables.host_np
+        if not tables.decode_constants:
+            h[B:2 * B] = np.arange(B)                     # tok_seq
+            h[3 * B:4 * B] = np.arange(B)                 # want_rows
+            h[5 * B:6 * B + 1] = np.arange(B + 1)         # seq_start
+            tables.decode_constants = True
+        h[0:B] = toks
+        h[2 * B:3 * B] = before                           # tok_pos
+        h[4 * B:5 * B] = slots
+        after = [L + 1 for L in before]
+        h[6 * B + 1:7 * B + 1] = after                    # seq_len
+        tables.upload()
+        if ids_dev is not None:
+            tables.part(0).copy_(ids_dev)                 # device to device, after the upload in stream order
+        ctx = StepContext(
+            tok_seq=tables.part(1), tok_pos=tables.part(2), seq_slot=tables.part(4), seq_start=tables.part(5),
+            seq_len=tables.part(6), num_tokens=B, num_seqs=B, max_new=1, max_len=max(after),
+            host_seq_slot=tuple(slots), host_new=(1,) * B, host_len=tuple(after))
+        if self.use_graphs:
+            logits = self._decode_step(tables, ctx, tables.part(3))
+        else:
+            logits = self.model.forward(tables.part(0), ctx, self.cache, tables.part(3))
+        self.cache.after_step(slots)
+        return logits
+
     # ---- graphs for one-token steps ------------------------------------------------------------
     def _tables_for(self, T, B, W, graphable) -> _Tables:
+        """Tables are kept per shape: pinned host memory is slow to allocate, and a captured
+        step needs its tables at fixed addresses."""
         if graphable:
             t = self._decode_tables.get(B)
             if t is None:
                 t = self._decode_tables[B] = _Tables(T, B, W, self.device)
             return t
-        return _Tables(T, B, W, self.device)
+        key = (T, B, W)
+        t = self._other_tables.pop(key, None)
+        if t is None:
+            t = _Tables(T, B, W, self.device)
+            if len(self._other_tables) >= 32:
+                self._other_tables.pop(next(iter(self._other_tables)))
+        self._other_tables[key] = t                       # most recently used last
+        return t
 
     def _graph_key(self, ctx) -> tuple:
         return (ctx.num_seqs, ctx.len_bucket)

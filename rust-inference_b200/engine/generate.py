@@ -12,6 +12,8 @@ from __future__ import annotations
 
 import time
 from dataclasses import dataclass, field
+
+import torch
 from typing import Iterable, List, Optional, Sequence
 
 from ..sampling import Sampler, SamplingParams
@@ -42,6 +44,21 @@ class _Seq:
     slot: int
     prompt: Sequence[int]
     out: List[int] = field(default_factory=list)
+
+
+class _Pending:
+    """Sampled ids of a step on their way to the host (pinned buffer, event)."""
+
+    def __init__(self, ids, seqs):
+        self.ids, self.seqs = ids, seqs
+        self.host = torch.empty(ids.shape, dtype=ids.dtype, pin_memory=True)
+        self.host.copy_(ids, non_blocking=True)
+        self.event = torch.cuda.Event()
+        self.event.record()
+
+    def wait(self):
+        self.event.synchronize()
+        return self.host.tolist()
 
 
 def plan_batches(prompt_lens: Sequence[int], max_new_tokens: int, max_seqs: int, page_size: int, num_pages: int,
@@ -89,49 +106,96 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int = 64,
     batches = plan_batches([len(p) for p in prompts], max_new_tokens, cache.slots.num_slots, cache.page_size,
                            cache.num_pages, engine.max_seq_len, batch_size)
     stats = result.stats
+    pipelined = hasattr(engine, "step_device_ids") and engine.device.type == "cuda"
     for batch in batches:
         stats.batches += 1
         live = [_Seq(req, row, engine.new_sequence(), prompts[req]) for row, req in enumerate(batch)]
         sampler.begin_batch(batch, [prompts[r] for r in batch])
+
+        def finish(s, reason):
+            result.tokens[s.request] = s.out
+            result.finish_reasons[s.request] = reason
+            engine.release(s.slot)
+            s.slot = -1
+
+        def accept(s, t):
+            """Take the sampled token t for sequence s; True while s goes on."""
+            if not ignore_eos and t in stops:
+                finish(s, "stop")
+                return False
+            s.out.append(int(t))
+            if len(s.out) >= max_new_tokens:
+                finish(s, "length")
+                return False
+            if len(s.prompt) + len(s.out) > engine.max_seq_len:
+                finish(s, "cache")
+                return False
+            return True
+
+        def goes_on_after_one_more(s):
+            """Whether s, if its pending token is no stop token, will be fed that token."""
+            return len(s.out) + 1 < max_new_tokens and len(s.prompt) + len(s.out) + 1 <= engine.max_seq_len
+
         t0 = time.perf_counter()
         try:
             logits = engine.step([Entry(s.slot, s.prompt, "last") for s in live])
-            first = True
-            while True:
-                toks = sampler.sample(logits, [s.row for s in live])       # reads the ids back: a sync
-                now = time.perf_counter()
-                if first:
-                    stats.prefill_s += now - t0
-                    stats.prefill_tokens += sum(len(s.prompt) for s in live)
-                    first = False
-                else:
-                    stats.decode_s += now - t0
-                    stats.decode_steps += 1
-                    stats.decode_tokens += len(live)
-                t0 = now
-                staying = []
-                for s, t in zip(live, toks):
-                    reason = None
-                    if not ignore_eos and t in stops:
-                        reason = "stop"
+            if not pipelined:
+                # ---- plain loop: sample, read the ids, decide, feed ------------------------------------
+                first = True
+                while True:
+                    toks = sampler.sample(logits, [s.row for s in live])       # reads the ids back: a sync
+                    now = time.perf_counter()
+                    if first:
+                        stats.prefill_s += now - t0
+                        stats.prefill_tokens += sum(len(s.prompt) for s in live)
+                        first = False
                     else:
-                        s.out.append(int(t))
-                        if len(s.out) >= max_new_tokens:
-                            reason = "length"
-                        elif len(s.prompt) + len(s.out) > engine.max_seq_len:
-                            reason = "cache"
-                    if reason:
-                        result.tokens[s.request] = s.out
-                        result.finish_reasons[s.request] = reason
-                        engine.release(s.slot)
-                        s.slot = -1
+                        stats.decode_s += now - t0
+                        stats.decode_steps += 1
+                        stats.decode_tokens += len(live)
+                    t0 = now
+                    live = [s for s, t in zip(live, toks) if accept(s, t)]
+                    if not live:
+                        break
+                    sampler.note_tokens([s.row for s in live], [s.out[-1] for s in live])
+                    logits = engine.step([Entry(s.slot, [s.out[-1]], "last") for s in live])
+            else:
+                # ---- pipelined loop: the next step is fed from the device and launched before the
+                # host reads the ids of this one.  Which sequences end by a stop token is known one
+                # step late: such a sequence runs one step too many, whose token is thrown away.
+                seqs = live
+                handle = _Pending(sampler.sample_device(logits, [s.row for s in seqs]), seqs)
+                handle.event.synchronize()            # the prompt step is timed on its own
+                stats.prefill_s += time.perf_counter() - t0
+                stats.prefill_tokens += sum(len(s.prompt) for s in seqs)
+                t0 = time.perf_counter()
+                first = True
+                while handle is not None:
+                    cont = [s for s in handle.seqs if s.slot >= 0 and goes_on_after_one_more(s)]
+                    nxt = None
+                    if cont:
+                        ids = handle.ids
+                        if len(cont) != len(handle.seqs):
+                            where = {id(s): i for i, s in enumerate(handle.seqs)}
+                            idx = torch.tensor([where[id(s)] for s in cont], dtype=torch.int64, device=ids.device)
+                            ids = ids.index_select(0, idx)
+                        sampler.note_tokens([s.row for s in cont], ids)
+                        logits = engine.step_device_ids([s.slot for s in cont], ids)
+                        nxt = _Pending(sampler.sample_device(logits, [s.row for s in cont]), cont)
+                    toks = handle.wait()
+                    if first:
+                        first = False                 # the prompt step's ids: already counted
                     else:
-                        staying.append(s)
-                live = staying
-                if not live:
-                    break
-                sampler.note_tokens([s.row for s in live], [s.out[-1] for s in live])
-                logits = engine.step([Entry(s.slot, [s.out[-1]], "last") for s in live])
+                        now = time.perf_counter()
+                        stats.decode_s += now - t0
+                        stats.decode_steps += 1
+                        stats.decode_tokens += sum(1 for s in handle.seqs if s.slot >= 0)
+                        t0 = now
+                    for s, t in zip(handle.seqs, toks):
+                        if s.slot >= 0:               # else: it had ended, this was its step too many
+                            accept(s, t)
+                    handle = nxt
+                live = []
         finally:
             for s in live:
                 if s.slot >= 0:

@@ -107,19 +107,28 @@ class Sampler:
             self.seen = None
 
     def note_tokens(self, rows, tokens) -> None:
-        """Tokens that entered the context of ``rows`` (needed by the repetition penalty)."""
+        """Tokens that entered the context of ``rows`` (needed by the repetition penalty);
+        ``tokens`` may be a device tensor."""
         if self.seen is None or len(rows) == 0:
             return
         r = torch.as_tensor(np.asarray(rows, dtype=np.int32), device=self.device)
-        t = torch.as_tensor(np.asarray(tokens, dtype=np.int32), device=self.device)
+        if isinstance(tokens, torch.Tensor):
+            t = tokens.to(device=self.device, dtype=torch.int32).contiguous()
+        else:
+            t = torch.as_tensor(np.asarray(tokens, dtype=np.int32), device=self.device)
         ops.mark_seen(self.seen, r, t)
 
     def sample(self, logits: torch.Tensor, rows: Sequence[int]) -> List[int]:
-        """One token for each row of ``logits`` [len(rows), vocab]."""
+        """One token for each row of ``logits`` [len(rows), vocab], read back to the host."""
+        return self.sample_device(logits, rows).tolist()
+
+    def sample_device(self, logits: torch.Tensor, rows: Sequence[int]) -> torch.Tensor:
+        """The same, left on the device (int32 [len(rows)]): the next step can be fed from it
+        before the host has seen the ids."""
         p = self.params
         n = len(rows)
         if p.greedy and not self.uses_context:
-            return ops.argmax(logits).tolist()
+            return ops.argmax(logits)
         c = self._const
         contiguous = list(rows) == list(range(n))
         idx = None if contiguous else torch.as_tensor(np.asarray(rows, dtype=np.int64), device=self.device)
@@ -132,4 +141,4 @@ class Sampler:
         seen_rows = torch.as_tensor(np.asarray(rows, dtype=np.int32), device=self.device) if self.seen is not None else None
         out = ops.sample(logits, take(c["temperature"]), uniform, top_k=take(c["top_k"]), top_p=take(c["top_p"]),
                          penalty=take(c["penalty"]), seen=self.seen, seen_rows=seen_rows)
-        return out.tolist()
+        return out
