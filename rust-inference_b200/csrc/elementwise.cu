@@ -206,19 +206,23 @@ extern "C" int ri_add_rows(float* resid, const void* delta, long long n, int dty
 }
 
 // ---------------------------------------------------------------------------
-// out[m, i] = silu(gu[m, i]) * gu[m, inter + i],  silu(t) = t / (1 + exp(-t))
-// `gu` holds the gate and the up projection side by side: [m, 2*inter].
+// out[m, c] = silu(gate[m, c]) * up[m, c],  silu(t) = t / (1 + exp(-t))
+// `gu` [m, 2*inter] holds gate and up in alternating blocks of `block` channels:
+// gate of channel c at column (c / block) * 2 * block + c % block, up `block` columns further.
+// block = inter is "all gates, then all ups"; block = 8 is the layout the skinny linear's
+// fused epilogue wants (a block of 16 output rows = 8 gates and their 8 ups).
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, int block, size_t total) {
     pdl_trigger();
     pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     size_t m = i / inter;
     int c = (int)(i - m * inter);
-    float g = ld_f(gu + m * 2 * inter + c);
-    float u = ld_f(gu + m * 2 * inter + inter + c);
+    int gc = (c / block) * 2 * block + c % block;
+    float g = ld_f(gu + m * 2 * inter + gc);
+    float u = ld_f(gu + m * 2 * inter + gc + block);
     st_f(out + i, (g / (1.0f + expf(-g))) * u);
 }
 
@@ -249,7 +253,7 @@ struct Pack8<float> {
 };
 
 template <typename T>
-__global__ void silu_mul_vec8_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total8) {
+__global__ void silu_mul_vec8_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, int block, size_t total8) {
     pdl_trigger();
     pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -258,8 +262,9 @@ __global__ void silu_mul_vec8_kernel(const T* __restrict__ gu, T* __restrict__ o
     size_t m = i / per_row;
     int c = (int)(i - m * per_row) << 3;
     Pack8<T> g, u, o;
-    g.load(gu + m * 2 * inter + c);
-    u.load(gu + m * 2 * inter + inter + c);
+    const int gc = (c / block) * 2 * block + c % block;        // block is a multiple of 8: the 8 channels stay together
+    g.load(gu + m * 2 * inter + gc);
+    u.load(gu + m * 2 * inter + gc + block);
 #pragma unroll
     for (int j = 0; j < 4; j++) {
         float g0 = g.get(2 * j), g1 = g.get(2 * j + 1);
@@ -268,22 +273,23 @@ __global__ void silu_mul_vec8_kernel(const T* __restrict__ gu, T* __restrict__ o
     o.store(out + m * inter + c);
 }
 
-extern "C" int ri_silu_mul(const void* gu, void* out, int rows, int inter, int dtype, cudaStream_t stream) {
+extern "C" int ri_silu_mul(const void* gu, void* out, int rows, int inter, int block, int dtype, cudaStream_t stream) {
     if (rows == 0) return 0;
     RI_REQUIRE(rows > 0 && inter > 0, "silu_mul: bad sizes rows=%d inter=%d", rows, inter);
+    RI_REQUIRE(block > 0 && inter % block == 0, "silu_mul: %d channels are not whole blocks of %d", inter, block);
     size_t total = (size_t)rows * inter;
-    if (inter % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
+    if (block % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
         size_t total8 = total / 8;
         unsigned blocks8 = (unsigned)((total8 + 255) / 256);
-        if (dtype == RI_DTYPE_F32) ri_launch_pdl(silu_mul_vec8_kernel<float>, dim3(blocks8), dim3(256), 0, stream, (const float*)gu, (float*)out, inter, total8);
-        else if (dtype == RI_DTYPE_BF16) ri_launch_pdl(silu_mul_vec8_kernel<__nv_bfloat16>, dim3(blocks8), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total8);
+        if (dtype == RI_DTYPE_F32) ri_launch_pdl(silu_mul_vec8_kernel<float>, dim3(blocks8), dim3(256), 0, stream, (const float*)gu, (float*)out, inter, block, total8);
+        else if (dtype == RI_DTYPE_BF16) ri_launch_pdl(silu_mul_vec8_kernel<__nv_bfloat16>, dim3(blocks8), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, block, total8);
         else RI_FAIL(-1, "silu_mul: unknown dtype %d", dtype);
         RI_CHECK_LAUNCH("silu_mul");
         return 0;
     }
     unsigned blocks = (unsigned)((total + 255) / 256);
-    if (dtype == RI_DTYPE_F32) ri_launch_pdl(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)out, inter, total);
-    else if (dtype == RI_DTYPE_BF16) ri_launch_pdl(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total);
+    if (dtype == RI_DTYPE_F32) ri_launch_pdl(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)out, inter, block, total);
+    else if (dtype == RI_DTYPE_BF16) ri_launch_pdl(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, block, total);
     else RI_FAIL(-1, "silu_mul: unknown dtype %d", dtype);
     RI_CHECK_LAUNCH("silu_mul");
     return 0;

@@ -76,8 +76,9 @@ struct __align__(16) SkinnySmem {
     float part[SK_WARPS][SK_ROWS][17];
 };
 
-// NT: token tiles of 8 (1 or 2)
-template <int NT, typename OutT>
+// NT: token tiles of 8 (1 or 2).  SWIGLU: the 16 rows of a block are 8 gate rows followed by their 8 up rows;
+// the block writes silu(gate) * up, 8 outputs per token, into y [M, N/2].
+template <int NT, typename OutT, bool SWIGLU>
 __global__ void __launch_bounds__(32 * SK_WARPS, SK_MIN_BLOCKS)
 linear_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ y, int M, int N, int K,
                      int* __restrict__ err) {
@@ -171,6 +172,20 @@ linear_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, Out
 #pragma unroll
         for (int e = 0; e < 4; e++) sm.part[warp][quad + (e >> 1) * 8][t * 8 + qc * 2 + (e & 1)] = acc[t][e];
     __syncthreads();
+    if (SWIGLU) {
+        for (int i = threadIdx.x; i < 8 * NT * 8; i += blockDim.x) {
+            int tok = i / 8, r = i % 8;
+            if (tok >= M || n0 + 8 + r >= N) continue;
+            float g = 0.0f, u = 0.0f;
+#pragma unroll
+            for (int wi = 0; wi < SK_WARPS; wi++) {
+                g += sm.part[wi][r][tok];
+                u += sm.part[wi][r + 8][tok];
+            }
+            st_f(y + (size_t)tok * (N / 2) + n0 / 2 + r, (g / (1.0f + expf(-g))) * u);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < SK_ROWS * NT * 8; i += blockDim.x) {
         int tok = i / SK_ROWS, row = i % SK_ROWS;              // consecutive threads: consecutive outputs of one token
         if (tok >= M || n0 + row >= N) continue;
@@ -181,33 +196,40 @@ linear_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, Out
     }
 }
 
-template <int NT, typename OutT>
+template <int NT, typename OutT, bool SWIGLU>
 static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, int* err, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<NT, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SkinnySmem));
+        cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<NT, OutT, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SkinnySmem));
         if (e != cudaSuccess) RI_FAIL((int)e, "linear_skinny: %s", cudaGetErrorString(e));
         configured = true;
     }
     dim3 grid((N + SK_ROWS - 1) / SK_ROWS);
-    ri_launch_pdl(linear_skinny_kernel<NT, OutT>, grid, dim3(32 * SK_WARPS), sizeof(SkinnySmem), stream, (const bf16*)x,
+    ri_launch_pdl(linear_skinny_kernel<NT, OutT, SWIGLU>, grid, dim3(32 * SK_WARPS), sizeof(SkinnySmem), stream, (const bf16*)x,
                   (const bf16*)w, (OutT*)y, M, N, K, err);
     return 0;
 }
 
 extern "C" int ri_linear_skinny_max_tokens() { return 16; }
 
-// out_f32: 0 = bfloat16 output, 1 = float32 output
-extern "C" int ri_linear_skinny(const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int* err_flag,
-                                cudaStream_t stream) {
+// out_f32: 0 = bfloat16 output, 1 = float32 output.  swiglu: 1 = w holds gate and up rows in alternating
+// blocks of 8 and y [M, N/2] gets silu(gate) * up (bfloat16 only).
+extern "C" int ri_linear_skinny(const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int swiglu,
+                                int* err_flag, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
     RI_REQUIRE(M > 0 && N > 0 && K > 0, "linear_skinny: bad sizes M=%d N=%d K=%d", M, N, K);
     RI_REQUIRE(M <= 16, "linear_skinny: at most 16 tokens, got %d", M);
     RI_REQUIRE(K % 8 == 0, "linear_skinny: K=%d must be a multiple of 8", K);
     RI_REQUIRE((((uintptr_t)x | (uintptr_t)w) & 15) == 0, "linear_skinny: x and w must be 16-byte aligned");
     int rc;
-    if (M <= 8) rc = out_f32 ? launch_skinny<1, float>(x, w, y, M, N, K, err_flag, stream) : launch_skinny<1, bf16>(x, w, y, M, N, K, err_flag, stream);
-    else rc = out_f32 ? launch_skinny<2, float>(x, w, y, M, N, K, err_flag, stream) : launch_skinny<2, bf16>(x, w, y, M, N, K, err_flag, stream);
+    if (swiglu) {
+        RI_REQUIRE(!out_f32 && N % 16 == 0, "linear_skinny: the fused SiLU-gate epilogue needs bfloat16 output and N a multiple of 16 (N=%d)", N);
+        rc = M <= 8 ? launch_skinny<1, bf16, true>(x, w, y, M, N, K, err_flag, stream) : launch_skinny<2, bf16, true>(x, w, y, M, N, K, err_flag, stream);
+    } else if (M <= 8) {
+        rc = out_f32 ? launch_skinny<1, float, false>(x, w, y, M, N, K, err_flag, stream) : launch_skinny<1, bf16, false>(x, w, y, M, N, K, err_flag, stream);
+    } else {
+        rc = out_f32 ? launch_skinny<2, float, false>(x, w, y, M, N, K, err_flag, stream) : launch_skinny<2, bf16, false>(x, w, y, M, N, K, err_flag, stream);
+    }
     if (rc) return rc;
     RI_CHECK_LAUNCH("linear_skinny");
     return 0;

@@ -24,7 +24,7 @@ _SIGNATURES = {
     ("elementwise", "ri_embed_rows"): [_P, _P, _P, _I, _I, _I, _I, _P, _P],
     ("elementwise", "ri_rmsnorm"): [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _P],
     ("elementwise", "ri_add_rows"): [_P, _P, _L, _I, _P],
-    ("elementwise", "ri_silu_mul"): [_P, _P, _I, _I, _I, _P],
+    ("elementwise", "ri_silu_mul"): [_P, _P, _I, _I, _I, _I, _P],
     ("rope_kv", "ri_qk_norm_rope_append"): [_P] * 10 + [_F, _P, _I, _I] + [_I] * 9 + [_P, _P],
     ("attention_plain", "ri_attention_plain"): [_P] * 8 + [_I] * 7 + [_F, _I, _I, _P, _P],
     ("linear_f32", "ri_linear_f32"): [_P, _P, _P, _I, _I, _I, _P],
@@ -32,7 +32,7 @@ _SIGNATURES = {
     ("sampling", "ri_argmax"): [_P, _L, _I, _I, _P, _P, _P, _P],
     ("sampling", "ri_mark_seen"): [_P, _L, _P, _P, _I, _I, _P],
     ("attention_decode", "ri_attention_decode"): [_P] * 9 + [_I] * 8 + [_F, _I, _P, _P],
-    ("linear_skinny", "ri_linear_skinny"): [_P, _P, _P, _I, _I, _I, _I, _P, _P],
+    ("linear_skinny", "ri_linear_skinny"): [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     ("attention_prefill_tc", "ri_attention_prefill_tc"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _P],
     ("attention_prefill", "ri_attention_prefill"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _P],
 }
@@ -40,6 +40,9 @@ DECODE_CHUNK = 128          # keys per partial result of the decode attention ke
 MAX_FAST_HEAD_DIM = 256
 TCGEN05_HEAD_DIMS = (64, 128)   # head sizes the tcgen05 prefill attention kernel is built for
 _NO_TCGEN05 = __import__("os").environ.get("RUST_INFERENCE_B200_NO_TCGEN05") == "1"   # for comparisons
+# the skinny linear can apply the SiLU gate in its epilogue; at batch 8 of Qwen3-8B shapes that measured 1 % slower
+# than the separate kernel (which overlaps through dependent launch), so it is off unless asked for
+_FUSED_SWIGLU = __import__("os").environ.get("RUST_INFERENCE_B200_FUSED_SWIGLU") == "1"
 SKINNY_MAX_TOKENS = 16      # up to here the bfloat16 linear is this package's weight-streaming kernel
 _fn_cache = {}
 
@@ -168,15 +171,36 @@ def add_rows(resid: torch.Tensor, delta: torch.Tensor) -> None:
     _call("elementwise", "ri_add_rows", resid.data_ptr(), delta.data_ptr(), resid.numel(), _code(delta.dtype), _stream())
 
 
-def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
-    """silu(gate) * up for ``gate_up`` [rows, 2*inter] (gate first)."""
+def silu_mul(gate_up: torch.Tensor, block: Optional[int] = None) -> torch.Tensor:
+    """silu(gate) * up for ``gate_up`` [rows, 2*inter], in which gate and up columns alternate
+    in blocks of ``block`` channels (default: all gates, then all ups)."""
     _need(gate_up, "gate_up")
     rows, two = gate_up.shape
     if two % 2:
         raise KernelError("silu_mul: the last dimension must be even")
-    out = torch.empty((rows, two // 2), dtype=gate_up.dtype, device=gate_up.device)
-    _call("elementwise", "ri_silu_mul", gate_up.data_ptr(), out.data_ptr(), rows, two // 2, _code(gate_up.dtype), _stream())
+    inter = two // 2
+    block = inter if block is None else int(block)
+    out = torch.empty((rows, inter), dtype=gate_up.dtype, device=gate_up.device)
+    _call("elementwise", "ri_silu_mul", gate_up.data_ptr(), out.data_ptr(), rows, inter, block,
+          _code(gate_up.dtype), _stream())
     return out
+
+
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, block: int) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) for ``w_gate_up`` [2*inter, K] with gate and up rows alternating in
+    blocks of ``block``.  A handful of bfloat16 tokens with block 8 run as one kernel (the product's
+    epilogue applies the gate); otherwise the product and ``silu_mul`` run one after the other."""
+    M, K = x.shape
+    N = w_gate_up.shape[0]
+    if (x.dtype == torch.bfloat16 and M <= SKINNY_MAX_TOKENS and K % 8 == 0 and block == 8 and N % 16 == 0
+            and _FUSED_SWIGLU):
+        _need(x, "x")
+        _need(w_gate_up, "w_gate_up", x.dtype)
+        y = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+        _call("linear_skinny", "ri_linear_skinny", x.data_ptr(), w_gate_up.data_ptr(), y.data_ptr(), M, N, K, 0, 1,
+              error_flag(x.device).data_ptr(), _stream())
+        return y
+    return silu_mul(linear(x, w_gate_up), block)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -203,7 +227,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         # a handful of tokens: the weight-streaming kernel of this package
         y = torch.empty((M, N), dtype=torch.float32 if out_dtype == torch.float32 else torch.bfloat16, device=x.device)
         _call("linear_skinny", "ri_linear_skinny", x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K,
-              1 if out_dtype == torch.float32 else 0, error_flag(x.device).data_ptr(), _stream())
+              1 if out_dtype == torch.float32 else 0, 0, error_flag(x.device).data_ptr(), _stream())
         return y
     if out_dtype == torch.float32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)

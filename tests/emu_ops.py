@@ -12,7 +12,7 @@ import math
 import numpy as np
 import torch
 
-__all__ = ["embed", "rmsnorm", "add_rows", "silu_mul", "linear", "qk_norm_rope_append", "attention", "argmax",
+__all__ = ["embed", "rmsnorm", "add_rows", "silu_mul", "linear_swiglu", "linear", "qk_norm_rope_append", "attention", "argmax",
            "sample", "mark_seen"]
 
 
@@ -37,10 +37,17 @@ def add_rows(resid, delta):
     resid += delta.float()
 
 
-def silu_mul(gate_up):
-    inter = gate_up.shape[1] // 2
-    g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+def silu_mul(gate_up, block=None):
+    rows, two = gate_up.shape
+    inter = two // 2
+    block = block or inter
+    v = gate_up.float().view(rows, inter // block, 2, block)
+    g, u = v[:, :, 0, :].reshape(rows, inter), v[:, :, 1, :].reshape(rows, inter)
     return ((g / (1.0 + torch.exp(-g))) * u).to(gate_up.dtype)
+
+
+def linear_swiglu(x, w_gate_up, block):
+    return silu_mul(linear(x, w_gate_up), block)
 
 
 def linear(x, w, out_dtype=None):

@@ -74,6 +74,10 @@ def test_silu_mul(dtype):
     got = ops.silu_mul(dev(gu, DT[dtype]))
     g, u = gu[:, :88].astype(np.float64), gu[:, 88:].astype(np.float64)
     close(got, plain.silu(g) * u, ETOL[dtype], "silu_mul")
+    for block in (8, 11, 44):          # gate and up alternating in blocks
+        v = gu.reshape(7, 88 // block, 2, block).astype(np.float64)
+        want = plain.silu(v[:, :, 0]) * v[:, :, 1]
+        close(ops.silu_mul(dev(gu, DT[dtype]), block), want.reshape(7, 88), ETOL[dtype], f"silu_mul block {block}")
 
 
 @pytest.mark.parametrize("shape", [(1, 64, 64), (5, 37, 70), (64, 192, 96), (130, 257, 1000), (3, 1000, 24)])

@@ -49,15 +49,18 @@ def test_rope_part_table():
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_swiglu_part(dtype):
+@pytest.mark.parametrize("inter,tokens", [(104, 9), (100, 9), (104, 40), (2048, 3)])
+def test_swiglu_part(dtype, inter, tokens):
+    """Widths that are and are not multiples of 8 (gate/up interleaved or not), few tokens (the
+    fused kernel in bfloat16) and many (library product, then the gate kernel)."""
     rng = np.random.default_rng(1)
-    part = build_part("ffn", SwiGLUSpec(hidden_size=72, intermediate_size=104), env(dtype))
+    part = build_part("ffn", SwiGLUSpec(hidden_size=72, intermediate_size=inter), env(dtype))
     W = {n: (rng.standard_normal(s) * 0.1).astype(np.float32) for n, s in
-         (("gate_proj.weight", (104, 72)), ("up_proj.weight", (104, 72)), ("down_proj.weight", (72, 104)))}
+         (("gate_proj.weight", (inter, 72)), ("up_proj.weight", (inter, 72)), ("down_proj.weight", (72, inter)))}
     if dtype == "bfloat16":
         W = {n: plain.bf16_round(w) for n, w in W.items()}
     part.load({n: dev(w, DT[dtype]) for n, w in W.items()})
-    x = rng.standard_normal((9, 72)).astype(np.float32)
+    x = rng.standard_normal((tokens, 72)).astype(np.float32)
     x = plain.bf16_round(x) if dtype == "bfloat16" else x
     got = part(dev(x, DT[dtype]), None).float().cpu().numpy()
     want = plain.swiglu_mlp(x, {"m." + n: w for n, w in W.items()}, "m.")
