@@ -47,7 +47,6 @@ static_assert(RI_HEAD_DIM % 16 == 0 && RI_HEAD_DIM >= 16 && RI_HEAD_DIM <= 256, 
 #define AD_CPITCH (AD_DH + 4)                // floats per row of the combine area
 #define AD_MERGE_THREADS 128
 #define AD_MERGE_TILE 128                    // chunks whose weights are staged at a time
-#define AD_WAIT_LIMIT (1 << 22)
 
 struct __align__(16) DecodeSmem {
     bf16 v[AD_CHUNK][AD_PITCH];
@@ -77,17 +76,7 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, unsign
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
-// true when the phase with this parity has completed; gives up after AD_WAIT_LIMIT tries
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
-    unsigned a = smem_u32(bar);
-    for (int i = 0; i < AD_WAIT_LIMIT; i++) {
-        unsigned ok;
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(ok) : "r"(a), "r"(parity) : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) { return ri_mbar_wait(bar, parity); }
 
 __global__ void __launch_bounds__(32 * AD_WARPS)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,

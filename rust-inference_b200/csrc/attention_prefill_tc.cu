@@ -43,7 +43,6 @@ static_assert(RI_HEAD_DIM == 64 || RI_HEAD_DIM == 128, "tcgen05 prefill attentio
 #define TC_KV_BYTES (TC_SLABS * TC_KV_SLAB)
 #define TC_P_BYTES (TC_BM * 128)        // P [128 x 64 keys]: one slab
 #define TC_TMEM_COLS 256                // S: columns 0..63, O_blk: columns 64..64+Dh-1
-#define TC_WAIT_LIMIT (1 << 20)
 
 // dynamic shared memory, 1024-byte aligned (swizzle atoms):
 //   q | k | v | p      then the small things
@@ -107,16 +106,7 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
 #pragma unroll
     for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
 }
-__device__ __forceinline__ bool tc_mbar_wait(unsigned long long* bar, unsigned parity) {
-    unsigned a = smem_u32(bar);
-    for (int i = 0; i < TC_WAIT_LIMIT; i++) {
-        unsigned ok;
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(ok) : "r"(a), "r"(parity) : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
+__device__ __forceinline__ bool tc_mbar_wait(unsigned long long* bar, unsigned parity) { return ri_mbar_wait(bar, parity); }
 
 // A piece of a row of a [rows x Dh] tile from global memory into the swizzled layout: `chunks`
 // 16-byte chunks starting at chunk `c0` of row `r`; `ok` false writes zeros.  `slab_bytes` is the
@@ -249,9 +239,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         phase ^= 1;
         tc_fence_after();
         // the key tile is free: ask for the next block's keys (an empty group after the last block)
-#ifndef TC_DBG_NO_LOADS
         if (kb < kb_hi) load_kv_tile(k_tile, k_pool, table, kvh, KV, num_pages, (kb + 1) * TC_BN, len, err);
-#endif
         cp_async_commit();
         // ---- my 32 scores of the row: mask, maximum (shared with the row's other thread) --------------
         const int k0 = kb * TC_BN + half * SW;                     // my first key
@@ -289,11 +277,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
 #pragma unroll
                 for (int e = 0; e < 8; e++) {
                     float x = s[c * 8 + e];
-#ifdef TC_DBG_NO_EXP
-                    p[e] = (x == -FLT_MAX) ? 0.0f : fmaf(x, scale_log2, neg_m);
-#else
                     p[e] = (x == -FLT_MAX) ? 0.0f : ex2_approx(fmaf(x, scale_log2, neg_m));
-#endif
                     l += p[e];
                 }
                 const int chunk = half * (SW / 8) + c;             // 16-byte chunk of the 64-key row
@@ -306,7 +290,6 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         tc_fence_before();
         __syncthreads();
         // ---- O_blk = P V --------------------------------------------------------------------------------
-#ifndef TC_DBG_NO_PV
         if (tid == 0) {
             tc_fence_after();
 #pragma unroll
@@ -320,9 +303,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         phase ^= 1;
         tc_fence_after();
         // the value tile is free: ask for the next block's values
-#ifndef TC_DBG_NO_LOADS
         if (kb < kb_hi) load_kv_tile(v_tile, v_pool, table, kvh, KV, num_pages, (kb + 1) * TC_BN, len, err);
-#endif
         cp_async_commit();
 #pragma unroll
         for (int c = 0; c < OW / 32; c++) {
@@ -331,9 +312,6 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
 #pragma unroll
             for (int i = 0; i < 32; i++) o[c * 32 + i] = fmaf(o[c * 32 + i], corr, ob[i]);
         }
-#else
-        cp_async_commit();
-#endif
         dead = tail.dead != 0;
         // the next iteration's first barrier comes before anything of S, O_blk or P is overwritten
     }

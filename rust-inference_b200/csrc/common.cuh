@@ -81,6 +81,31 @@ static inline cudaError_t ri_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// ---- bounded wait on an mbarrier ---------------------------------------------------------------
+// True when the phase with this parity has completed.  Gives up after about four milliseconds
+// (a copy or a tensor-core batch takes microseconds), so that a mistake in the bookkeeping of a
+// kernel ends in an error code and a wrong result, never in a kernel that does not return.
+__device__ __forceinline__ unsigned long long ri_globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool ri_mbar_wait(unsigned long long* bar, unsigned parity) {
+    unsigned a = (unsigned)__cvta_generic_to_shared(bar);
+    unsigned long long start = 0;
+    for (int i = 0;; i++) {
+        unsigned ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((i & 63) == 63) {
+            unsigned long long now = ri_globaltimer();
+            if (start == 0) start = now;
+            else if (now - start > 4000000ull) return false;
+        }
+    }
+}
+
 __device__ __forceinline__ float ld_f(const float* p) { return *p; }
 __device__ __forceinline__ float ld_f(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 __device__ __forceinline__ void st_f(float* p, float v) { *p = v; }

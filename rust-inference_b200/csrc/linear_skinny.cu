@@ -38,7 +38,6 @@
 #ifndef SK_MIN_BLOCKS
 #define SK_MIN_BLOCKS 3
 #endif
-#define SK_WAIT_LIMIT (1 << 20)
 
 __device__ __forceinline__ uint4 ld_ca16(const void* p) { return __ldg((const uint4*)p); }
 __device__ __forceinline__ uint4 lds16(const void* p) {
@@ -56,16 +55,7 @@ __device__ __forceinline__ void sk_bulk_g2s(void* dst, const void* src, unsigned
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ bool sk_wait(unsigned long long* bar, unsigned parity) {
-    unsigned a = smem_u32(bar);
-    for (int i = 0; i < SK_WAIT_LIMIT; i++) {
-        unsigned ok;
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(ok) : "r"(a), "r"(parity) : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
+__device__ __forceinline__ bool sk_wait(unsigned long long* bar, unsigned parity) { return ri_mbar_wait(bar, parity); }
 
 struct __align__(16) SkinnyWarpSmem {
     unsigned char w[SK_STAGES][SK_ROWS][SK_PITCH];
@@ -172,7 +162,7 @@ linear_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, Out
 #pragma unroll
         for (int e = 0; e < 4; e++) sm.part[warp][quad + (e >> 1) * 8][t * 8 + qc * 2 + (e & 1)] = acc[t][e];
     __syncthreads();
-    if (SWIGLU) {
+    if constexpr (SWIGLU) {
         for (int i = threadIdx.x; i < 8 * NT * 8; i += blockDim.x) {
             int tok = i / 8, r = i % 8;
             if (tok >= M || n0 + 8 + r >= N) continue;
@@ -184,15 +174,15 @@ linear_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, Out
             }
             st_f(y + (size_t)tok * (N / 2) + n0 / 2 + r, (g / (1.0f + expf(-g))) * u);
         }
-        return;
-    }
-    for (int i = threadIdx.x; i < SK_ROWS * NT * 8; i += blockDim.x) {
-        int tok = i / SK_ROWS, row = i % SK_ROWS;              // consecutive threads: consecutive outputs of one token
-        if (tok >= M || n0 + row >= N) continue;
-        float v = 0.0f;
+    } else {
+        for (int i = threadIdx.x; i < SK_ROWS * NT * 8; i += blockDim.x) {
+            int tok = i / SK_ROWS, row = i % SK_ROWS;          // consecutive threads: consecutive outputs of one token
+            if (tok >= M || n0 + row >= N) continue;
+            float v = 0.0f;
 #pragma unroll
-        for (int wi = 0; wi < SK_WARPS; wi++) v += sm.part[wi][row][tok];
-        st_f(y + (size_t)tok * N + n0 + row, v);
+            for (int wi = 0; wi < SK_WARPS; wi++) v += sm.part[wi][row][tok];
+            st_f(y + (size_t)tok * N + n0 + row, v);
+        }
     }
 }
 

@@ -413,3 +413,27 @@ def test_attention_prefill_kernel(H, KV, Dh, window):
                                 dev(np.array([0, new[4]]), torch.int32), dev(np.array(lens[4:5]), torch.int32), new[4],
                                 1.0 / math.sqrt(Dh), window)
     assert torch.equal(one, out[starts[4]:starts[5]])
+
+
+@pytest.mark.parametrize("H,KV,Dh,window", [(8, 8, 64, 0), (16, 4, 128, 0), (6, 2, 32, 300)])
+def test_attention_decode_many_sequences(H, KV, Dh, window):
+    """Far more (sequence, kv head, chunk) items than blocks: every block of the persistent kernel
+    walks several items, with pages that hold no key for some of its warps in between."""
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(H + Dh)
+    lens = [int(n) for n in rng.integers(1, 1100, size=44)] + [1024, 1025, 33, 1]
+    table, slots, k, v, k_pool, v_pool = _fill_pools(rng, lens, KV, Dh, "bfloat16", scale=0.5)
+    q = rnd(rng, len(lens), H, Dh, dtype="bfloat16")
+    bt = torch.bfloat16
+    args = (dev(k_pool, bt), dev(v_pool, bt), dev(table, torch.int32), dev(slots, torch.int32),
+            dev(np.array(lens), torch.int32), 1.0 / math.sqrt(Dh), window)
+    out = ops.attention_decode(dev(q, bt), *args, max(lens))
+    torch.cuda.synchronize()
+    assert int(ops.error_flag("cuda").item()) == 0
+    for b in range(0, len(lens), 3):
+        n = lens[b]
+        qall = np.concatenate([np.zeros((n - 1, H, Dh)), q[b:b + 1].astype(np.float64)])
+        want = plain.causal_attention(qall, k[b].astype(np.float64), v[b].astype(np.float64), window=window)[n - 1:]
+        close(out[b:b + 1], want, 2e-2, f"decode attention, sequence {b} of length {n}")
+    again = ops.attention_decode(dev(q, bt), *args, 2048)           # another grid, the same bits
+    assert torch.equal(again, out)
