@@ -1,5 +1,8 @@
 // Decode attention over the paged cache for bfloat16: one new token per sequence,
-// the keys split into chunks of 128 (four pages), partial results merged afterwards.
+// the keys split into chunks, partial results merged afterwards.  Two kernels make the
+// partial results: the streaming kernel further down (groups of up to 16 query heads,
+// head sizes up to 128) and the one described here, which takes every other case, in
+// chunks of 128 keys (four pages).
 //
 // Grid (chunk, kv head, sequence), four warps.  Warp w owns page w of the chunk.
 //  * Values: each lane starts one bulk copy (cp.async.bulk, completion on an mbarrier)
@@ -30,6 +33,7 @@
 // Formula: thanhauco/rust-inference src/attention.rs:111-150.
 #include "common.cuh"
 #include "mma_helpers.cuh"
+#include <cuda.h>
 #include <float.h>
 
 #ifndef RI_HEAD_DIM
@@ -278,6 +282,387 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The streaming kernel, for groups of at most 16 query heads and head sizes of 64 and 128.
+//
+// One block per SM, ADS_WARPS warps, and every warp works alone: it walks the items (run of
+// pages, sequence, kv head) w, w + W, w + 2W, ... (W warps in the grid) and, inside an item,
+// the pages in rising order with the running maximum, sum and output of a flash decoder in
+// its registers, so nothing is combined across warps and the block never synchronises.
+// The keys and the values of a page are two tiles of a stream that runs through the warp's
+// own ring of ADS_SLOTS shared-memory slots: one lane starts a TMA tensor copy
+// (cp.async.bulk.tensor.2d, 128-byte swizzle, completion on the slot's mbarrier) per 64
+// head elements of the tile, the warp waits for the oldest tile, reads it with ldmatrix
+// (keys) or ldmatrix.trans (values) for mma.sync m16n8k16, and refills the slot with the
+// tile ADS_SLOTS ahead - which may belong to the warp's next item, so the copies never stop
+// between items.  A tile is one or two instructions to start, where a copy per row costs
+// the warp a loop over its lanes; the swizzle makes the ldmatrix reads free of bank
+// conflicts without padding.  With three slots of 8 KB for each of eight warps an SM has
+// 192 KB on its way at all times.
+//
+// An item is a run of `chunk_pages` pages (a multiple of four), chosen by the launcher from
+// the batch's size so that the items fill the grid's warps once (see ri_attention_decode).
+// Whatever that number is, the warp writes one partial result for every 128 keys (four
+// pages, starting afresh after each), in the layout of the kernel above, and the same merge
+// kernel adds them: the bits of a sequence's result do not depend on the batch it is in.
+//
+// The running maximum is only raised when a page's maximum exceeds it by more than 2^8
+// (the weights stay below 2^8, exact in float32 and as good as any in bfloat16), which
+// saves rescaling the output on most pages.
+// ---------------------------------------------------------------------------------------------
+#define ADS_OK (AD_DH == 64 || AD_DH == 128)
+#ifndef ADS_WARPS
+#define ADS_WARPS 8
+#endif
+#define ADS_BOXES ((AD_DH + 63) / 64)                  // copies per tile: 64 head elements (128 bytes) x 32 rows each
+#define ADS_BOX_BYTES (AD_PAGE * 128)
+#define ADS_SLOT_BYTES (ADS_BOXES * ADS_BOX_BYTES)
+#ifndef ADS_SLOTS
+#define ADS_SLOTS_RAW ((208 * 1024) / (ADS_WARPS * ADS_SLOT_BYTES))
+#define ADS_SLOTS (ADS_SLOTS_RAW > 6 ? 6 : ADS_SLOTS_RAW)
+#endif
+// a small batch has fewer items than the grid has warps: then fewer warps per block (four, or two), each with
+// a deeper ring, so that more of an item's tiles are on their way at once
+#define ADS_SLOTS_FOR(warps) ((208 * 1024) / ((warps) * ADS_SLOT_BYTES) > 12 ? 12 : (208 * 1024) / ((warps) * ADS_SLOT_BYTES))
+#define ADS_SMEM_BYTES(warps, slots) ((size_t)(warps) * (slots) * ADS_SLOT_BYTES + (size_t)(warps) * (slots) * 8 + 1024)
+#define ADS_LAZY 8.0f                                  // log2 of how far a page's maximum may exceed the running one
+
+// where a warp stands in its list of pages
+struct StreamCursor {
+    int item;          // index of the item, or >= n_items when the list is at its end
+    int b, kvh, chunk;
+    int len, first_key;
+    int p, p_end;      // the page (index within the sequence) and the end of the item's pages
+    int ids_base;      // lane l holds the pool index of page ids_base + l of the sequence
+    int id_lane;
+    int slot_row;      // the sequence's row of the page table
+};
+
+struct StreamArgs {
+    const int* page_table;
+    const int* seq_slot;
+    const int* seq_len;
+    int seqs, KV, mpps, num_pages, n_items, chunk_pages, window, stride;
+    int* err;
+};
+
+__device__ __forceinline__ void stream_load_ids(StreamCursor& c, const StreamArgs& a, int lane) {
+    c.ids_base = c.p;
+    int pg = c.p + lane;
+    int id = (pg < c.p_end) ? a.page_table[(size_t)c.slot_row * a.mpps + pg] : 0;
+    if (id < 0 || id >= a.num_pages) {
+        atomicExch(a.err, 4);
+        id = 0;
+    }
+    c.id_lane = id;
+}
+
+// moves to the first item at or after c.item that has a visible page; false at the end of the list.
+// IDS: the cursor is the one that copies, so it needs the pages' places in the pool.
+template <bool IDS>
+__device__ __forceinline__ bool stream_open(StreamCursor& c, const StreamArgs& a, int lane) {
+    for (; c.item < a.n_items; c.item += a.stride) {
+        c.kvh = c.item % a.KV;
+        int r = c.item / a.KV;
+        c.b = r % a.seqs;
+        c.chunk = r / a.seqs;
+        c.len = a.seq_len[c.b];
+        c.first_key = (a.window > 0 && c.len - a.window > 0) ? c.len - a.window : 0;
+        int p_lo = c.chunk * a.chunk_pages, p_hi = p_lo + a.chunk_pages;
+        int p_first = c.first_key / AD_PAGE, p_last = (c.len + AD_PAGE - 1) / AD_PAGE;
+        c.p = p_lo > p_first ? p_lo : p_first;
+        c.p_end = p_hi < p_last ? p_hi : p_last;
+        if (c.p < c.p_end) {
+            if (IDS) {
+                c.slot_row = a.seq_slot[c.b];
+                stream_load_ids(c, a, lane);
+            }
+            return true;
+        }
+    }
+    return false;
+}
+
+// the next page of the list; false at its end
+template <bool IDS>
+__device__ __forceinline__ bool stream_next(StreamCursor& c, const StreamArgs& a, int lane) {
+    if (++c.p < c.p_end) {
+        if (IDS && c.p - c.ids_base == 32) stream_load_ids(c, a, lane);
+        return true;
+    }
+    c.item += a.stride;
+    return stream_open<IDS>(c, a, lane);
+}
+
+// one box of a tensor map into shared memory: x in elements (a multiple of 64 here, so of 16 bytes), y the row
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+                 ::"r"(smem_u32(dst)), "l"((unsigned long long)map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+#if ADS_OK
+template <int WARPS, int SLOTS>
+__global__ void __launch_bounds__(32 * WARPS, 1)
+attention_decode_stream_kernel(const bf16* __restrict__ q, const __grid_constant__ CUtensorMap map_k,
+                               const __grid_constant__ CUtensorMap map_v, float* __restrict__ o_part,
+                               float* __restrict__ ml_part, StreamArgs a, int H, int max_chunks, float scale_log2) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int quad = lane >> 2, qc = lane & 3;
+    // the swizzle works on address bits 4..9: tiles start on multiples of 1024 bytes
+    unsigned char* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    unsigned char* ring = base + (size_t)warp * SLOTS * ADS_SLOT_BYTES;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(base + (size_t)WARPS * SLOTS * ADS_SLOT_BYTES)
+                               + warp * SLOTS;
+    const int G = H / a.KV;
+    if (lane == 0) {
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_v) : "memory");
+#pragma unroll
+        for (int s = 0; s < SLOTS; s++) mbar_init(&bars[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncwarp();
+
+    StreamCursor ci, cc;                  // the page whose tiles are copied next, the page that is worked on
+    ci.item = blockIdx.x + gridDim.x * warp;
+    bool more = stream_open<true>(ci, a, lane);
+    cc = ci;
+    bool live = more;
+    int issue_v = 0;                      // 0: the keys of ci's page come next, 1: its values
+    int in_flight = 0, slot_i = 0, slot_c = 0;
+    unsigned phases = 0;
+    bool dead = false;
+
+    // starts the copies of the next tile of the stream into slot `slot_i`
+    auto issue = [&]() {
+        const int id = __shfl_sync(0xffffffffu, ci.id_lane, ci.p - ci.ids_base);
+        if (lane == 0) {
+            unsigned char* dst = ring + (size_t)slot_i * ADS_SLOT_BYTES;
+            const int row = (id * a.KV + ci.kvh) * AD_PAGE;
+            mbar_expect_tx(&bars[slot_i], ADS_SLOT_BYTES);
+#pragma unroll
+            for (int x = 0; x < ADS_BOXES; x++)
+                tma_load_2d(dst + x * ADS_BOX_BYTES, issue_v ? &map_v : &map_k, x * 64, row, &bars[slot_i]);
+        }
+        slot_i = slot_i + 1 == SLOTS ? 0 : slot_i + 1;
+        in_flight++;
+        if (issue_v) more = stream_next<true>(ci, a, lane);
+        issue_v ^= 1;
+    };
+    auto wait_tile = [&]() {
+        if (!dead && !ri_mbar_wait(&bars[slot_c], (phases >> slot_c) & 1u)) {
+            if (lane == 0) atomicExch(a.err, 5);
+            dead = true;
+        }
+        phases ^= 1u << slot_c;
+    };
+    auto release_tile = [&]() {
+        __syncwarp();                     // every lane has read the tile
+        slot_c = slot_c + 1 == SLOTS ? 0 : slot_c + 1;
+        in_flight--;
+        if (more && !dead) issue();
+    };
+
+    // The kernel before this one wrote the queries and the newest key and value (the last page of each
+    // sequence); the pages before that one were written by earlier steps and may be copied at once.
+#pragma unroll 1
+    while (more && in_flight < SLOTS && (ci.p + 1) * AD_PAGE < ci.len) issue();
+    pdl_wait();
+#pragma unroll 1
+    while (more && in_flight < SLOTS) issue();
+
+    float m_run[2] = {-FLT_MAX, -FLT_MAX}, l_run[2] = {0.0f, 0.0f};
+    float o[AD_DH / 8][4];
+    unsigned qf[AD_DH / 16][4];
+    bool fresh = true, new_item = true;   // the next page is the first of a chunk of 128 keys, of an item
+    // this lane's corner of the 8x8 matrices that ldmatrix reads (rows of 128 bytes, 16-byte pieces swizzled by the row)
+    const int k_row = (lane & 7) + ((lane >> 4) & 1) * 8, k_piece = (lane >> 3) & 1;
+    const int v_row = (lane & 7) + ((lane >> 3) & 1) * 8, v_piece = lane >> 4;
+#pragma unroll 1
+    while (live) {
+        if (new_item) {
+            // ---- the item's query fragments: rows quad and quad + 8 of the group ---------------------------
+            const bf16* pa = q + ((size_t)cc.b * H + cc.kvh * G + (quad < G ? quad : 0)) * AD_DH + qc * 2;
+            const bf16* pb = q + ((size_t)cc.b * H + cc.kvh * G + (quad + 8 < G ? quad + 8 : 0)) * AD_DH + qc * 2;
+#pragma unroll
+            for (int ks = 0; ks < AD_DH / 16; ks++) {
+                qf[ks][0] = quad < G ? *(const unsigned*)(pa + ks * 16) : 0u;
+                qf[ks][1] = quad + 8 < G ? *(const unsigned*)(pb + ks * 16) : 0u;
+                qf[ks][2] = quad < G ? *(const unsigned*)(pa + ks * 16 + 8) : 0u;
+                qf[ks][3] = quad + 8 < G ? *(const unsigned*)(pb + ks * 16 + 8) : 0u;
+            }
+            new_item = false;
+        }
+        if (fresh) {
+#pragma unroll
+            for (int t = 0; t < AD_DH / 8; t++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) o[t][e] = 0.0f;
+            m_run[0] = m_run[1] = -FLT_MAX;
+            l_run[0] = l_run[1] = 0.0f;
+            fresh = false;
+        }
+        const int key0 = cc.p * AD_PAGE;
+        const int rows = min(AD_PAGE, cc.len - key0);
+        // ---- S[16 rows, 32 keys] = Q K^T ----------------------------------------------------------------
+        float s[4][4];
+#pragma unroll
+        for (int t = 0; t < 4; t++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) s[t][e] = 0.0f;
+        wait_tile();
+        {
+            const unsigned char* kt = ring + (size_t)slot_c * ADS_SLOT_BYTES + k_row * 128;
+#pragma unroll
+            for (int ks = 0; ks < AD_DH / 16; ks++) {
+                const unsigned char* kb = kt + (ks / 4) * ADS_BOX_BYTES + ((((ks * 2 + k_piece) & 7) ^ (lane & 7)) << 4);
+#pragma unroll
+                for (int tp = 0; tp < 2; tp++) {              // keys 16 tp .. 16 tp + 15
+                    unsigned b0, b1, b2, b3;
+                    ldmatrix_x4(b0, b1, b2, b3, kb + tp * 16 * 128);
+                    mma_bf16(s[tp * 2], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
+                    mma_bf16(s[tp * 2 + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
+                }
+            }
+        }
+        release_tile();
+        // ---- mask (only the pages at the ends of the visible range need it), maximum, weights ---------------
+        if (key0 < cc.first_key || rows < AD_PAGE) {
+#pragma unroll
+            for (int t = 0; t < 4; t++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    int key = key0 + t * 8 + qc * 2 + (e & 1);
+                    if (key >= cc.len || key < cc.first_key) s[t][e] = -FLT_MAX;
+                }
+        }
+        float mx[2] = {-FLT_MAX, -FLT_MAX};
+#pragma unroll
+        for (int t = 0; t < 4; t++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) mx[e >> 1] = fmaxf(mx[e >> 1], s[t][e]);
+        bool raise = false;
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            mx[r] = mx[r] == -FLT_MAX ? -FLT_MAX : mx[r] * scale_log2;      // the scale is positive
+            raise = raise || mx[r] > m_run[r] + ADS_LAZY || m_run[r] == -FLT_MAX;
+        }
+        if (__any_sync(0xffffffffu, raise)) {
+            // a row's maximum has moved far: every row takes its new maximum and the output is rescaled
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const float m_new = fmaxf(m_run[r], mx[r]);
+                const float corr = ex2_fast(m_run[r] - m_new);   // 1 while nothing has been seen (both are -FLT_MAX)
+                m_run[r] = m_new;
+                l_run[r] *= corr;
+#pragma unroll
+                for (int t = 0; t < AD_DH / 8; t++) {
+                    o[t][r * 2] *= corr;
+                    o[t][r * 2 + 1] *= corr;
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < 4; t++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                // a masked score is -FLT_MAX: its weight underflows to zero against any maximum of a visible key
+                float p = ex2_fast(fmaf(s[t][e], scale_log2, -m_run[e >> 1]));
+                s[t][e] = p;
+                l_run[e >> 1] += p;                       // this lane's columns; the quad is summed at the chunk's end
+            }
+        // ---- O[16, Dh] += P V ---------------------------------------------------------------------------
+        wait_tile();
+        {
+            unsigned char* vt = ring + (size_t)slot_c * ADS_SLOT_BYTES;
+            if (rows < AD_PAGE) {
+                // rows past the sequence's end hold whatever the pool holds there: zero them (0 x NaN is NaN)
+                if (lane >= rows)
+#pragma unroll
+                    for (int x = 0; x < ADS_BOXES; x++)
+#pragma unroll
+                        for (int c = 0; c < 8; c++) *(uint4*)(vt + x * ADS_BOX_BYTES + lane * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+                __syncwarp();
+            }
+            const unsigned char* vl = vt + v_row * 128;
+#pragma unroll
+            for (int kk = 0; kk < 2; kk++) {           // 16 keys at a time
+                unsigned a0 = pack_bf16(s[kk * 2][0], s[kk * 2][1]), a1 = pack_bf16(s[kk * 2][2], s[kk * 2][3]);
+                unsigned a2 = pack_bf16(s[kk * 2 + 1][0], s[kk * 2 + 1][1]), a3 = pack_bf16(s[kk * 2 + 1][2], s[kk * 2 + 1][3]);
+#pragma unroll
+                for (int dp = 0; dp < AD_DH / 16; dp++) {
+                    unsigned b0, b1, b2, b3;
+                    ldmatrix_x4_trans(b0, b1, b2, b3,
+                                      vl + kk * 16 * 128 + (dp / 4) * ADS_BOX_BYTES + ((((dp * 2 + v_piece) & 7) ^ (lane & 7)) << 4));
+                    mma_bf16(o[dp * 2], a0, a1, a2, a3, b0, b1);
+                    mma_bf16(o[dp * 2 + 1], a0, a1, a2, a3, b2, b3);
+                }
+            }
+            if (rows < AD_PAGE) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the zeros, before the next copy into the slot
+        }
+        release_tile();
+        // ---- the last page of a chunk of 128 keys: write the chunk's partial result ----------------------
+        const bool item_ends = cc.p + 1 == cc.p_end;
+        if (item_ends || (cc.p + 1) % (AD_CHUNK / AD_PAGE) == 0) {
+            const int chunk = cc.p / (AD_CHUNK / AD_PAGE);
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+                l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+                const int row = quad + r * 8;
+                if (row < G) {
+                    const size_t at = ((size_t)cc.b * H + cc.kvh * G + row) * max_chunks + chunk;
+                    float* dst = o_part + at * AD_DH + qc * 2;
+#pragma unroll
+                    for (int t = 0; t < AD_DH / 8; t++) *(float2*)(dst + t * 8) = make_float2(o[t][r * 2], o[t][r * 2 + 1]);
+                    if (qc == 0) *(float2*)(ml_part + at * 2) = make_float2(m_run[r], l_run[r]);
+                }
+            }
+            fresh = true;
+            new_item = item_ends;
+        }
+        live = stream_next<false>(cc, a, lane);
+        if (dead) break;
+    }
+    pdl_trigger();
+}
+
+// ---- tensor maps of the pools, made on the host -------------------------------------------------------
+typedef CUresult (*ri_encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                       CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// a pool [pages, KV, 32, Dh] of bfloat16 as a matrix [pages * KV * 32, Dh], copied in boxes of 32 rows x 64 elements
+static int pool_tensor_map(CUtensorMap* map, const void* pool, long long rows) {
+    static ri_encode_tiled_fn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &res);
+        if (e != cudaSuccess || res != cudaDriverEntryPointSuccess || !fn)
+            RI_FAIL(-1, "attention_decode: the driver has no cuTensorMapEncodeTiled");
+        encode = (ri_encode_tiled_fn)fn;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)AD_DH, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)AD_DH * 2};
+    cuuint32_t box[2] = {64, AD_PAGE};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) RI_FAIL(-1, "attention_decode: cuTensorMapEncodeTiled failed with %d", (int)r);
+    return 0;
+}
+#endif  // ADS_OK
+
 // out[b, h, :] = sum over the visible chunks, in rising order, of the partial results
 __global__ void __launch_bounds__(AD_MERGE_THREADS)
 attention_decode_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
@@ -351,6 +736,25 @@ static int decode_configure(int G, size_t* smem_out) {
     return 0;
 }
 
+#if ADS_OK
+template <int WARPS, int SLOTS>
+static int launch_stream(int blocks, cudaStream_t stream, const bf16* q, const CUtensorMap& map_k, const CUtensorMap& map_v,
+                         float* o_part, float* ml_part, StreamArgs a, int H, int max_chunks, float scale_log2) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_stream_kernel<WARPS, SLOTS>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ADS_SMEM_BYTES(WARPS, SLOTS));
+        if (e != cudaSuccess) RI_FAIL((int)e, "attention_decode: shared memory limit: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    a.stride = blocks * WARPS;
+    ri_launch_pdl(attention_decode_stream_kernel<WARPS, SLOTS>, dim3(blocks), dim3(32 * WARPS), ADS_SMEM_BYTES(WARPS, SLOTS),
+                  stream, q, map_k, map_v, o_part, ml_part, a, H, max_chunks, scale_log2);
+    RI_CHECK_LAUNCH("attention_decode_stream");
+    return 0;
+}
+#endif
+
 // q, out [seqs, H, Dh] bf16; o_part [seqs, H, max_chunks, Dh] f32; ml_part [seqs, H, max_chunks, 2] f32.
 // max_chunks * 128 must cover the longest sequence of the step.
 extern "C" int ri_attention_decode(const void* q, const void* k_pool, const void* v_pool, void* out, float* o_part,
@@ -364,6 +768,63 @@ extern "C" int ri_attention_decode(const void* q, const void* k_pool, const void
     RI_REQUIRE(max_chunks > 0 && seqs <= 65535 && KV <= 65535, "attention_decode: bad grid");
     RI_REQUIRE(window >= 0, "attention_decode: negative window");
     RI_REQUIRE((((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0, "attention_decode: q and the pools must be 16-byte aligned");
+#if ADS_OK && !defined(AD_NO_STREAM)
+    if (H / KV <= AD_ROWS && scale > 0.0f) {
+        static int sms = 0;
+        if (!sms) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (sms <= 0) sms = 148;
+        }
+        // Pages per item: the fewest (whole chunks of 128 keys) with which the items fill the grid's warps
+        // at most once; a batch too large for that takes items of 16 pages.
+        const int max_pages = max_chunks * (AD_CHUNK / AD_PAGE);
+        const long long workers = (long long)sms * ADS_WARPS;
+        int chunk_pages = 16;
+        for (int c = AD_CHUNK / AD_PAGE; c <= 32; c += AD_CHUNK / AD_PAGE) {
+            if ((long long)seqs * KV * ((max_pages + c - 1) / c) <= workers) {
+                chunk_pages = c;
+                break;
+            }
+        }
+        RI_REQUIRE((long long)num_pages * KV * AD_PAGE < (1ll << 31), "attention_decode: a pool of %d pages", num_pages);
+        CUtensorMap map_k, map_v;
+        int rc_map = pool_tensor_map(&map_k, k_pool, (long long)num_pages * KV * AD_PAGE);
+        if (rc_map) return rc_map;
+        rc_map = pool_tensor_map(&map_v, v_pool, (long long)num_pages * KV * AD_PAGE);
+        if (rc_map) return rc_map;
+        StreamArgs a;
+        a.page_table = page_table;
+        a.seq_slot = seq_slot;
+        a.seq_len = seq_len;
+        a.seqs = seqs;
+        a.KV = KV;
+        a.mpps = mpps;
+        a.num_pages = num_pages;
+        long long n_items = (long long)seqs * KV * ((max_pages + chunk_pages - 1) / chunk_pages);
+        RI_REQUIRE(n_items < (1ll << 30), "attention_decode: %lld items", n_items);
+        a.n_items = (int)n_items;
+        a.chunk_pages = chunk_pages;
+        a.window = window;
+        a.err = err_flag;
+        const long long smallest = (long long)seqs * KV * ((max_pages + 3) / 4);       // items of four pages
+        const int blocks = n_items < sms ? (int)n_items : sms;      // warp w of block x starts at item x + blocks * w
+        const float scale_log2 = scale * 1.4426950408889634f;
+        int rc;
+        if (smallest <= (long long)sms * 2)
+            rc = launch_stream<2, ADS_SLOTS_FOR(2)>(blocks, stream, (const bf16*)q, map_k, map_v, o_part, ml_part, a, H, max_chunks, scale_log2);
+        else if (smallest <= (long long)sms * 4)
+            rc = launch_stream<4, ADS_SLOTS_FOR(4)>(blocks, stream, (const bf16*)q, map_k, map_v, o_part, ml_part, a, H, max_chunks, scale_log2);
+        else
+            rc = launch_stream<ADS_WARPS, ADS_SLOTS>(blocks, stream, (const bf16*)q, map_k, map_v, o_part, ml_part, a, H, max_chunks, scale_log2);
+        if (rc) return rc;
+        ri_launch_pdl(attention_decode_merge_kernel, dim3(H, seqs), dim3(AD_MERGE_THREADS), 0, stream,
+                      (const float*)o_part, (const float*)ml_part, (bf16*)out, seq_len, H, max_chunks, window);
+        RI_CHECK_LAUNCH("attention_decode_merge");
+        return 0;
+    }
+#endif
     size_t smem = 0;
     int rc = decode_configure(H / KV, &smem);
     if (rc) return rc;

@@ -324,13 +324,15 @@ def test_sample_frequencies_and_top_p():
     assert (got == 0).all()
 
 
-def _fill_pools(rng, lens, KV, Dh, dtype, scale=1.0):
+def _fill_pools(rng, lens, KV, Dh, dtype, scale=1.0, junk_nan=False):
     P = 32
     table, slots, total = _paged(rng, lens, KV, Dh, P, dtype)
     k = [rnd(rng, n, KV, Dh, scale=scale, dtype=dtype) for n in lens]
     v = [rnd(rng, n, KV, Dh, dtype=dtype) for n in lens]
     k_pool = (rng.standard_normal((total, KV, P, Dh)) * 50).astype(np.float32)     # junk where nothing is stored:
     v_pool = (rng.standard_normal((total, KV, P, Dh)) * 50).astype(np.float32)     # a kernel that reads it is caught
+    if junk_nan:
+        k_pool[:], v_pool[:] = np.nan, np.nan
     for b, n in enumerate(lens):
         for j in range(n):
             pg = table[slots[b], j // P]
@@ -363,6 +365,27 @@ def test_attention_decode_kernel(H, KV, Dh, window):
                                dev(slots[8:9], torch.int32), dev(np.array(lens[8:9]), torch.int32),
                                1.0 / math.sqrt(Dh), window, 2048)
     assert torch.equal(one[0], out[8])
+
+
+@pytest.mark.parametrize("H,KV,Dh", [(8, 2, 128), (4, 4, 64), (6, 2, 32), (20, 1, 64)])
+def test_attention_decode_unwritten_rows_are_nan(H, KV, Dh):
+    """The rows of a sequence's last page past its end may hold anything, not-a-number included
+    (a weight of zero times that would still be not-a-number)."""
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(Dh)
+    lens = [1, 5, 31, 33, 64, 100, 129, 257]
+    table, slots, k, v, k_pool, v_pool = _fill_pools(rng, lens, KV, Dh, "bfloat16", scale=0.5, junk_nan=True)
+    q = rnd(rng, len(lens), H, Dh, dtype="bfloat16")
+    bt = torch.bfloat16
+    out = ops.attention_decode(dev(q, bt), dev(k_pool, bt), dev(v_pool, bt), dev(table, torch.int32),
+                               dev(slots, torch.int32), dev(np.array(lens), torch.int32), 1.0 / math.sqrt(Dh), 0,
+                               max(lens))
+    assert int(ops.error_flag("cuda").item()) == 0
+    assert bool(torch.isfinite(out.float()).all())
+    for b, n in enumerate(lens):
+        qall = np.concatenate([np.zeros((n - 1, H, Dh)), q[b:b + 1].astype(np.float64)])
+        want = plain.causal_attention(qall, k[b].astype(np.float64), v[b].astype(np.float64))[n - 1:]
+        close(out[b:b + 1], want, 2e-2, f"decode attention, length {n}")
 
 
 def test_attention_decode_far_key():
@@ -415,13 +438,16 @@ def test_attention_prefill_kernel(H, KV, Dh, window):
     assert torch.equal(one, out[starts[4]:starts[5]])
 
 
-@pytest.mark.parametrize("H,KV,Dh,window", [(8, 8, 64, 0), (16, 4, 128, 0), (6, 2, 32, 300)])
-def test_attention_decode_many_sequences(H, KV, Dh, window):
-    """Far more (sequence, kv head, chunk) items than blocks: every block of the persistent kernel
-    walks several items, with pages that hold no key for some of its warps in between."""
+@pytest.mark.parametrize("H,KV,Dh,window,seqs,longest", [(8, 8, 64, 0, 44, 1100), (16, 4, 128, 0, 44, 1100),
+                                                         (6, 2, 32, 300, 44, 1100), (12, 1, 128, 500, 44, 1100),
+                                                         (16, 8, 128, 0, 196, 200)])
+def test_attention_decode_many_sequences(H, KV, Dh, window, seqs, longest):
+    """Many (sequence, kv head, run of pages) items: the streaming kernel with eight and with four
+    warps per block, warps that walk several items one after another (more items than the grid
+    has warps), items that hold no key in between."""
     from rust_inference_b200 import ops
     rng = np.random.default_rng(H + Dh)
-    lens = [int(n) for n in rng.integers(1, 1100, size=44)] + [1024, 1025, 33, 1]
+    lens = [int(n) for n in rng.integers(1, longest, size=seqs)] + [longest - 76, longest - 75, 33, 1]
     table, slots, k, v, k_pool, v_pool = _fill_pools(rng, lens, KV, Dh, "bfloat16", scale=0.5)
     q = rnd(rng, len(lens), H, Dh, dtype="bfloat16")
     bt = torch.bfloat16
@@ -430,7 +456,7 @@ def test_attention_decode_many_sequences(H, KV, Dh, window):
     out = ops.attention_decode(dev(q, bt), *args, max(lens))
     torch.cuda.synchronize()
     assert int(ops.error_flag("cuda").item()) == 0
-    for b in range(0, len(lens), 3):
+    for b in range(0, len(lens), 3 if seqs < 100 else 11):
         n = lens[b]
         qall = np.concatenate([np.zeros((n - 1, H, Dh)), q[b:b + 1].astype(np.float64)])
         want = plain.causal_attention(qall, k[b].astype(np.float64), v[b].astype(np.float64), window=window)[n - 1:]
