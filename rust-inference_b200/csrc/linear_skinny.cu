@@ -3,24 +3,29 @@
 //
 // A block owns 16 rows of W (16 outputs) and all of K; its four warps each take a
 // quarter of K.  A warp streams its part of the 16 rows through a ring of two stages
-// in shared memory: per stage each of 16 lanes starts one bulk copy (cp.async.bulk,
-// 512 bytes of one row, completion counted on the stage's mbarrier), so 16 KB per
-// warp are in flight without holding a register, and three blocks share an SM.  The copies of the first stages are
-// started before the kernel waits for its predecessor (programmatic dependent
-// launch): W is never written, so they overlap the predecessor's tail.
+// of 256 k in shared memory: per stage one lane starts four TMA tensor copies
+// (cp.async.bulk.tensor.2d, boxes of 16 rows x 64 k with the 128-byte swizzle,
+// completion counted on the stage's mbarrier), so 16 KB per warp are in flight without
+// holding a register, and three blocks share an SM.  What a box holds beyond N or K is
+// filled with zeros by the copy.  The copies of the first stages are started before
+// the kernel waits for its predecessor (programmatic dependent launch): W is never
+// written, so they overlap the predecessor's tail.
 //
 // The products run on the tensor cores (mma.sync m16n8k16, W rows as the 16 MMA rows,
 // tokens as the 8 columns).  Within a group of 32 k the order of the k index is
 // permuted the same way for W and for x, which a dot product does not notice, so
 // that the 16 bytes a lane reads (8 consecutive k of one row) are exactly its MMA
-// fragment; rows sit 576 bytes apart in shared memory, which makes those reads free
-// of bank conflicts.  The warps' partial sums are added in warp order.
+// fragment.  MMA row r is W row rho(r) = (r >> 1) | ((r & 1) << 2) of its half of the
+// tile: with the swizzle that makes the eight lanes of a shared-memory transaction
+// read eight different 16-byte columns.  The warps' partial sums are added in warp
+// order.
 //
 // A token's result does not depend on M or on the other tokens.  Output is bfloat16
 // or float32 (the float32 accumulator, for the logits).  Waits are bounded: if one
 // runs out the kernel sets the error word (5) and finishes.
 #include "common.cuh"
 #include "mma_helpers.cuh"
+#include <cuda.h>
 
 #ifndef SK_WARPS
 #define SK_WARPS 4
@@ -30,8 +35,9 @@
 #define SK_STAGE_K 256                       // k per stage
 #endif
 #define SK_GROUPS (SK_STAGE_K / 32)          // groups of 32 k in a stage
-#define SK_STAGE_BYTES (SK_STAGE_K * 2)      // bytes of a row in a stage
-#define SK_PITCH (SK_STAGE_BYTES + 64)       // rows 64 bytes apart modulo 128: no bank conflicts
+#define SK_BOXES (SK_STAGE_K / 64)           // copies per stage: 16 rows x 64 k (128 bytes) each
+#define SK_BOX_BYTES (SK_ROWS * 128)
+#define SK_STAGE_TOTAL (SK_BOXES * SK_BOX_BYTES)
 #ifndef SK_STAGES
 #define SK_STAGES 2
 #endif
@@ -51,61 +57,55 @@ __device__ __forceinline__ void sk_mbar_init(unsigned long long* bar) {
 __device__ __forceinline__ void sk_expect_tx(unsigned long long* bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void sk_bulk_g2s(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+// one box of the tensor map into shared memory: x in elements (a multiple of 64 here, so of 16 bytes), y the row
+__device__ __forceinline__ void sk_tma_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+                 ::"r"(smem_u32(dst)), "l"((unsigned long long)map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool sk_wait(unsigned long long* bar, unsigned parity) { return ri_mbar_wait(bar, parity); }
 
-struct __align__(16) SkinnyWarpSmem {
-    unsigned char w[SK_STAGES][SK_ROWS][SK_PITCH];
-};
-struct __align__(16) SkinnySmem {
-    SkinnyWarpSmem warp[SK_WARPS];
+struct __align__(1024) SkinnySmem {
+    unsigned char w[SK_WARPS][SK_STAGES][SK_STAGE_TOTAL];      // boxes start on multiples of 1024 bytes (the swizzle's period)
     unsigned long long bar[SK_WARPS][SK_STAGES];
     float part[SK_WARPS][SK_ROWS][17];
 };
+#define SK_SMEM_BYTES (sizeof(SkinnySmem) + 1024)
 
 // NT: token tiles of 8 (1 or 2).  SWIGLU: the 16 rows of a block are 8 gate rows followed by their 8 up rows;
 // the block writes silu(gate) * up, 8 outputs per token, into y [M, N/2].
 template <int NT, typename OutT, bool SWIGLU>
 __global__ void __launch_bounds__(32 * SK_WARPS, SK_MIN_BLOCKS)
-linear_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ y, int M, int N, int K,
-                     int* __restrict__ err) {
+linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ y, int M, int N,
+                     int K, int* __restrict__ err) {
     extern __shared__ __align__(16) unsigned char sk_raw[];
-    SkinnySmem& sm = *reinterpret_cast<SkinnySmem*>(sk_raw);
+    SkinnySmem& sm = *reinterpret_cast<SkinnySmem*>(sk_raw + ((1024u - (smem_u32(sk_raw) & 1023u)) & 1023u));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int quad = lane >> 2, qc = lane & 3;
+    const int rho = (quad >> 1) | ((quad & 1) << 2);          // the W row (of 8) behind MMA row `quad`
     const int n0 = blockIdx.x * SK_ROWS;
-    const int rows_here = min(SK_ROWS, N - n0);
     // this warp's share of K, in stages of 128 k
     const int stages_total = (K + SK_STAGE_K - 1) / SK_STAGE_K;
     const int st_lo = (int)((long long)stages_total * warp / SK_WARPS), st_hi = (int)((long long)stages_total * (warp + 1) / SK_WARPS);
     const int my_stages = st_hi - st_lo;
-    SkinnyWarpSmem& ws = sm.warp[warp];
+    unsigned char (*ws)[SK_STAGE_TOTAL] = sm.w[warp];
     unsigned long long* bar = sm.bar[warp];
 
     if (lane == 0) {
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_w) : "memory");
 #pragma unroll
         for (int s = 0; s < SK_STAGES; s++) sk_mbar_init(&bar[s]);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncwarp();
 
-    // start the copy of stage `i` (counted from this warp's first) into ring slot i % SK_STAGES
+    // start the copies of stage `i` (counted from this warp's first) into ring slot i % SK_STAGES
     auto issue = [&](int i) {
-        const int slot = i % SK_STAGES;
-        const int k0 = (st_lo + i) * SK_STAGE_K;
-        const int kbytes = min(SK_STAGE_K, K - k0) * 2;                 // K is a multiple of 8: a multiple of 16 bytes
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // earlier reads and writes of the slot come first
-        if (lane == 0) sk_expect_tx(&bar[slot], (unsigned)(rows_here * kbytes));
-        __syncwarp();
-        if (lane < rows_here) {
-            sk_bulk_g2s(&ws.w[slot][lane][0], w + (size_t)(n0 + lane) * K + k0, (unsigned)kbytes, &bar[slot]);
-            // the tail of a partial stage is read as zeros
-            for (int bofs = kbytes; bofs < SK_STAGE_BYTES; bofs += 16) *(uint4*)&ws.w[slot][lane][bofs] = make_uint4(0, 0, 0, 0);
-        } else if (lane < SK_ROWS) {
-            for (int bofs = 0; bofs < SK_STAGE_BYTES; bofs += 16) *(uint4*)&ws.w[slot][lane][bofs] = make_uint4(0, 0, 0, 0);
+        if (lane == 0) {
+            const int slot = i % SK_STAGES;
+            const int k0 = (st_lo + i) * SK_STAGE_K;
+            sk_expect_tx(&bar[slot], SK_STAGE_TOTAL);
+#pragma unroll
+            for (int j = 0; j < SK_BOXES; j++) sk_tma_2d(&ws[slot][j * SK_BOX_BYTES], &map_w, k0 + j * 64, n0, &bar[slot]);
         }
     };
     const int prefill = my_stages < SK_STAGES ? my_stages : SK_STAGES;
@@ -141,11 +141,12 @@ linear_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, Out
             if (lane == 0) atomicExch(err, 5);
             dead = true;
         }
-        __syncwarp();                                   // zero tails written by other lanes
 #pragma unroll
         for (int g = 0; g < SK_GROUPS; g++) {
-            uint4 a = lds16(&ws.w[slot][quad][g * 64 + qc * 16]);
-            uint4 b = lds16(&ws.w[slot][quad + 8][g * 64 + qc * 16]);
+            // box g / 2, row rho (and rho + 8), 16-byte column (g % 2) * 4 + qc, swizzled by the row
+            const unsigned char* pw = &ws[slot][(g >> 1) * SK_BOX_BYTES + rho * 128 + (((((g & 1) << 2) | qc) ^ rho) << 4)];
+            uint4 a = lds16(pw);
+            uint4 b = lds16(pw + 8 * 128);
 #pragma unroll
             for (int t = 0; t < NT; t++) {
                 mma_bf16(acc[t], a.x, b.x, a.y, b.y, xv[g][t].x, xv[g][t].y);
@@ -156,11 +157,11 @@ linear_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, Out
         if (i + SK_STAGES < my_stages) issue(i + SK_STAGES);
     }
     pdl_trigger_late();
-    // acc[t][0,1]: (row quad, tokens t*8 + 2qc, +1); acc[t][2,3]: (row quad+8, same tokens)
+    // acc[t][0,1]: (W row rho, tokens t*8 + 2qc, +1); acc[t][2,3]: (W row rho + 8, same tokens)
 #pragma unroll
     for (int t = 0; t < NT; t++)
 #pragma unroll
-        for (int e = 0; e < 4; e++) sm.part[warp][quad + (e >> 1) * 8][t * 8 + qc * 2 + (e & 1)] = acc[t][e];
+        for (int e = 0; e < 4; e++) sm.part[warp][rho + (e >> 1) * 8][t * 8 + qc * 2 + (e & 1)] = acc[t][e];
     __syncthreads();
     if constexpr (SWIGLU) {
         for (int i = threadIdx.x; i < 8 * NT * 8; i += blockDim.x) {
@@ -186,17 +187,64 @@ linear_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, Out
     }
 }
 
+// ---- the tensor map of W, made on the host and kept for the next call with the same matrix --------------
+typedef CUresult (*sk_encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                       CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+struct SkMapEntry {
+    const void* w;
+    int N, K;
+    CUtensorMap map;
+};
+#define SK_MAP_CACHE 1024
+
+// W [N, K] bfloat16, row-major, copied in boxes of 16 rows x 64 k; out-of-range parts of a box read as zeros
+static int weight_tensor_map(const CUtensorMap** out, const void* w, int N, int K) {
+    static sk_encode_tiled_fn encode = nullptr;
+    static thread_local SkMapEntry cache[SK_MAP_CACHE];
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &res);
+        if (e != cudaSuccess || res != cudaDriverEntryPointSuccess || !fn)
+            RI_FAIL(-1, "linear_skinny: the driver has no cuTensorMapEncodeTiled");
+        encode = (sk_encode_tiled_fn)fn;
+    }
+    SkMapEntry& slot = cache[(((uintptr_t)w >> 8) ^ ((uintptr_t)w >> 20)) % SK_MAP_CACHE];
+    if (slot.w != w || slot.N != N || slot.K != K) {
+        cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)N};
+        cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+        cuuint32_t box[2] = {64, SK_ROWS};
+        cuuint32_t elem[2] = {1, 1};
+        CUresult r = encode(&slot.map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(w), dims, strides, box, elem,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            slot.w = nullptr;
+            RI_FAIL(-1, "linear_skinny: cuTensorMapEncodeTiled failed with %d (N=%d, K=%d)", (int)r, N, K);
+        }
+        slot.w = w;
+        slot.N = N;
+        slot.K = K;
+    }
+    *out = &slot.map;
+    return 0;
+}
+
 template <int NT, typename OutT, bool SWIGLU>
 static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, int* err, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<NT, OutT, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SkinnySmem));
+        cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<NT, OutT, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM_BYTES);
         if (e != cudaSuccess) RI_FAIL((int)e, "linear_skinny: %s", cudaGetErrorString(e));
         configured = true;
     }
+    const CUtensorMap* map = nullptr;
+    int rc = weight_tensor_map(&map, w, N, K);
+    if (rc) return rc;
     dim3 grid((N + SK_ROWS - 1) / SK_ROWS);
-    ri_launch_pdl(linear_skinny_kernel<NT, OutT, SWIGLU>, grid, dim3(32 * SK_WARPS), sizeof(SkinnySmem), stream, (const bf16*)x,
-                  (const bf16*)w, (OutT*)y, M, N, K, err);
+    ri_launch_pdl(linear_skinny_kernel<NT, OutT, SWIGLU>, grid, dim3(32 * SK_WARPS), SK_SMEM_BYTES, stream, (const bf16*)x,
+                  *map, (OutT*)y, M, N, K, err);
     return 0;
 }
 
