@@ -663,12 +663,17 @@ static int pool_tensor_map(CUtensorMap* map, const void* pool, long long rows) {
 }
 #endif  // ADS_OK
 
-// out[b, h, :] = sum over the visible chunks, in rising order, of the partial results
+// out[b, h, :] = the partial results of the visible chunks added up.  The block's four warps each take a
+// quarter of the chunks (in rising order, four head elements per lane), then the four sums are added in
+// warp order: the order of the additions depends on the sequence's length only.
 __global__ void __launch_bounds__(AD_MERGE_THREADS)
 attention_decode_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
                               bf16* __restrict__ out, const int* __restrict__ seq_len, int H, int max_chunks,
                               int window) {
+    constexpr int MW = AD_MERGE_THREADS / 32;            // warps
+    constexpr int PER = (AD_DH + 127) / 128;             // float4 per lane
     const int h = blockIdx.x, b = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     pdl_trigger();
     pdl_wait();
     const int len = seq_len[b];
@@ -676,47 +681,64 @@ attention_decode_merge_kernel(const float* __restrict__ o_part, const float* __r
     const int c_lo = first_key / AD_CHUNK, c_hi = (len + AD_CHUNK - 1) / AD_CHUNK;     // [c_lo, c_hi)
     const float* ml = ml_part + ((size_t)b * H + h) * max_chunks * 2;
     const float* op = o_part + ((size_t)b * H + h) * max_chunks * AD_DH;
-    __shared__ float s_w[AD_MERGE_TILE], s_lw[AD_MERGE_TILE], s_red[32];
+    __shared__ float s_w[AD_MERGE_TILE], s_red[MW], s_l[MW];
+    __shared__ __align__(16) float s_acc[MW][AD_DH];
     // the maximum over the visible chunks
     float M = -FLT_MAX;
-    for (int c = c_lo + (int)threadIdx.x; c < c_hi; c += blockDim.x) M = fmaxf(M, ml[c * 2]);
+    for (int c = c_lo + (int)threadIdx.x; c < c_hi; c += AD_MERGE_THREADS) M = fmaxf(M, ml[c * 2]);
     M = warp_max(M);
-    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = M;
+    if (lane == 0) s_red[warp] = M;
     __syncthreads();
     M = s_red[0];
-    for (int w = 1; w < (int)(blockDim.x >> 5); w++) M = fmaxf(M, s_red[w]);
-    // weights of a tile of chunks into shared memory, then sums in rising chunk order
-    constexpr int PER = (AD_DH + AD_MERGE_THREADS - 1) / AD_MERGE_THREADS;
-    float L = 0.0f;
-    float acc[PER];
 #pragma unroll
-    for (int j = 0; j < PER; j++) acc[j] = 0.0f;
+    for (int w = 1; w < MW; w++) M = fmaxf(M, s_red[w]);
+    float L = 0.0f;
+    float4 acc[PER];
+#pragma unroll
+    for (int j = 0; j < PER; j++) acc[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     for (int t0 = c_lo; t0 < c_hi; t0 += AD_MERGE_TILE) {
         const int n = min(AD_MERGE_TILE, c_hi - t0);
         __syncthreads();
-        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        for (int i = threadIdx.x; i < n; i += AD_MERGE_THREADS) {
             float m = ml[(t0 + i) * 2];
-            float w = m == -FLT_MAX ? 0.0f : exp2f(m - M);
-            s_w[i] = w;
-            s_lw[i] = ml[(t0 + i) * 2 + 1] * w;
+            s_w[i] = m == -FLT_MAX ? 0.0f : exp2f(m - M);
         }
         __syncthreads();
-        for (int i = 0; i < n; i++) L += s_lw[i];
+        // this warp's quarter of the tile
+        const int lo = n * warp / MW, hi = n * (warp + 1) / MW;
+        for (int i = lo + lane; i < hi; i += 32) L += ml[(t0 + i) * 2 + 1] * s_w[i];
+#pragma unroll 4
+        for (int i = lo; i < hi; i++) {
+            const float w = s_w[i];
 #pragma unroll
-        for (int j = 0; j < PER; j++) {
-            int d = threadIdx.x + j * AD_MERGE_THREADS;
-            if (d < AD_DH) {
-                float a = acc[j];
-#pragma unroll 8
-                for (int i = 0; i < n; i++) a += op[(size_t)(t0 + i) * AD_DH + d] * s_w[i];
-                acc[j] = a;
+            for (int j = 0; j < PER; j++) {
+                const int d = (j * 32 + lane) * 4;
+                if (d < AD_DH) {
+                    const float4 v = *(const float4*)(op + (size_t)(t0 + i) * AD_DH + d);
+                    acc[j].x = fmaf(v.x, w, acc[j].x);
+                    acc[j].y = fmaf(v.y, w, acc[j].y);
+                    acc[j].z = fmaf(v.z, w, acc[j].z);
+                    acc[j].w = fmaf(v.w, w, acc[j].w);
+                }
             }
         }
     }
+    L = warp_sum(L);
+    if (lane == 0) s_l[warp] = L;
 #pragma unroll
     for (int j = 0; j < PER; j++) {
-        int d = threadIdx.x + j * AD_MERGE_THREADS;
-        if (d < AD_DH) out[((size_t)b * H + h) * AD_DH + d] = __float2bfloat16_rn(acc[j] / L);
+        const int d = (j * 32 + lane) * 4;
+        if (d < AD_DH) *(float4*)&s_acc[warp][d] = acc[j];
+    }
+    __syncthreads();
+    L = s_l[0];
+#pragma unroll
+    for (int w = 1; w < MW; w++) L += s_l[w];
+    for (int d = threadIdx.x; d < AD_DH; d += AD_MERGE_THREADS) {
+        float a = s_acc[0][d];
+#pragma unroll
+        for (int w = 1; w < MW; w++) a += s_acc[w][d];
+        out[((size_t)b * H + h) * AD_DH + d] = __float2bfloat16_rn(a / L);
     }
 }
 

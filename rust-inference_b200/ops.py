@@ -40,9 +40,9 @@ DECODE_CHUNK = 128          # keys per partial result of the decode attention ke
 MAX_FAST_HEAD_DIM = 256
 TCGEN05_HEAD_DIMS = (64, 128)   # head sizes the tcgen05 prefill attention kernel is built for
 _NO_TCGEN05 = __import__("os").environ.get("RUST_INFERENCE_B200_NO_TCGEN05") == "1"   # for comparisons
-# the skinny linear can apply the SiLU gate in its epilogue; at batch 8 of Qwen3-8B shapes that measured 1 % slower
-# than the separate kernel (which overlaps through dependent launch), so it is off unless asked for
-_FUSED_SWIGLU = __import__("os").environ.get("RUST_INFERENCE_B200_FUSED_SWIGLU") == "1"
+# the skinny linear applies the SiLU gate in its epilogue (one kernel less per layer: 2 % faster at batch 1 of
+# Qwen3-8B shapes, 0.3 % at batch 8); RUST_INFERENCE_B200_FUSED_SWIGLU=0 takes the separate kernel, for comparisons
+_FUSED_SWIGLU = __import__("os").environ.get("RUST_INFERENCE_B200_FUSED_SWIGLU", "1") != "0"
 SKINNY_MAX_TOKENS = 16      # up to here the bfloat16 linear is this package's weight-streaming kernel
 _fn_cache = {}
 

@@ -109,6 +109,24 @@ def test_linear_bf16(shape):
         assert torch.equal(alone[0], full[M - 1])
 
 
+@pytest.mark.parametrize("shape", [(1, 32, 64), (5, 208, 520), (16, 4096, 1024), (9, 48, 72)])
+def test_linear_swiglu_fused(shape):
+    """The weight-streaming linear with the SiLU gate in its epilogue: gate and up rows interleaved
+    in blocks of 8, widths and depths that end inside a tile or a stage."""
+    from rust_inference_b200 import ops
+    M, N, K = shape                      # N rows of gate and up together
+    rng = np.random.default_rng(N)
+    x = rnd(rng, M, K, dtype="bfloat16")
+    gate, up = rnd(rng, N // 2, K, scale=0.2, dtype="bfloat16"), rnd(rng, N // 2, K, scale=0.2, dtype="bfloat16")
+    w = np.stack([gate.reshape(-1, 8, K), up.reshape(-1, 8, K)], axis=1).reshape(N, K)
+    got = ops.linear_swiglu(dev(x, torch.bfloat16), dev(w, torch.bfloat16), 8)
+    assert got.shape == (M, N // 2)
+    g, u = plain.linear(x, gate), plain.linear(x, up)
+    close(got, g / (1.0 + np.exp(-g)) * u, 5e-3, f"fused swiglu {shape}")
+    alone = ops.linear_swiglu(dev(x[M - 1:M], torch.bfloat16), dev(w, torch.bfloat16), 8)
+    assert torch.equal(alone[0], got[M - 1])
+
+
 def _paged(rng, lens, KV, Dh, P, dtype, extra_pages=3):
     """Random pools with a shuffled page table for sequences of the given lengths."""
     pages_per = [-(-n // P) for n in lens]
