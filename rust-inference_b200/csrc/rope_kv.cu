@@ -101,6 +101,7 @@ struct alignas(sizeof(T) * V) VecOf {
     T v[V];
 };
 
+#define RK_UNROLL 4
 template <typename T, int VEC>
 __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pool,
                                                T* __restrict__ v_pool, const int* __restrict__ page_table,
@@ -141,47 +142,59 @@ __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, T* __r
             cs_s[j] = (lane < 16) ? -c.y : c.y;                  // low half: a*c - b*s; high half: b*c + a*s
         }
     }
-    for (int h = blockIdx.y * RK_WARPS + warp; h < heads_total; h += RK_WARPS * gridDim.y) {
-        const int which = h < H ? 0 : (h < H + KV ? 1 : 2);
-        T* dst;
-        if (which == 0) {
-            dst = q_out + ((size_t)t * H + h) * Dh;
-        } else {
-            if (!write_kv || page < 0) continue;
-            const int kvh = which == 1 ? h - H : h - H - KV;
-            T* pool = which == 1 ? k_pool : v_pool;
-            dst = pool + (((size_t)page * KV + kvh) * page_size + pos % page_size) * Dh;
-        }
-        VecOf<T, VEC> in = *(const VecOf<T, VEC>*)(row + (size_t)h * Dh + d0);
-        if (which == 2) {
-            *(VecOf<T, VEC>*)(dst + d0) = in;
-            continue;
-        }
-        float x[VEC];
-        float ss = 0.0f;
+    // heads in batches of RK_UNROLL: all their loads are started before the first is worked on
+    const int stride = RK_WARPS * gridDim.y;
+    for (int h0 = blockIdx.y * RK_WARPS + warp; h0 < heads_total; h0 += stride * RK_UNROLL) {
+        VecOf<T, VEC> in[RK_UNROLL];
 #pragma unroll
-        for (int j = 0; j < VEC; j++) {
-            x[j] = ld_f(&in.v[j]);
-            ss += x[j] * x[j];
+        for (int u = 0; u < RK_UNROLL; u++) {
+            const int h = h0 + u * stride;
+            if (h < heads_total) in[u] = *(const VecOf<T, VEC>*)(row + (size_t)h * Dh + d0);
         }
-        const float* gain = which == 0 ? q_gain : k_gain;
-        if (gain) {
-            ss = warp_sum(ss);
-            const float inv = 1.0f / sqrtf(ss / (float)Dh + eps);
 #pragma unroll
-            for (int j = 0; j < VEC; j++) x[j] = x[j] * inv * gain[d0 + j];
-        }
-        VecOf<T, VEC> o;
-#pragma unroll
-        for (int j = 0; j < VEC; j++) {
-            float v = x[j];
-            if (rope) {
-                float other = __shfl_xor_sync(0xffffffffu, x[j], 16);
-                v = x[j] * cs_c[j] + other * cs_s[j];
+        for (int u = 0; u < RK_UNROLL; u++) {
+            const int h = h0 + u * stride;
+            if (h >= heads_total) break;
+            const int which = h < H ? 0 : (h < H + KV ? 1 : 2);
+            T* dst;
+            if (which == 0) {
+                dst = q_out + ((size_t)t * H + h) * Dh;
+            } else {
+                if (!write_kv || page < 0) continue;
+                const int kvh = which == 1 ? h - H : h - H - KV;
+                T* pool = which == 1 ? k_pool : v_pool;
+                dst = pool + (((size_t)page * KV + kvh) * page_size + pos % page_size) * Dh;
             }
-            st_f(&o.v[j], v);
+            if (which == 2) {
+                *(VecOf<T, VEC>*)(dst + d0) = in[u];
+                continue;
+            }
+            float x[VEC];
+            float ss = 0.0f;
+#pragma unroll
+            for (int j = 0; j < VEC; j++) {
+                x[j] = ld_f(&in[u].v[j]);
+                ss += x[j] * x[j];
+            }
+            const float* gain = which == 0 ? q_gain : k_gain;
+            if (gain) {
+                ss = warp_sum(ss);
+                const float inv = 1.0f / sqrtf(ss / (float)Dh + eps);
+#pragma unroll
+                for (int j = 0; j < VEC; j++) x[j] = x[j] * inv * gain[d0 + j];
+            }
+            VecOf<T, VEC> o;
+#pragma unroll
+            for (int j = 0; j < VEC; j++) {
+                float v = x[j];
+                if (rope) {
+                    float other = __shfl_xor_sync(0xffffffffu, x[j], 16);
+                    v = x[j] * cs_c[j] + other * cs_s[j];
+                }
+                st_f(&o.v[j], v);
+            }
+            *(VecOf<T, VEC>*)(dst + d0) = o;
         }
-        *(VecOf<T, VEC>*)(dst + d0) = o;
     }
 }
 
