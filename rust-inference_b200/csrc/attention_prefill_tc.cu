@@ -1,20 +1,25 @@
 // Prefill attention on the 5th-generation tensor cores (tcgen05) for bfloat16, head size 64 or 128.
 //
 // Grid (head, query tile, sequence); a tile is 128 consecutive new tokens of one
-// sequence, two threads per token (8 warps).  For every block of 64 keys the block
-//   1. brings the keys and values from the paged cache into shared memory in the
-//      128-byte-swizzled layout the tensor core reads (cp.async; the next block's keys
-//      are asked for as soon as S is done, its values as soon as O_blk is done);
+// sequence, two threads per token (8 warps), two blocks per SM.  For every block of
+// 64 keys
+//   1. one thread starts TMA tensor copies (cp.async.bulk.tensor.2d, 128-byte swizzle:
+//      the layout the tensor core reads) of the two pages of keys and of values from
+//      the paged cache; the next block's keys are asked for as soon as S is done, its
+//      values go into the second value buffer while this block is worked on;
 //   2. S = Q K^T: one thread issues tcgen05.mma (M 128 queries, N 64 keys), the
 //      accumulator lives in tensor memory (TMEM columns 0..63);
-//   3. every thread reads its own row of S from TMEM (tcgen05.ld), takes the online
-//      softmax in float32 (maximum, then exp2 and sum), and writes its row of P as
-//      bfloat16 into shared memory, again in the swizzled operand layout;
-//   4. O_blk = P V: tcgen05.mma with V read as an MN-major operand straight from the
-//      [key][element] tile (TMEM columns 64..), read back and added to the thread's
-//      running output, rescaled by exp2(old maximum - new maximum).
-// Completion of the MMAs is signalled through tcgen05.commit on an mbarrier; every
-// wait is bounded and ends in an error code, not a hang.
+//   3. every thread reads its half row of S from TMEM (tcgen05.ld), and writes its
+//      part of P = exp2(S * scale - m) as bfloat16 into shared memory in the operand
+//      layout.  m is the row's running maximum, raised only when some row of the tile
+//      meets a score more than 2^8 above its own (then every row takes its true
+//      maximum and rescales its output in TMEM with tcgen05.ld / tcgen05.st); weights
+//      up to 2^8 are exact in float32 and as good as any in bfloat16;
+//   4. O += P V: tcgen05.mma with V read as an MN-major operand straight from the
+//      [key][element] tile, accumulated in TMEM columns 64.. over all blocks.
+// The thread that issues P V issues the next block's Q K^T right behind it and one
+// tcgen05.commit for both, so a block waits for the tensor core once per 64 keys.
+// Every wait is bounded and ends in an error code, not a hang.
 //
 // Token t of sequence b: q row seq_start[b] + t, position seq_len[b] - n_b + t;
 // it sees keys max(0, pos-window+1)..pos.  A query's result depends on its position
@@ -24,6 +29,7 @@
 // Formula: thanhauco/rust-inference src/attention.rs:4-8, 111-150.
 #include "common.cuh"
 #include "mma_helpers.cuh"
+#include <cuda.h>
 #include <float.h>
 
 #ifndef RI_HEAD_DIM
@@ -42,12 +48,13 @@ static_assert(RI_HEAD_DIM == 64 || RI_HEAD_DIM == 128, "tcgen05 prefill attentio
 #define TC_Q_BYTES (TC_SLABS * TC_Q_SLAB)
 #define TC_KV_BYTES (TC_SLABS * TC_KV_SLAB)
 #define TC_P_BYTES (TC_BM * 128)        // P [128 x 64 keys]: one slab
-#define TC_TMEM_COLS 256                // S: columns 0..63, O_blk: columns 64..64+Dh-1
+#define TC_TMEM_COLS 256                // S: columns 0..63, O: columns 64..64+Dh-1
+#define TC_LAZY 8.0f                    // log2 of how far a score may exceed the running maximum
 
 // dynamic shared memory, 1024-byte aligned (swizzle atoms):
-//   q | k | v | p      then the small things
+//   q | k | v0 | v1 | p      then the small things
 struct TcTail {
-    unsigned long long mma_bar;
+    unsigned long long mma_bar, k_bar, v_bar[2];
     unsigned tmem_base;
     int dead;
     float rowmax[2][128];             // exchange between the two threads of a row
@@ -55,9 +62,9 @@ struct TcTail {
 #define TC_OFF_Q 0
 #define TC_OFF_K (TC_OFF_Q + TC_Q_BYTES)
 #define TC_OFF_V (TC_OFF_K + TC_KV_BYTES)
-#define TC_OFF_P (TC_OFF_V + TC_KV_BYTES)
+#define TC_OFF_P (TC_OFF_V + 2 * TC_KV_BYTES)
 #define TC_OFF_TAIL (TC_OFF_P + TC_P_BYTES)
-#define TC_SMEM_BYTES (TC_OFF_TAIL + 1088 + 1024)   // + slack to align the base to 1024
+#define TC_SMEM_BYTES (TC_OFF_TAIL + 1152 + 1024)   // + slack to align the base to 1024
 
 // The swizzled operand layout: a tile is cut into slabs of 64 elements (128 bytes) along its rows;
 // inside a slab rows are 128 bytes apart and the 16-byte chunk c of a row sits at chunk position
@@ -119,38 +126,82 @@ __device__ __forceinline__ void copy_row_piece(unsigned char* tile, int slab_byt
         cp_async16(dst_row + (c >> 3) * slab_bytes + (((c & 7) ^ (r & 7)) << 4), src_row + c * 8, ok);
     }
 }
-// keys [key0, key0+64) of one kv head: thread t copies a quarter of row t/4
-__device__ __forceinline__ void load_kv_tile(unsigned char* tile, const bf16* __restrict__ pool,
-                                             const int* __restrict__ table, int kvh, int KV, int num_pages, int key0,
-                                             int len, int* err) {
-    constexpr int Q4 = TC_DH / 32;                      // chunks in a quarter row
-    const int r = threadIdx.x >> 2;
-    const int key = key0 + r;
-    bool ok = key < len;
-    size_t off = 0;
-    if (ok) {
-        int page = table[key / TC_PAGE];
-        if (page < 0 || page >= num_pages) {
-            atomicExch(err, 4);
-            ok = false;
-        } else {
-            off = (((size_t)page * KV + kvh) * TC_PAGE + key % TC_PAGE) * TC_DH;
-        }
-    }
-    copy_row_piece(tile, TC_KV_SLAB, r, (threadIdx.x & 3) * Q4, Q4, pool + off, ok);
+__device__ __forceinline__ void tmem_st32(unsigned taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+          "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+          "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+          "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+          "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])),
+          "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+          "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+          "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])),
+          "r"(__float_as_uint(v[31]))
+        : "memory");
 }
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// one box (32 rows x 64 elements) of a pool's tensor map into shared memory: x in elements (0 or 64: a multiple
+// of 16 bytes), y the row of the pool seen as a matrix [pages * KV * 32, Dh]
+__device__ __forceinline__ void tc_tma_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+                 ::"r"(smem_u32(dst)), "l"((unsigned long long)map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+// block-wide barrier that also tells every thread whether any thread's predicate was set
+__device__ __forceinline__ bool sync_or(bool pred) { return __syncthreads_or(pred ? 1 : 0) != 0; }
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
 
+// The places in the pool of the two pages that hold keys 64 kb .. 64 kb + 63 (-1: the sequence has no such page)
+struct TcPages {
+    int id[2];
+};
+__device__ __forceinline__ TcPages tc_pages(const int* __restrict__ table, int kb, int len, int num_pages, int* err) {
+    TcPages r;
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+        const int pg = kb * (TC_BN / TC_PAGE) + j;
+        int id = -1;
+        if (pg * TC_PAGE < len) {
+            id = table[pg];
+            if (id < 0 || id >= num_pages) {
+                atomicExch(err, 4);
+                id = -1;
+            }
+        }
+        r.id[j] = id;
+    }
+    return r;
+}
+// starts the copies of a tile of 64 keys (or values): per page and per slab of 64 head elements one box
+__device__ __forceinline__ void tc_load_tile(unsigned char* tile, const CUtensorMap* map, const TcPages& pg, int kvh, int KV,
+                                             unsigned long long* bar) {
+    const int boxes = ((pg.id[0] >= 0) + (pg.id[1] >= 0)) * TC_SLABS;
+    tc_expect_tx(bar, (unsigned)boxes * (TC_PAGE * 128));       // also completes the phase when there is nothing to copy
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+        if (pg.id[j] < 0) continue;
+        const int row = (pg.id[j] * KV + kvh) * TC_PAGE;
+#pragma unroll
+        for (int sl = 0; sl < TC_SLABS; sl++)
+            tc_tma_2d(tile + sl * TC_KV_SLAB + j * (TC_PAGE * 128), map, sl * 64, row, bar);
+    }
+}
+
 // 256 threads: thread t works on query row t % 128; threads t and t + 128 share a row, the first
 // takes keys 0..31 of a block and the first half of the output elements, the second the rest.
 // Two blocks fit on an SM: while one waits for the tensor core the other does its softmax.
 __global__ void __launch_bounds__(TC_THREADS, 2)
-attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool,
-                            const bf16* __restrict__ v_pool, bf16* __restrict__ out,
+attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
                             const int* __restrict__ page_table, const int* __restrict__ seq_slot,
                             const int* __restrict__ seq_start, const int* __restrict__ seq_len, int H, int KV, int mpps,
                             int num_pages, float scale_log2, int window, int* __restrict__ err) {
@@ -176,72 +227,80 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     const int row = tid & (TC_BM - 1), half = tid >> 7;            // my query row, my half of keys / elements
     const int my_pos = pos_first + row;
     unsigned char* k_tile = smem + TC_OFF_K;
-    unsigned char* v_tile = smem + TC_OFF_V;
+    unsigned char* v_tiles = smem + TC_OFF_V;
 
-    // ---- set-up: tensor memory, the MMA barrier --------------------------------------------------
+    // ---- set-up: tensor memory, the barriers, the first copies ----------------------------------------
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
                      ::"r"(smem_u32(&tail.tmem_base)), "r"(TC_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
+    TcPages next_pages;                                            // thread 0: the pages of the block after this one
     if (tid == 0) {
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_v) : "memory");
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&tail.mma_bar)));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&tail.k_bar)));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&tail.v_bar[0])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&tail.v_bar[1])));
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         tail.dead = 0;
+        const TcPages first = tc_pages(table, kb_lo, len, num_pages, err);
+        tc_load_tile(k_tile, &map_k, first, kvh, KV, &tail.k_bar);
+        tc_load_tile(v_tiles, &map_v, first, kvh, KV, &tail.v_bar[0]);
+        next_pages = tc_pages(table, kb_lo + 1, len, num_pages, err);
     }
-    // ---- copies in flight: group 1 = queries and the first keys, group 2 = the first values --------
     {
         const int r = tid >> 1;
         const bool ok = r < rows;
         copy_row_piece(smem + TC_OFF_Q, TC_Q_SLAB, r, (tid & 1) * (TC_DH / 16), TC_DH / 16,
                        q + ((size_t)(t_begin + r_base + (ok ? r : 0)) * H + h) * TC_DH, ok);
     }
-    load_kv_tile(k_tile, k_pool, table, kvh, KV, num_pages, kb_lo * TC_BN, len, err);
     cp_async_commit();
-    load_kv_tile(v_tile, v_pool, table, kvh, KV, num_pages, kb_lo * TC_BN, len, err);
-    cp_async_commit();
+    cp_async_wait<0>();
+    fence_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = tail.tmem_base;
     const unsigned tmem_row = tmem + ((unsigned)((warp & 3) * 32) << 16);      // this warp's 32 lanes
     const unsigned q_addr = smem_u32(smem + TC_OFF_Q), p_addr = smem_u32(smem + TC_OFF_P);
-    const unsigned k_addr = smem_u32(k_tile), v_addr = smem_u32(v_tile);
+    const unsigned k_addr = smem_u32(k_tile);
     constexpr unsigned IDESC_QK = instr_desc(TC_BM, TC_BN, 0);
     constexpr unsigned IDESC_PV = instr_desc(TC_BM, TC_DH, 1);
     constexpr int OW = TC_DH / 2;                                  // output elements per thread
     constexpr int SW = TC_BN / 2;                                  // scores per thread (32)
 
-    float o[OW];
+    // S = Q K^T of a block whose keys are in the key tile (thread 0)
+    auto issue_qk = [&]() {
 #pragma unroll
-    for (int i = 0; i < OW; i++) o[i] = 0.0f;
-    float m = -FLT_MAX, l = 0.0f;                                  // m: in units of scaled log2 scores
-    unsigned phase = 0;
-    bool dead = false;
-
-    for (int kb = kb_lo; kb <= kb_hi && !dead; kb++) {
-        // the keys of this block have arrived (the values may still be on their way)
-        cp_async_wait<1>();
-        fence_async_smem();
-        tc_fence_before();
-        __syncthreads();
-        // ---- S = Q K^T ---------------------------------------------------------------------------------
-        if (tid == 0) {
-            tc_fence_after();
-#pragma unroll
-            for (int j = 0; j < TC_DH / 16; j++) {
-                unsigned qo = (unsigned)((j >> 2) * TC_Q_SLAB + (j & 3) * 32), ko = (unsigned)((j >> 2) * TC_KV_SLAB + (j & 3) * 32);
-                umma_bf16(tmem, smem_desc(q_addr + qo, 16, 1024), smem_desc(k_addr + ko, 16, 1024), IDESC_QK, j > 0);
-            }
-            umma_commit(&tail.mma_bar);
+        for (int j = 0; j < TC_DH / 16; j++) {
+            unsigned qo = (unsigned)((j >> 2) * TC_Q_SLAB + (j & 3) * 32), ko = (unsigned)((j >> 2) * TC_KV_SLAB + (j & 3) * 32);
+            umma_bf16(tmem, smem_desc(q_addr + qo, 16, 1024), smem_desc(k_addr + ko, 16, 1024), IDESC_QK, j > 0);
         }
-        if (!tc_mbar_wait(&tail.mma_bar, phase)) { atomicExch(err, 5); tail.dead = 1; }
-        phase ^= 1;
+    };
+    bool dead = false;
+    if (tid == 0) {
+        if (!tc_mbar_wait(&tail.k_bar, 0)) { atomicExch(err, 5); tail.dead = 1; }
         tc_fence_after();
-        // the key tile is free: ask for the next block's keys (an empty group after the last block)
-        if (kb < kb_hi) load_kv_tile(k_tile, k_pool, table, kvh, KV, num_pages, (kb + 1) * TC_BN, len, err);
-        cp_async_commit();
-        // ---- my 32 scores of the row: mask, maximum (shared with the row's other thread) --------------
+        issue_qk();
+        umma_commit(&tail.mma_bar);
+    }
+
+    float m = -FLT_MAX, l = 0.0f;                                  // m: in units of scaled log2 scores
+    int it = 0;                                                    // blocks done
+    for (int kb = kb_lo; kb <= kb_hi; kb++, it++) {
+        const int vbuf = it & 1;
+        unsigned char* v_tile = v_tiles + vbuf * TC_KV_BYTES;
+        // S of this block is done, and with it every earlier product: the key tile, P and the other value tile are free
+        if (!tc_mbar_wait(&tail.mma_bar, (unsigned)(it & 1))) { atomicExch(err, 5); tail.dead = 1; }
+        tc_fence_after();
+        if (tid == 0 && kb < kb_hi) {
+            tc_load_tile(k_tile, &map_k, next_pages, kvh, KV, &tail.k_bar);
+            tc_load_tile(v_tiles + (vbuf ^ 1) * TC_KV_BYTES, &map_v, next_pages, kvh, KV, &tail.v_bar[vbuf ^ 1]);
+            if (kb + 1 < kb_hi) next_pages = tc_pages(table, kb + 2, len, num_pages, err);
+        }
+        // ---- my 32 scores of the row: mask, maximum ------------------------------------------------------
         const int k0 = kb * TC_BN + half * SW;                     // my first key
         const bool edge = (kb * TC_BN + TC_BN - 1 > pos_first) || (window > 0 && kb * TC_BN < pos_last - window + 1);
         float s[SW];
@@ -259,14 +318,34 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
 #pragma unroll
             for (int i = 0; i < SW; i++) mx = fmaxf(mx, s[i]);
         }
-        tail.rowmax[half][row] = mx;
-        __syncthreads();
-        mx = fmaxf(mx, tail.rowmax[half ^ 1][row]);
         mx = mx == -FLT_MAX ? -FLT_MAX : mx * scale_log2;          // scale > 0: the maximum of the scaled scores
-        mx = fmaxf(mx, m);
-        const float corr = (m == -FLT_MAX) ? 0.0f : ex2_approx(m - mx);
-        m = mx;
-        l *= corr;
+        // every thread has read S (the next S may overwrite it); does any row have to raise its maximum?
+        tc_fence_before();
+        const bool raise = sync_or(mx > m + TC_LAZY || (m == -FLT_MAX && mx != -FLT_MAX));
+        // a wait that ran out (this block's by any thread, thread 0's of the block before) is known to all here
+        dead = tail.dead != 0;
+        if (dead) break;
+        if (raise) {
+            tail.rowmax[half][row] = mx;
+            __syncthreads();
+            const float m_new = fmaxf(m, fmaxf(mx, tail.rowmax[half ^ 1][row]));
+            const float corr = m_new == m ? 1.0f : ((m == -FLT_MAX) ? 0.0f : ex2_approx(m - m_new));
+            m = m_new;
+            l *= corr;
+            // the output so far, in tensor memory: the loads and stores are the whole warp's, so all its rows go along
+            if (it > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < OW / 32; c++) {
+                    float ob[32];
+                    tmem_ld32(tmem_row + TC_BN + half * OW + c * 32, ob);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) ob[i] *= corr;
+                    tmem_st32(tmem_row + TC_BN + half * OW + c * 32, ob);
+                }
+                tmem_st_wait();
+            }
+        }
         // ---- P = exp2(S * scale - m) as bfloat16 into the operand layout; sum --------------------------
         {
             const float neg_m = (m == -FLT_MAX) ? 0.0f : -m;
@@ -277,7 +356,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
 #pragma unroll
                 for (int e = 0; e < 8; e++) {
                     float x = s[c * 8 + e];
-                    p[e] = (x == -FLT_MAX) ? 0.0f : ex2_approx(fmaf(x, scale_log2, neg_m));
+                    p[e] = (edge && x == -FLT_MAX) ? 0.0f : ex2_approx(fmaf(x, scale_log2, neg_m));
                     l += p[e];
                 }
                 const int chunk = half * (SW / 8) + c;             // 16-byte chunk of the 64-key row
@@ -285,53 +364,68 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
                     make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
             }
         }
-        cp_async_wait<1>();              // the values of this block have arrived (the next keys may be on their way)
+        // the values of this block have arrived (asked for a whole block ago)
+        if (!tc_mbar_wait(&tail.v_bar[vbuf], (unsigned)((it >> 1) & 1))) { atomicExch(err, 5); tail.dead = 1; }
+        if (kb * TC_BN + TC_BN > len) {
+            // rows past the sequence's end hold whatever the pool holds there (or what the tile held before):
+            // zero them, a weight of zero times not-a-number would still be not-a-number
+            const int r = tid >> 2, first_bad = len - kb * TC_BN;
+            if (r >= first_bad) {
+#pragma unroll
+                for (int sl = 0; sl < TC_SLABS; sl++)
+#pragma unroll
+                    for (int c = 0; c < 2; c++)
+                        *(uint4*)(v_tile + sl * TC_KV_SLAB + r * 128 + (((tid & 3) * 2 + c) << 4)) = make_uint4(0, 0, 0, 0);
+            }
+        }
         fence_async_smem();
         tc_fence_before();
         __syncthreads();
-        // ---- O_blk = P V --------------------------------------------------------------------------------
+        // ---- O += P V, and right behind it S of the next block --------------------------------------------
         if (tid == 0) {
             tc_fence_after();
+            const unsigned v_addr = smem_u32(v_tile);
 #pragma unroll
             for (int j = 0; j < TC_BN / 16; j++) {
                 umma_bf16(tmem + TC_BN, smem_desc(p_addr + j * 32, 16, 1024),
-                          smem_desc(v_addr + j * 16 * 128, TC_KV_SLAB, 1024), IDESC_PV, j > 0);
+                          smem_desc(v_addr + j * 16 * 128, TC_KV_SLAB, 1024), IDESC_PV, (it > 0 || j > 0) ? 1u : 0u);
+            }
+            if (kb < kb_hi) {
+                if (!tc_mbar_wait(&tail.k_bar, (unsigned)((it + 1) & 1))) { atomicExch(err, 5); tail.dead = 1; }
+                tc_fence_after();
+                issue_qk();
             }
             umma_commit(&tail.mma_bar);
         }
-        if (!tc_mbar_wait(&tail.mma_bar, phase)) { atomicExch(err, 5); tail.dead = 1; }
-        phase ^= 1;
-        tc_fence_after();
-        // the value tile is free: ask for the next block's values
-        if (kb < kb_hi) load_kv_tile(v_tile, v_pool, table, kvh, KV, num_pages, (kb + 1) * TC_BN, len, err);
-        cp_async_commit();
-#pragma unroll
-        for (int c = 0; c < OW / 32; c++) {
-            float ob[32];
-            tmem_ld32(tmem_row + TC_BN + half * OW + c * 32, ob);
-#pragma unroll
-            for (int i = 0; i < 32; i++) o[c * 32 + i] = fmaf(o[c * 32 + i], corr, ob[i]);
-        }
-        dead = tail.dead != 0;
-        // the next iteration's first barrier comes before anything of S, O_blk or P is overwritten
     }
-    cp_async_wait<0>();
-    // ---- out = O / l (l: both halves of the row) ---------------------------------------------------------
+    // ---- the last product is done: out = O / l (l: both halves of the row) --------------------------------
+    if (!dead && !tc_mbar_wait(&tail.mma_bar, (unsigned)(it & 1))) { atomicExch(err, 5); tail.dead = 1; }
+    tc_fence_after();
     __syncthreads();
+    dead = tail.dead != 0;
     tail.rowmax[half][row] = l;
     __syncthreads();
     l += tail.rowmax[half ^ 1][row];
-    if (row < rows && !dead) {
+    {
+        // every lane of a warp takes part in the loads from tensor memory, whether its row is one of the tile's or not
+        const bool mine = row < rows && !dead;
         const float inv = 1.0f / l;
-        bf16* dst = out + ((size_t)(t_begin + r_base + row) * H + h) * TC_DH + half * OW;
+        bf16* dst = out + ((size_t)(t_begin + r_base + (mine ? row : 0)) * H + h) * TC_DH + half * OW;
 #pragma unroll
-        for (int i = 0; i < OW; i += 8) {
-            uint4 w;
-            w.x = pack_bf16(o[i] * inv, o[i + 1] * inv);
-            w.y = pack_bf16(o[i + 2] * inv, o[i + 3] * inv);
-            w.z = pack_bf16(o[i + 4] * inv, o[i + 5] * inv);
-            w.w = pack_bf16(o[i + 6] * inv, o[i + 7] * inv);
-            *(uint4*)(dst + i) = w;
+        for (int c = 0; c < OW / 32; c++) {
+            float o[32];
+            tmem_ld32(tmem_row + TC_BN + half * OW + c * 32, o);
+            if (mine) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    uint4 w;
+                    w.x = pack_bf16(o[i] * inv, o[i + 1] * inv);
+                    w.y = pack_bf16(o[i + 2] * inv, o[i + 3] * inv);
+                    w.z = pack_bf16(o[i + 4] * inv, o[i + 5] * inv);
+                    w.w = pack_bf16(o[i + 6] * inv, o[i + 7] * inv);
+                    *(uint4*)(dst + c * 32 + i) = w;
+                }
+            }
         }
     }
     tc_fence_before();
@@ -339,6 +433,31 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TC_TMEM_COLS) : "memory");
     }
+}
+
+// a pool [pages, KV, 32, Dh] of bfloat16 as a matrix [pages * KV * 32, Dh], copied in boxes of 32 rows x 64 elements
+typedef CUresult (*tc_encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                       CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static int tc_pool_tensor_map(CUtensorMap* map, const void* pool, long long rows) {
+    static tc_encode_tiled_fn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &res);
+        if (e != cudaSuccess || res != cudaDriverEntryPointSuccess || !fn)
+            RI_FAIL(-1, "attention_prefill_tc: the driver has no cuTensorMapEncodeTiled");
+        encode = (tc_encode_tiled_fn)fn;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)TC_DH, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)TC_DH * 2};
+    cuuint32_t box[2] = {64, TC_PAGE};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) RI_FAIL(-1, "attention_prefill_tc: cuTensorMapEncodeTiled failed with %d", (int)r);
+    return 0;
 }
 
 extern "C" int ri_attention_prefill_tc_head_dim() { return TC_DH; }
@@ -366,8 +485,14 @@ extern "C" int ri_attention_prefill_tc(const void* q, const void* k_pool, const 
     }
     dim3 grid(H, (max_new + TC_BM - 1) / TC_BM, seqs);
     RI_REQUIRE(grid.y <= 65535, "attention_prefill_tc: too many tokens in one sequence of a step");
+    RI_REQUIRE((long long)num_pages * KV * TC_PAGE < (1ll << 31), "attention_prefill_tc: a pool of %d pages", num_pages);
+    CUtensorMap map_k, map_v;
+    int rc = tc_pool_tensor_map(&map_k, k_pool, (long long)num_pages * KV * TC_PAGE);
+    if (rc) return rc;
+    rc = tc_pool_tensor_map(&map_v, v_pool, (long long)num_pages * KV * TC_PAGE);
+    if (rc) return rc;
     attention_prefill_tc_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(
-        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, page_table, seq_slot, seq_start, seq_len,
+        (const bf16*)q, map_k, map_v, (bf16*)out, page_table, seq_slot, seq_start, seq_len,
         H, KV, mpps, num_pages, scale * 1.4426950408889634f, window, err_flag);
     RI_CHECK_LAUNCH("attention_prefill_tc");
     return 0;

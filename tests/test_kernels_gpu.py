@@ -456,6 +456,29 @@ def test_attention_prefill_kernel(H, KV, Dh, window):
     assert torch.equal(one, out[starts[4]:starts[5]])
 
 
+@pytest.mark.parametrize("H,KV,Dh", [(8, 2, 128), (4, 4, 64), (6, 2, 32)])
+def test_attention_prefill_unwritten_rows_are_nan(H, KV, Dh):
+    """As for decoding: what the pool holds past a sequence's end, not-a-number included, changes nothing."""
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(Dh + 1)
+    old = [0, 10, 64, 0, 200]
+    new = [40, 23, 1, 129, 100]
+    lens = [a + b for a, b in zip(old, new)]
+    table, slots, k, v, k_pool, v_pool = _fill_pools(rng, lens, KV, Dh, "bfloat16", scale=0.5, junk_nan=True)
+    q = rnd(rng, sum(new), H, Dh, dtype="bfloat16")
+    starts = np.concatenate([[0], np.cumsum(new)]).astype(np.int32)
+    bt = torch.bfloat16
+    out = ops.attention_prefill(dev(q, bt), dev(k_pool, bt), dev(v_pool, bt), dev(table, torch.int32),
+                                dev(slots, torch.int32), dev(starts, torch.int32), dev(np.array(lens), torch.int32),
+                                max(new), 1.0 / math.sqrt(Dh), 0)
+    assert int(ops.error_flag("cuda").item()) == 0
+    assert bool(torch.isfinite(out.float()).all())
+    for b, (o, n) in enumerate(zip(old, new)):
+        qall = np.concatenate([np.zeros((o, H, Dh)), q[starts[b]:starts[b + 1]].astype(np.float64)])
+        want = plain.causal_attention(qall, k[b].astype(np.float64), v[b].astype(np.float64))[o:]
+        close(out[starts[b]:starts[b + 1]], want, 2e-2, f"prefill attention, sequence {b}")
+
+
 @pytest.mark.parametrize("H,KV,Dh,window,seqs,longest", [(8, 8, 64, 0, 44, 1100), (16, 4, 128, 0, 44, 1100),
                                                          (6, 2, 32, 300, 44, 1100), (12, 1, 128, 500, 44, 1100),
                                                          (16, 8, 128, 0, 196, 200)])
