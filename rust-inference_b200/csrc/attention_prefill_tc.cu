@@ -5,10 +5,13 @@
 // 64 keys
 //   1. one thread starts TMA tensor copies (cp.async.bulk.tensor.2d, 128-byte swizzle:
 //      the layout the tensor core reads) of the two pages of keys and of values from
-//      the paged cache; the next block's keys are asked for as soon as S is done, its
-//      values go into the second value buffer while this block is worked on;
+//      the paged cache, two blocks ahead for the keys and one for the values (two
+//      buffers each);
 //   2. S = Q K^T: one thread issues tcgen05.mma (M 128 queries, N 64 keys), the
-//      accumulator lives in tensor memory (TMEM columns 0..63);
+//      accumulator lives in tensor memory.  There are two S buffers (TMEM columns 0..63
+//      and 64..127): S of the next block is issued as soon as every thread has read S
+//      of this block, so the tensor core works on it and on the last P V while the
+//      threads are busy with this block's softmax;
 //   3. every thread reads its half row of S from TMEM (tcgen05.ld), and writes its
 //      part of P = exp2(S * scale - m) as bfloat16 into shared memory in the operand
 //      layout.  m is the row's running maximum, raised only when some row of the tile
@@ -16,10 +19,12 @@
 //      maximum and rescales its output in TMEM with tcgen05.ld / tcgen05.st); weights
 //      up to 2^8 are exact in float32 and as good as any in bfloat16;
 //   4. O += P V: tcgen05.mma with V read as an MN-major operand straight from the
-//      [key][element] tile, accumulated in TMEM columns 64.. over all blocks.
-// The thread that issues P V issues the next block's Q K^T right behind it and one
-// tcgen05.commit for both, so a block waits for the tensor core once per 64 keys.
-// Every wait is bounded and ends in an error code, not a hang.
+//      [key][element] tile, accumulated in TMEM columns 128.. over all blocks.
+// Completion of the products is signalled through tcgen05.commit on mbarriers (one for
+// S, one for P V).  Every wait is bounded and ends in an error code, not a hang.
+// The block's shared memory (112.6 KB, two blocks per SM) leaves no room for slack: the
+// dynamic shared memory must start on a multiple of 1024 bytes, else the kernel reports
+// error 6 and does nothing.
 //
 // Token t of sequence b: q row seq_start[b] + t, position seq_len[b] - n_b + t;
 // it sees keys max(0, pos-window+1)..pos.  A query's result depends on its position
@@ -48,23 +53,24 @@ static_assert(RI_HEAD_DIM == 64 || RI_HEAD_DIM == 128, "tcgen05 prefill attentio
 #define TC_Q_BYTES (TC_SLABS * TC_Q_SLAB)
 #define TC_KV_BYTES (TC_SLABS * TC_KV_SLAB)
 #define TC_P_BYTES (TC_BM * 128)        // P [128 x 64 keys]: one slab
-#define TC_TMEM_COLS 256                // S: columns 0..63, O: columns 64..64+Dh-1
+#define TC_TMEM_COLS 256                // S: columns 0..63 and 64..127, O: columns 128..128+Dh-1
+#define TC_O_COL (2 * TC_BN)
 #define TC_LAZY 8.0f                    // log2 of how far a score may exceed the running maximum
 
 // dynamic shared memory, 1024-byte aligned (swizzle atoms):
-//   q | k | v0 | v1 | p      then the small things
+//   q | k0 | k1 | v0 | v1 | p      then the small things
 struct TcTail {
-    unsigned long long mma_bar, k_bar, v_bar[2];
+    unsigned long long s_bar, pv_bar, p_bar, k_bar[2], v_bar[2];
     unsigned tmem_base;
     int dead;
-    float rowmax[2][128];             // exchange between the two threads of a row
+    float rowmax[128];                // exchange between the two threads of a row
 };
 #define TC_OFF_Q 0
 #define TC_OFF_K (TC_OFF_Q + TC_Q_BYTES)
-#define TC_OFF_V (TC_OFF_K + TC_KV_BYTES)
+#define TC_OFF_V (TC_OFF_K + 2 * TC_KV_BYTES)
 #define TC_OFF_P (TC_OFF_V + 2 * TC_KV_BYTES)
 #define TC_OFF_TAIL (TC_OFF_P + TC_P_BYTES)
-#define TC_SMEM_BYTES (TC_OFF_TAIL + 1152 + 1024)   // + slack to align the base to 1024
+#define TC_SMEM_BYTES (TC_OFF_TAIL + 576)
 
 // The swizzled operand layout: a tile is cut into slabs of 64 elements (128 bytes) along its rows;
 // inside a slab rows are 128 bytes apart and the 16-byte chunk c of a row sits at chunk position
@@ -205,8 +211,11 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
                             const int* __restrict__ page_table, const int* __restrict__ seq_slot,
                             const int* __restrict__ seq_start, const int* __restrict__ seq_len, int H, int KV, int mpps,
                             int num_pages, float scale_log2, int window, int* __restrict__ err) {
-    extern __shared__ unsigned char smem_dyn[];
-    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) unsigned char smem[];
+    if (smem_u32(smem) & 1023u) {                                  // see the note on shared memory at the top
+        if (threadIdx.x == 0) atomicExch(err, 6);
+        return;
+    }
     TcTail& tail = *reinterpret_cast<TcTail*>(smem + TC_OFF_TAIL);
     // blocks start in the order of blockIdx.x, then y: heads vary fastest, so the late tiles of all
     // heads, which see the most keys, start first
@@ -226,7 +235,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int row = tid & (TC_BM - 1), half = tid >> 7;            // my query row, my half of keys / elements
     const int my_pos = pos_first + row;
-    unsigned char* k_tile = smem + TC_OFF_K;
+    unsigned char* k_tiles = smem + TC_OFF_K;
     unsigned char* v_tiles = smem + TC_OFF_V;
 
     // ---- set-up: tensor memory, the barriers, the first copies ----------------------------------------
@@ -235,20 +244,22 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
                      ::"r"(smem_u32(&tail.tmem_base)), "r"(TC_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
-    TcPages next_pages;                                            // thread 0: the pages of the block after this one
     if (tid == 0) {
         asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_v) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&tail.mma_bar)));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&tail.k_bar)));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&tail.v_bar[0])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&tail.v_bar[1])));
+        unsigned long long* bars[6] = {&tail.s_bar, &tail.pv_bar, &tail.k_bar[0], &tail.k_bar[1], &tail.v_bar[0], &tail.v_bar[1]};
+#pragma unroll
+        for (int i = 0; i < 6; i++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(bars[i])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(&tail.p_bar)), "r"(TC_THREADS));
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         tail.dead = 0;
         const TcPages first = tc_pages(table, kb_lo, len, num_pages, err);
-        tc_load_tile(k_tile, &map_k, first, kvh, KV, &tail.k_bar);
+        tc_load_tile(k_tiles, &map_k, first, kvh, KV, &tail.k_bar[0]);
         tc_load_tile(v_tiles, &map_v, first, kvh, KV, &tail.v_bar[0]);
-        next_pages = tc_pages(table, kb_lo + 1, len, num_pages, err);
+        if (kb_lo < kb_hi) {
+            const TcPages second = tc_pages(table, kb_lo + 1, len, num_pages, err);
+            tc_load_tile(k_tiles + TC_KV_BYTES, &map_k, second, kvh, KV, &tail.k_bar[1]);
+        }
     }
     {
         const int r = tid >> 1;
@@ -265,83 +276,108 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
     const unsigned tmem = tail.tmem_base;
     const unsigned tmem_row = tmem + ((unsigned)((warp & 3) * 32) << 16);      // this warp's 32 lanes
     const unsigned q_addr = smem_u32(smem + TC_OFF_Q), p_addr = smem_u32(smem + TC_OFF_P);
-    const unsigned k_addr = smem_u32(k_tile);
     constexpr unsigned IDESC_QK = instr_desc(TC_BM, TC_BN, 0);
     constexpr unsigned IDESC_PV = instr_desc(TC_BM, TC_DH, 1);
     constexpr int OW = TC_DH / 2;                                  // output elements per thread
     constexpr int SW = TC_BN / 2;                                  // scores per thread (32)
 
-    // S = Q K^T of a block whose keys are in the key tile (thread 0)
-    auto issue_qk = [&]() {
-#pragma unroll
-        for (int j = 0; j < TC_DH / 16; j++) {
-            unsigned qo = (unsigned)((j >> 2) * TC_Q_SLAB + (j & 3) * 32), ko = (unsigned)((j >> 2) * TC_KV_SLAB + (j & 3) * 32);
-            umma_bf16(tmem, smem_desc(q_addr + qo, 16, 1024), smem_desc(k_addr + ko, 16, 1024), IDESC_QK, j > 0);
-        }
-    };
-    bool dead = false;
-    if (tid == 0) {
-        if (!tc_mbar_wait(&tail.k_bar, 0)) { atomicExch(err, 5); tail.dead = 1; }
+    // Four threads of four different warps share the side work, so that no warp falls far behind the others:
+    // thread 0 issues Q K^T, thread 32 P V, thread 64 copies keys, thread 96 copies values.  The copying threads
+    // look the pages up one block before they need them.
+    const bool qk_thread = tid == 0, pv_thread = tid == 32, k_thread = tid == 64, v_thread = tid == 96;
+    TcPages ahead;                                                 // k_thread: pages of block kb + 2; v_thread: of block kb + 1
+    ahead.id[0] = ahead.id[1] = -1;
+    if (k_thread && kb_lo + 1 < kb_hi) ahead = tc_pages(table, kb_lo + 2, len, num_pages, err);
+    if (v_thread && kb_lo < kb_hi) ahead = tc_pages(table, kb_lo + 1, len, num_pages, err);
+
+    // qk_thread: S[j & 1] = Q K^T for the j-th block of this tile, once its keys have arrived
+    auto issue_qk = [&](int j) {
+        if (!tc_mbar_wait(&tail.k_bar[j & 1], (unsigned)((j >> 1) & 1))) { atomicExch(err, 5); tail.dead = 1; }
         tc_fence_after();
-        issue_qk();
-        umma_commit(&tail.mma_bar);
-    }
+        const unsigned k_addr = smem_u32(k_tiles + (j & 1) * TC_KV_BYTES);
+#pragma unroll
+        for (int i = 0; i < TC_DH / 16; i++) {
+            unsigned qo = (unsigned)((i >> 2) * TC_Q_SLAB + (i & 3) * 32), ko = (unsigned)((i >> 2) * TC_KV_SLAB + (i & 3) * 32);
+            umma_bf16(tmem + (j & 1) * TC_BN, smem_desc(q_addr + qo, 16, 1024), smem_desc(k_addr + ko, 16, 1024), IDESC_QK, i > 0);
+        }
+        umma_commit(&tail.s_bar);
+    };
+    if (qk_thread) issue_qk(0);
 
     float m = -FLT_MAX, l = 0.0f;                                  // m: in units of scaled log2 scores
+    bool dead = false;
     int it = 0;                                                    // blocks done
     for (int kb = kb_lo; kb <= kb_hi; kb++, it++) {
-        const int vbuf = it & 1;
-        unsigned char* v_tile = v_tiles + vbuf * TC_KV_BYTES;
-        // S of this block is done, and with it every earlier product: the key tile, P and the other value tile are free
-        if (!tc_mbar_wait(&tail.mma_bar, (unsigned)(it & 1))) { atomicExch(err, 5); tail.dead = 1; }
+        const int buf = it & 1;
+        unsigned char* v_tile = v_tiles + buf * TC_KV_BYTES;
+        // ---- S of this block is done (its key tile is free) ------------------------------------------------
+        if (!tc_mbar_wait(&tail.s_bar, (unsigned)buf)) { atomicExch(err, 5); tail.dead = 1; }
         tc_fence_after();
-        if (tid == 0 && kb < kb_hi) {
-            tc_load_tile(k_tile, &map_k, next_pages, kvh, KV, &tail.k_bar);
-            tc_load_tile(v_tiles + (vbuf ^ 1) * TC_KV_BYTES, &map_v, next_pages, kvh, KV, &tail.v_bar[vbuf ^ 1]);
-            if (kb + 1 < kb_hi) next_pages = tc_pages(table, kb + 2, len, num_pages, err);
+        // the keys of the block after the next go into the tile that S of this block has just finished with
+        if (k_thread && kb + 1 < kb_hi) {
+            tc_load_tile(k_tiles + buf * TC_KV_BYTES, &map_k, ahead, kvh, KV, &tail.k_bar[buf]);
+            if (kb + 2 < kb_hi) ahead = tc_pages(table, kb + 3, len, num_pages, err);
         }
         // ---- my 32 scores of the row: mask, maximum ------------------------------------------------------
         const int k0 = kb * TC_BN + half * SW;                     // my first key
         const bool edge = (kb * TC_BN + TC_BN - 1 > pos_first) || (window > 0 && kb * TC_BN < pos_last - window + 1);
         float s[SW];
-        tmem_ld32(tmem_row + half * SW, s);
-        float mx = -FLT_MAX;
+        tmem_ld32(tmem_row + buf * TC_BN + half * SW, s);
         if (edge) {
 #pragma unroll
             for (int i = 0; i < SW; i++) {
                 int key = k0 + i;
                 bool vis = key <= my_pos && (window <= 0 || key > my_pos - window);
                 s[i] = vis ? s[i] : -FLT_MAX;
-                mx = fmaxf(mx, s[i]);
             }
-        } else {
-#pragma unroll
-            for (int i = 0; i < SW; i++) mx = fmaxf(mx, s[i]);
         }
+        float mx4[4] = {-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX};   // four chains instead of one of 32 steps
+#pragma unroll
+        for (int i = 0; i < SW; i++) mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         mx = mx == -FLT_MAX ? -FLT_MAX : mx * scale_log2;          // scale > 0: the maximum of the scaled scores
-        // every thread has read S (the next S may overwrite it); does any row have to raise its maximum?
+        // every thread has read S; does any row have to raise its maximum?
         tc_fence_before();
         const bool raise = sync_or(mx > m + TC_LAZY || (m == -FLT_MAX && mx != -FLT_MAX));
         // a wait that ran out (this block's by any thread, thread 0's of the block before) is known to all here
         dead = tail.dead != 0;
         if (dead) break;
+        // S of the next block goes into the other S buffer, which every thread has read by now.  It is started
+        // only here, behind the block-wide barrier: every thread has then seen this block's phase of the S
+        // barrier, so that barrier is never two phases ahead of a thread that waits on it by parity.
+        if (qk_thread && kb < kb_hi) issue_qk(it + 1);
+        // ---- P V of the block before is done: P, its value tile and the output are free -------------------
+        if (it > 0) {
+            if (!tc_mbar_wait(&tail.pv_bar, (unsigned)((it - 1) & 1))) { atomicExch(err, 5); tail.dead = 1; }
+            tc_fence_after();
+        }
+        if (v_thread && kb < kb_hi) {
+            tc_load_tile(v_tiles + (buf ^ 1) * TC_KV_BYTES, &map_v, ahead, kvh, KV, &tail.v_bar[buf ^ 1]);
+            if (kb + 1 < kb_hi) ahead = tc_pages(table, kb + 2, len, num_pages, err);
+        }
         if (raise) {
-            tail.rowmax[half][row] = mx;
+            // the row's two threads agree on its maximum: the second tells the first, the first answers
+            if (half) tail.rowmax[row] = mx;
             __syncthreads();
-            const float m_new = fmaxf(m, fmaxf(mx, tail.rowmax[half ^ 1][row]));
+            float m_new = 0.0f;
+            if (!half) {
+                m_new = fmaxf(m, fmaxf(mx, tail.rowmax[row]));
+                tail.rowmax[row] = m_new;
+            }
+            __syncthreads();
+            if (half) m_new = tail.rowmax[row];
             const float corr = m_new == m ? 1.0f : ((m == -FLT_MAX) ? 0.0f : ex2_approx(m - m_new));
             m = m_new;
             l *= corr;
             // the output so far, in tensor memory: the loads and stores are the whole warp's, so all its rows go along
             if (it > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
-                tc_fence_after();
 #pragma unroll
                 for (int c = 0; c < OW / 32; c++) {
                     float ob[32];
-                    tmem_ld32(tmem_row + TC_BN + half * OW + c * 32, ob);
+                    tmem_ld32(tmem_row + TC_O_COL + half * OW + c * 32, ob);
 #pragma unroll
                     for (int i = 0; i < 32; i++) ob[i] *= corr;
-                    tmem_st32(tmem_row + TC_BN + half * OW + c * 32, ob);
+                    tmem_st32(tmem_row + TC_O_COL + half * OW + c * 32, ob);
                 }
                 tmem_st_wait();
             }
@@ -350,6 +386,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
         {
             const float neg_m = (m == -FLT_MAX) ? 0.0f : -m;
             unsigned char* p_row = smem + TC_OFF_P + row * 128;
+            float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int c = 0; c < SW / 8; c++) {
                 float p[8];
@@ -357,15 +394,16 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
                 for (int e = 0; e < 8; e++) {
                     float x = s[c * 8 + e];
                     p[e] = (edge && x == -FLT_MAX) ? 0.0f : ex2_approx(fmaf(x, scale_log2, neg_m));
-                    l += p[e];
+                    l4[e & 3] += p[e];
                 }
                 const int chunk = half * (SW / 8) + c;             // 16-byte chunk of the 64-key row
                 *(uint4*)(p_row + ((chunk ^ (row & 7)) << 4)) =
                     make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
             }
+            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
         }
         // the values of this block have arrived (asked for a whole block ago)
-        if (!tc_mbar_wait(&tail.v_bar[vbuf], (unsigned)((it >> 1) & 1))) { atomicExch(err, 5); tail.dead = 1; }
+        if (!tc_mbar_wait(&tail.v_bar[buf], (unsigned)((it >> 1) & 1))) { atomicExch(err, 5); tail.dead = 1; }
         if (kb * TC_BN + TC_BN > len) {
             // rows past the sequence's end hold whatever the pool holds there (or what the tile held before):
             // zero them, a weight of zero times not-a-number would still be not-a-number
@@ -378,34 +416,37 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
                         *(uint4*)(v_tile + sl * TC_KV_SLAB + r * 128 + (((tid & 3) * 2 + c) << 4)) = make_uint4(0, 0, 0, 0);
             }
         }
+        // my part of P (and of the value tile) is written: tell the thread that issues P V and go on; nobody
+        // waits here, the next block-wide barrier is the vote on the maximum of the next block
         fence_async_smem();
         tc_fence_before();
-        __syncthreads();
-        // ---- O += P V, and right behind it S of the next block --------------------------------------------
-        if (tid == 0) {
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&tail.p_bar)) : "memory");
+        // ---- O += P V --------------------------------------------------------------------------------------
+        if (pv_thread) {
+            if (!tc_mbar_wait(&tail.p_bar, (unsigned)buf)) { atomicExch(err, 5); tail.dead = 1; }
             tc_fence_after();
             const unsigned v_addr = smem_u32(v_tile);
 #pragma unroll
             for (int j = 0; j < TC_BN / 16; j++) {
-                umma_bf16(tmem + TC_BN, smem_desc(p_addr + j * 32, 16, 1024),
+                umma_bf16(tmem + TC_O_COL, smem_desc(p_addr + j * 32, 16, 1024),
                           smem_desc(v_addr + j * 16 * 128, TC_KV_SLAB, 1024), IDESC_PV, (it > 0 || j > 0) ? 1u : 0u);
             }
-            if (kb < kb_hi) {
-                if (!tc_mbar_wait(&tail.k_bar, (unsigned)((it + 1) & 1))) { atomicExch(err, 5); tail.dead = 1; }
-                tc_fence_after();
-                issue_qk();
-            }
-            umma_commit(&tail.mma_bar);
+            umma_commit(&tail.pv_bar);
         }
     }
     // ---- the last product is done: out = O / l (l: both halves of the row) --------------------------------
-    if (!dead && !tc_mbar_wait(&tail.mma_bar, (unsigned)(it & 1))) { atomicExch(err, 5); tail.dead = 1; }
+    if (!dead && it > 0 && !tc_mbar_wait(&tail.pv_bar, (unsigned)((it - 1) & 1))) { atomicExch(err, 5); tail.dead = 1; }
     tc_fence_after();
     __syncthreads();
     dead = tail.dead != 0;
-    tail.rowmax[half][row] = l;
+    if (half) tail.rowmax[row] = l;
     __syncthreads();
-    l += tail.rowmax[half ^ 1][row];
+    if (!half) {
+        l += tail.rowmax[row];
+        tail.rowmax[row] = l;
+    }
+    __syncthreads();
+    if (half) l = tail.rowmax[row];
     {
         // every lane of a warp takes part in the loads from tensor memory, whether its row is one of the tile's or not
         const bool mine = row < rows && !dead;
@@ -414,7 +455,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
 #pragma unroll
         for (int c = 0; c < OW / 32; c++) {
             float o[32];
-            tmem_ld32(tmem_row + TC_BN + half * OW + c * 32, o);
+            tmem_ld32(tmem_row + TC_O_COL + half * OW + c * 32, o);
             if (mine) {
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {
