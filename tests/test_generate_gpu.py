@@ -61,7 +61,7 @@ def test_greedy_generation_matches_plain(dirs, name, dtype):
 def test_long_decoding_and_first_tokens(dirs, tmp_path, dtype):
     """One token, then 299 single-token steps (graphs, page and chunk edges, the bucket
     edge at 1,024 with config C's prompt): every position's logits against the plain model."""
-    for name, prompt_len, total in (("B", 1, 250), ("C", 1000, 1060)):
+    for name, prompt_len, total in (("B", 1, 250), ("C", 1000, 1060), ("D", 1000, 1050)):
         cfg, _ = ALL[name]
         rng = np.random.default_rng(11)
         reqs = H.random_requests(rng, cfg["vocab_size"], [total])

@@ -9,7 +9,8 @@ from tiny_configs import ALL
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [5, 9, 13, 1, 40, 34, 70, 100], "B": [1, 17, 33, 64, 65, 150, 2, 96], "C": [300, 47, 129, 33, 520]}
+LENGTHS = {"A": [5, 9, 13, 1, 40, 34, 70, 100], "B": [1, 17, 33, 64, 65, 150, 2, 96], "C": [300, 47, 129, 33, 520],
+           "D": [200, 65, 129, 1, 300, 40]}
 
 
 @pytest.fixture(scope="module")
@@ -20,7 +21,7 @@ def model_dirs(tmp_path_factory):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_replay_three_ways(tmp_path, model_dirs, name, dtype):
     cfg, _ = ALL[name]
     d = model_dirs[name]

@@ -29,4 +29,15 @@ TINY_C = {
 }
 TINY_C_STORED = "bfloat16"
 
-ALL = {"A": (TINY_A, TINY_A_STORED), "B": (TINY_B, TINY_B_STORED), "C": (TINY_C, TINY_C_STORED)}
+# the head size of the large models (128: the tcgen05 prefill and the streaming decode attention), three query
+# heads per kv head, a width that is no multiple of 64
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 168, "num_attention_heads": 6, "num_key_value_heads": 2,
+    "head_dim": 128, "intermediate_size": 328, "vocab_size": 777, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 2048,
+}
+TINY_D_STORED = "bfloat16"
+
+ALL = {"A": (TINY_A, TINY_A_STORED), "B": (TINY_B, TINY_B_STORED), "C": (TINY_C, TINY_C_STORED),
+       "D": (TINY_D, TINY_D_STORED)}
