@@ -1,7 +1,9 @@
-"""Each kind of part alone against its plain formula, and a toy architecture whose
-mixer keeps state of its own, defined in this file and registered without touching the
-package: one layer with the toy mixer, one with attention, the first layer scheduled
-twice (once more at the end, reading its own state on)."""
+"""Each kind of part alone against its plain formula, and toy architectures defined in
+this file and registered without touching the package: one whose mixer keeps state of
+its own (one layer with the toy mixer, one with attention, the first layer scheduled
+twice, once more at the end, reading its own state on); a position encoding with a rule
+of its own; and one with two kinds of cache (all keys, a window), a layer that reads the
+cache another layer wrote, and a feed-forward that routes tokens to experts."""
 import math
 from dataclasses import dataclass
 
@@ -306,3 +308,164 @@ def test_attention_part_with_a_position_encoding_of_its_own(dtype):
     v = plain.linear(x, W["v_proj.weight"]).reshape(n, KV, Dh)
     want = plain.linear(plain.causal_attention(q, k, v).reshape(n, Hh * Dh), W["o_proj.weight"])
     assert np.abs(got - want).max() <= (2e-5 if dtype == "float32" else 4e-2) * np.abs(want).max()
+
+
+# ---- a toy architecture with two kinds of cache and a routed feed-forward, all of it defined here -------------
+#
+# layer 0: attention over all keys (head size 64: in bfloat16 the tcgen05 and the streaming kernels) + SwiGLU
+# layer 1: attention over a window of 40 keys, other head counts and size (a cache group of its own, pages behind
+#          the window go back) + a feed-forward that routes every token to one of three small experts
+# layer 2: attention that appends nothing: its queries read the keys and values that layer 0 wrote + SwiGLU
+
+from rust_inference_b200.parts import FeedForward, register_ffn  # noqa: E402
+
+
+@dataclass(frozen=True)
+class RoutedSpec:
+    hidden_size: int
+    expert_size: int
+    experts: int
+    kind: str = "toy_routed"
+
+
+@register_ffn("toy_routed")
+class RoutedFfn(FeedForward):
+    """Router logits in float32, the best expert takes the token: y = W2[e] relu(W1[e] x) * softmax(logits)[e]."""
+    graph_safe = True            # device tensors only, no host decisions
+
+    @classmethod
+    def param_infos(cls, spec):
+        E, I, D = spec.experts, spec.expert_size, spec.hidden_size
+        infos = {"router.weight": ParamInfo((E, D))}
+        for e in range(E):
+            infos[f"experts.{e}.w1.weight"] = ParamInfo((I, D))
+            infos[f"experts.{e}.w2.weight"] = ParamInfo((D, I))
+        return infos
+
+    def load(self, tensors):
+        E = self.spec.experts
+        self.router = tensors["router.weight"].float()
+        self.w1 = torch.stack([tensors[f"experts.{e}.w1.weight"] for e in range(E)]).float()
+        self.w2 = torch.stack([tensors[f"experts.{e}.w2.weight"] for e in range(E)]).float()
+
+    def __call__(self, x, ctx):
+        xf = x.float()
+        probs = torch.softmax(xf @ self.router.t(), dim=-1)
+        best = probs.argmax(dim=-1)
+        hid = torch.relu(torch.einsum("td,tid->ti", xf, self.w1[best]))
+        y = torch.einsum("ti,tdi->td", hid, self.w2[best]) * probs.gather(1, best[:, None])
+        return y.to(x.dtype)
+
+
+@register_architecture("ToyMixedLM")
+@dataclass(frozen=True)
+class MixedConfig:
+    vocab_size: int = 131
+    hidden_size: int = 72
+    window: int = 40
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(**{k: d[k] for k in ("vocab_size", "hidden_size", "window") if k in d})
+
+    def validate(self):
+        pass
+
+    def to_dict(self):
+        return {"architectures": ["ToyMixedLM"], "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
+                "window": self.window}
+
+    def to_spec(self):
+        D = self.hidden_size
+        norm = RMSNormSpec(size=D, eps=1e-6)
+        wide = AttentionSpec(hidden_size=D, num_heads=4, num_kv_heads=2, head_dim=64,
+                             position=RopeSpec(head_dim=64, theta=1e4), qk_norm=RMSNormSpec(size=64, eps=1e-6))
+        near = AttentionSpec(hidden_size=D, num_heads=2, num_kv_heads=1, head_dim=32,
+                             position=RopeSpec(head_dim=32, theta=1e5), qk_norm=None, window=self.window)
+        dense = SwiGLUSpec(hidden_size=D, intermediate_size=104)
+        routed = RoutedSpec(hidden_size=D, expert_size=40, experts=3)
+
+        def layer(i, mixer, ffn):
+            return LayerSpec(mixer=mixer, ffn=ffn, mixer_norm=norm, ffn_norm=norm, names=(
+                ("mixer", f"layers.{i}.attn."), ("ffn", f"layers.{i}.ffn."), ("mixer_norm", f"layers.{i}.norm1."),
+                ("ffn_norm", f"layers.{i}.norm2.")))
+        layers = (layer(0, wide, dense), layer(1, near, routed), layer(2, wide, dense))
+        schedule = (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(2, 0, writes=False))
+        return ModelSpec(architecture="ToyMixedLM", vocab_size=self.vocab_size, hidden_size=D, layers=layers,
+                         schedule=schedule, final_norm=norm, tie_embeddings=False, max_positions=1024,
+                         embedding_name="embed.weight", head_name="head.weight", final_norm_prefix="norm.")
+
+
+def mixed_plain(cfg, W, ids, margins=None):
+    """Logits; `margins` (a list) receives, per position, how far the router's best logit is ahead of the second,
+    as a fraction of the largest."""
+    n = len(ids)
+    h = W["embed.weight"][np.asarray(ids)]
+
+    def qkv(x, p, H_, KV, Dh, theta, normed):
+        q = plain.linear(x, W[p + "q_proj.weight"]).reshape(n, H_, Dh)
+        k = plain.linear(x, W[p + "k_proj.weight"]).reshape(n, KV, Dh)
+        v = plain.linear(x, W[p + "v_proj.weight"]).reshape(n, KV, Dh)
+        if normed:
+            q, k = plain.rms_norm(q, W[p + "q_norm.weight"], 1e-6), plain.rms_norm(k, W[p + "k_norm.weight"], 1e-6)
+        cos, sin = plain.rope_cos_sin(np.arange(n), Dh, theta)
+        return plain.apply_rope(q, cos, sin), plain.apply_rope(k, cos, sin), v
+
+    def routed(x, p):
+        logits = x @ W[p + "router.weight"].T
+        probs = np.exp(logits - logits.max(-1, keepdims=True))
+        probs /= probs.sum(-1, keepdims=True)
+        out = np.zeros_like(x)
+        if margins is not None:
+            top = np.sort(logits, axis=-1)
+            margins.extend(((top[:, -1] - top[:, -2]) / np.abs(logits).max(-1)).tolist())
+        for t in range(n):
+            e = int(np.argmax(probs[t]))
+            hid = np.maximum(W[p + f"experts.{e}.w1.weight"] @ x[t], 0.0)
+            out[t] = (W[p + f"experts.{e}.w2.weight"] @ hid) * probs[t, e]
+        return out
+
+    # layer 0
+    x = plain.rms_norm(h, W["layers.0.norm1.weight"], 1e-6)
+    q0, k0, v0 = qkv(x, "layers.0.attn.", 4, 2, 64, 1e4, True)
+    h = h + plain.linear(plain.causal_attention(q0, k0, v0).reshape(n, 256), W["layers.0.attn.o_proj.weight"])
+    h = h + plain.swiglu_mlp(plain.rms_norm(h, W["layers.0.norm2.weight"], 1e-6), W, "layers.0.ffn.")
+    # layer 1: a window
+    x = plain.rms_norm(h, W["layers.1.norm1.weight"], 1e-6)
+    q1, k1, v1 = qkv(x, "layers.1.attn.", 2, 1, 32, 1e5, False)
+    h = h + plain.linear(plain.causal_attention(q1, k1, v1, window=cfg.window).reshape(n, 64), W["layers.1.attn.o_proj.weight"])
+    h = h + routed(plain.rms_norm(h, W["layers.1.norm2.weight"], 1e-6), "layers.1.ffn.")
+    # layer 2: its own queries over layer 0's keys and values
+    x = plain.rms_norm(h, W["layers.2.norm1.weight"], 1e-6)
+    q2, _, _ = qkv(x, "layers.2.attn.", 4, 2, 64, 1e4, True)
+    h = h + plain.linear(plain.causal_attention(q2, k0, v0).reshape(n, 256), W["layers.2.attn.o_proj.weight"])
+    h = h + plain.swiglu_mlp(plain.rms_norm(h, W["layers.2.norm2.weight"], 1e-6), W, "layers.2.ffn.")
+    return plain.rms_norm(h, W["norm.weight"], 1e-6) @ W["head.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_with_two_cache_groups_a_shared_cache_and_routing(tmp_path, dtype):
+    from rust_inference_b200.engine import Engine, Model
+    cfg = MixedConfig()
+    d = H.make_model_dir(tmp_path, cfg.to_dict(), seed=8, stored="float32" if dtype == "float32" else "bfloat16", name="mixed")
+    W = plain.read_safetensors(d + "/model.safetensors")
+    model = Model.from_dir(d, dtype, "cuda:0")
+    groups = Engine(model, max_tokens=2048, max_seqs=3).cache.groups
+    assert len(groups) == 2 and sorted(g.req.window for g in groups) == [0, cfg.window]
+    rng = np.random.default_rng(2)
+    reqs = H.random_requests(rng, cfg.vocab_size, [7, 90, 33, 150, 64, 41])
+    W64 = {k: v.astype(np.float64) for k, v in W.items()}
+    want, close_call = {}, set()
+    for rid, toks in reqs.items():
+        margins = []
+        want[rid] = mixed_plain(cfg, W64, toks, margins)
+        # in bfloat16 a token whose two best experts nearly tie may go to the other one: a choice, not an error
+        close_call |= {(rid, t) for t, m in enumerate(margins) if dtype == "bfloat16" and m < 0.05}
+    assert len(close_call) < 0.3 * sum(len(t) for t in reqs.values())
+    for label, steps in (("whole", H.trace_whole(reqs)), ("tail", H.trace_tail(reqs, tail=32)),
+                         ("batches", H.trace_batches(reqs, 3, [12, 0, 35]))):
+        out = str(tmp_path / f"mixed_{label}")
+        H.replay_inprocess(d, dtype, steps, out, device="cuda")      # in this process: the toy parts live here
+        rows = H.collect(steps, out, cfg.vocab_size)
+        assert len(rows) == sum(len(t) for t in reqs.values())
+        H.assert_rows_close({k: r for k, r in rows.items() if k not in close_call}, want, dtype, f"mixed {dtype} {label}")
