@@ -1,30 +1,39 @@
 // Prefill attention on the 5th-generation tensor cores (tcgen05) for bfloat16, head size 64 or 128.
 //
-// Grid (head, query tile, sequence); a tile is 128 consecutive new tokens of one
-// sequence, two threads per token (8 warps), two blocks per SM.  For every block of
-// 64 keys
-//   1. one thread starts TMA tensor copies (cp.async.bulk.tensor.2d, 128-byte swizzle:
-//      the layout the tensor core reads) of the two pages of keys and of values from
-//      the paged cache, two blocks ahead for the keys and one for the values (two
-//      buffers each);
-//   2. S = Q K^T: one thread issues tcgen05.mma (M 128 queries, N 64 keys), the
-//      accumulator lives in tensor memory.  There are two S buffers (TMEM columns 0..63
-//      and 64..127): S of the next block is issued as soon as every thread has read S
-//      of this block, so the tensor core works on it and on the last P V while the
-//      threads are busy with this block's softmax;
-//   3. every thread reads its half row of S from TMEM (tcgen05.ld), and writes its
-//      part of P = exp2(S * scale - m) as bfloat16 into shared memory in the operand
-//      layout.  m is the row's running maximum, raised only when some row of the tile
-//      meets a score more than 2^8 above its own (then every row takes its true
-//      maximum and rescales its output in TMEM with tcgen05.ld / tcgen05.st); weights
-//      up to 2^8 are exact in float32 and as good as any in bfloat16;
-//   4. O += P V: tcgen05.mma with V read as an MN-major operand straight from the
-//      [key][element] tile, accumulated in TMEM columns 128.. over all blocks.
-// Completion of the products is signalled through tcgen05.commit on mbarriers (one for
-// S, one for P V).  Every wait is bounded and ends in an error code, not a hang.
-// The block's shared memory (112.6 KB, two blocks per SM) leaves no room for slack: the
-// dynamic shared memory must start on a multiple of 1024 bytes, else the kernel reports
-// error 6 and does nothing.
+// Grid (head, group of 256 query rows, sequence), one block per SM, 352 threads.  A block holds two
+// query tiles of 128 consecutive new tokens of one sequence.  Warps 0..3 own tile 0 (thread = row),
+// warps 4..7 tile 1; one lane of warp 8 issues the tcgen05.mma of tile 0, one lane of warp 9 those of
+// tile 1, one lane of warp 10 starts every TMA copy.  For every block of 64 keys
+//   1. the keys and the values (two pages each) come from the paged cache by TMA tensor copies
+//      (cp.async.bulk.tensor.2d, 128-byte swizzle: the layout the tensor core reads) into a ring of
+//      TC_STAGES tiles, loaded once for both query tiles; a tile is refilled when a tcgen05.commit
+//      behind its last reader has signalled k_empty / v_empty;
+//   2. S_t = Q_t K^T (M 128 queries, N 64 keys) goes into tensor memory.  S_t has two buffers, and the
+//      product of block j + 2 is issued as soon as the tile's threads hold S_t of block j in their
+//      registers: a message from the tensor core (tcgen05.commit -> mbarrier) takes longer to arrive
+//      than a block's softmax, so the answer must be on its way two blocks ahead;
+//   3. a thread reads its row of S_t (tcgen05.ld, 64 scores), and writes P_t = exp2(S_t * scale - m)
+//      as bfloat16 into shared memory in the operand layout (two P buffers per tile, so that nobody
+//      waits for the product that read the last one).  m is the row's running maximum, raised only
+//      when some row of the warp meets a score more than 2^8 above its own (then the warp's rows take
+//      their true maxima and rescale their output in tensor memory with tcgen05.ld / tcgen05.st);
+//      weights up to 2^8 are exact in float32 and as good as any in bfloat16.  No thread exchanges
+//      anything with another, and there is no block-wide barrier in the loop;
+//   4. O_t += P_t V: tcgen05.mma with V read as an MN-major operand straight from the [key][element]
+//      tile, accumulated in tensor memory over all blocks.
+// Everything is handed over through mbarriers:
+//   s_full[t][b]  (tcgen05.commit)  S_t of a block is in tensor memory, in S buffer b
+//   s_read[t][b]  (4 arrivals, one per warp)  the tile's threads hold it in registers: the buffer may be overwritten
+//   p_ready[t][b] (4 arrivals)      the tile's threads have written P_t into P buffer b
+//   pv_done[t][b] (tcgen05.commit)  O_t holds the block whose P_t was in buffer b: that buffer and O_t may be touched
+//   k_full[s], v_full[s] (TMA)      a key / value tile has landed in stage s
+//   k_empty[s], v_empty[s] (tcgen05.commit of both tiles)  both tiles' products have read stage s
+// Every barrier belongs to one buffer; a barrier waited on by parity is never two phases ahead of a
+// waiter, because its next phase needs something that waiter does after the wait.  Every wait is
+// bounded by time and ends in an error code (5), not a hang.
+// Tensor memory (512 columns): S_t buffer b at column (2 t + b) * 64, O_0 and O_1 at 256 and 384.
+// Shared memory (224 KB at head size 128) leaves no room for slack: the dynamic shared memory must
+// start on a multiple of 1024 bytes (the swizzle's period), else the kernel reports error 6.
 //
 // Token t of sequence b: q row seq_start[b] + t, position seq_len[b] - n_b + t;
 // it sees keys max(0, pos-window+1)..pos.  A query's result depends on its position
@@ -44,8 +53,7 @@ static_assert(RI_HEAD_DIM == 64 || RI_HEAD_DIM == 128, "tcgen05 prefill attentio
 
 #define TC_DH RI_HEAD_DIM
 #define TC_PAGE 32
-#define TC_BM 128                       // queries per block
-#define TC_THREADS 256                  // two threads per query row
+#define TC_BM 128                       // queries per tile
 #define TC_BN 64                        // keys per step
 #define TC_SLABS (TC_DH / 64)           // 64-element (128-byte) slabs along the head
 #define TC_Q_SLAB (TC_BM * 128)         // a slab of the query tile: 128 rows of 128 bytes
@@ -53,24 +61,7 @@ static_assert(RI_HEAD_DIM == 64 || RI_HEAD_DIM == 128, "tcgen05 prefill attentio
 #define TC_Q_BYTES (TC_SLABS * TC_Q_SLAB)
 #define TC_KV_BYTES (TC_SLABS * TC_KV_SLAB)
 #define TC_P_BYTES (TC_BM * 128)        // P [128 x 64 keys]: one slab
-#define TC_TMEM_COLS 256                // S: columns 0..63 and 64..127, O: columns 128..128+Dh-1
-#define TC_O_COL (2 * TC_BN)
 #define TC_LAZY 8.0f                    // log2 of how far a score may exceed the running maximum
-
-// dynamic shared memory, 1024-byte aligned (swizzle atoms):
-//   q | k0 | k1 | v0 | v1 | p      then the small things
-struct TcTail {
-    unsigned long long s_bar, pv_bar, p_bar, k_bar[2], v_bar[2];
-    unsigned tmem_base;
-    int dead;
-    float rowmax[128];                // exchange between the two threads of a row
-};
-#define TC_OFF_Q 0
-#define TC_OFF_K (TC_OFF_Q + TC_Q_BYTES)
-#define TC_OFF_V (TC_OFF_K + 2 * TC_KV_BYTES)
-#define TC_OFF_P (TC_OFF_V + 2 * TC_KV_BYTES)
-#define TC_OFF_TAIL (TC_OFF_P + TC_P_BYTES)
-#define TC_SMEM_BYTES (TC_OFF_TAIL + 576)
 
 // The swizzled operand layout: a tile is cut into slabs of 64 elements (128 bytes) along its rows;
 // inside a slab rows are 128 bytes apart and the 16-byte chunk c of a row sits at chunk position
@@ -119,6 +110,19 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
 #pragma unroll
     for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
 }
+// the same load without the wait: the caller issues several and then tmem_ld_wait() once
+__device__ __forceinline__ void tmem_ld32_start(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ bool tc_mbar_wait(unsigned long long* bar, unsigned parity) { return ri_mbar_wait(bar, parity); }
 
 // A piece of a row of a [rows x Dh] tile from global memory into the swizzled layout: `chunks`
@@ -158,8 +162,35 @@ __device__ __forceinline__ void tc_tma_2d(void* dst, const CUtensorMap* map, int
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
                  ::"r"(smem_u32(dst)), "l"((unsigned long long)map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
-// block-wide barrier that also tells every thread whether any thread's predicate was set
-__device__ __forceinline__ bool sync_or(bool pred) { return __syncthreads_or(pred ? 1 : 0) != 0; }
+// sm_100 arithmetic that halves the instruction count of the softmax: a maximum of three, and float32 pairs
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long pack2(float a, float b) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long r, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;\n" : "=f"(a), "=f"(b) : "l"(r));
+}
+__device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long fadd2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+// two non-negative finite floats to bfloat16 (round to nearest, ties up) with integer instructions: the
+// conversion instruction shares a pipe with ex2, which is the busiest one here
+__device__ __forceinline__ unsigned pack_bf16_alu(float lo, float hi) {
+    return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
+}
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
@@ -202,260 +233,330 @@ __device__ __forceinline__ void tc_load_tile(unsigned char* tile, const CUtensor
     }
 }
 
-// 256 threads: thread t works on query row t % 128; threads t and t + 128 share a row, the first
-// takes keys 0..31 of a block and the first half of the output elements, the second the rest.
-// Two blocks fit on an SM: while one waits for the tensor core the other does its softmax.
-__global__ void __launch_bounds__(TC_THREADS, 2)
+#define TC_TILES 2
+#define TC_THREADS (32 * (4 * TC_TILES + TC_TILES + 1))
+#define TC_Q_TILE_BYTES (TC_SLABS * TC_Q_SLAB)
+#define TC_OFF_Q 0
+#ifndef TC_STAGES
+#define TC_STAGES (TC_DH == 128 ? 3 : 6)     // key and value tiles in flight or in use
+#endif
+#define TC_OFF_K (TC_OFF_Q + TC_TILES * TC_Q_TILE_BYTES)
+#define TC_OFF_V (TC_OFF_K + TC_STAGES * TC_KV_BYTES)
+#define TC_OFF_P (TC_OFF_V + TC_STAGES * TC_KV_BYTES)
+#define TC_OFF_TAIL (TC_OFF_P + TC_TILES * 2 * TC_P_BYTES)      // two P buffers per tile
+struct TcTail {
+    unsigned long long s_full[2][2], s_read[2][2], p_ready[2][2], pv_done[2][2], k_full[TC_STAGES], v_full[TC_STAGES], k_empty[TC_STAGES], v_empty[TC_STAGES];
+    unsigned tmem_base;
+    volatile int dead;
+};
+#define TC_SMEM_BYTES (TC_OFF_TAIL + 384)
+#define TC_TMEM_COLS 512
+#define TC_S_COL(t, b) (((t) * 2 + (b)) * TC_BN)       // two S buffers per tile
+#define TC_O_COL(t) (4 * TC_BN + (t) * 128)
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
 attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ CUtensorMap map_k,
-                            const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
-                            const int* __restrict__ page_table, const int* __restrict__ seq_slot,
-                            const int* __restrict__ seq_start, const int* __restrict__ seq_len, int H, int KV, int mpps,
-                            int num_pages, float scale_log2, int window, int* __restrict__ err) {
+                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
+                             const int* __restrict__ page_table, const int* __restrict__ seq_slot,
+                             const int* __restrict__ seq_start, const int* __restrict__ seq_len, int H, int KV, int mpps,
+                             int num_pages, float scale_log2, int window, int* __restrict__ err) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    if (smem_u32(smem) & 1023u) {                                  // see the note on shared memory at the top
+    if (smem_u32(smem) & 1023u) {
         if (threadIdx.x == 0) atomicExch(err, 6);
         return;
     }
     TcTail& tail = *reinterpret_cast<TcTail*>(smem + TC_OFF_TAIL);
-    // blocks start in the order of blockIdx.x, then y: heads vary fastest, so the late tiles of all
-    // heads, which see the most keys, start first
     const int b = blockIdx.z, h = blockIdx.x;
     const int t_begin = seq_start[b], n_new = seq_start[b + 1] - t_begin;
-    const int tiles = (n_new + TC_BM - 1) / TC_BM;
-    const int tile = (int)gridDim.y - 1 - (int)blockIdx.y;
-    if (tile >= tiles) return;
+    constexpr int ROWS = TC_TILES * TC_BM;
+    const int groups = (n_new + ROWS - 1) / ROWS;
+    const int group = (int)gridDim.y - 1 - (int)blockIdx.y;        // late rows, which see the most keys, first
+    if (group >= groups) return;
     const int len = seq_len[b];
-    const int r_base = tile * TC_BM;
-    const int rows = min(TC_BM, n_new - r_base);
+    const int r_base = group * ROWS;
+    const int rows = min(ROWS, n_new - r_base);                    // query rows of this block (both tiles)
+    const int n_tiles = rows > TC_BM ? 2 : 1;
     const int pos_first = len - n_new + r_base, pos_last = pos_first + rows - 1;
     const int key_lo = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
     const int kb_lo = key_lo / TC_BN, kb_hi = pos_last / TC_BN;
+    const int n_blocks = kb_hi - kb_lo + 1;
     const int kvh = h / (H / KV);
     const int* table = page_table + (size_t)seq_slot[b] * mpps;
-    const int tid = threadIdx.x, warp = tid >> 5;
-    const int row = tid & (TC_BM - 1), half = tid >> 7;            // my query row, my half of keys / elements
-    const int my_pos = pos_first + row;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool mma_warp = warp >= 4 * TC_TILES && warp < 5 * TC_TILES, tma_warp = warp == 5 * TC_TILES;
+    const bool control = mma_warp || tma_warp;
     unsigned char* k_tiles = smem + TC_OFF_K;
     unsigned char* v_tiles = smem + TC_OFF_V;
 
-    // ---- set-up: tensor memory, the barriers, the first copies ----------------------------------------
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
                      ::"r"(smem_u32(&tail.tmem_base)), "r"(TC_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
-    if (tid == 0) {
+    if (tma_warp && lane == 0) {
         asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_v) : "memory");
-        unsigned long long* bars[6] = {&tail.s_bar, &tail.pv_bar, &tail.k_bar[0], &tail.k_bar[1], &tail.v_bar[0], &tail.v_bar[1]};
 #pragma unroll
-        for (int i = 0; i < 6; i++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(bars[i])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(&tail.p_bar)), "r"(TC_THREADS));
+        for (int i = 0; i < 2; i++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&tail.s_full[i][0])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&tail.s_full[i][1])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&tail.pv_done[i][0])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&tail.pv_done[i][1])));
+#pragma unroll
+            for (int b2 = 0; b2 < 2; b2++) {
+                asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(&tail.p_ready[i][b2])), "r"(TC_BM / 32));
+                asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(&tail.s_read[i][b2])), "r"(TC_BM / 32));
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < TC_STAGES; i++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&tail.k_full[i])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&tail.v_full[i])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(&tail.k_empty[i])), "r"(n_tiles));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(&tail.v_empty[i])), "r"(n_tiles));
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         tail.dead = 0;
-        const TcPages first = tc_pages(table, kb_lo, len, num_pages, err);
-        tc_load_tile(k_tiles, &map_k, first, kvh, KV, &tail.k_bar[0]);
-        tc_load_tile(v_tiles, &map_v, first, kvh, KV, &tail.v_bar[0]);
-        if (kb_lo < kb_hi) {
-            const TcPages second = tc_pages(table, kb_lo + 1, len, num_pages, err);
-            tc_load_tile(k_tiles + TC_KV_BYTES, &map_k, second, kvh, KV, &tail.k_bar[1]);
+        // the first blocks of keys and values, one per stage
+        for (int j = 0; j < TC_STAGES && j < n_blocks; j++) {
+            const TcPages pg = tc_pages(table, kb_lo + j, len, num_pages, err);
+            tc_load_tile(k_tiles + j * TC_KV_BYTES, &map_k, pg, kvh, KV, &tail.k_full[j]);
+            tc_load_tile(v_tiles + j * TC_KV_BYTES, &map_v, pg, kvh, KV, &tail.v_full[j]);
         }
     }
-    {
-        const int r = tid >> 1;
+    if (!control) {
+        // the queries: a thread copies its own row (zeros past the tile's rows)
+        const int r = tid;                                          // row of the block, 0..255
         const bool ok = r < rows;
-        copy_row_piece(smem + TC_OFF_Q, TC_Q_SLAB, r, (tid & 1) * (TC_DH / 16), TC_DH / 16,
+        copy_row_piece(smem + TC_OFF_Q + (r >> 7) * TC_Q_TILE_BYTES, TC_Q_SLAB, r & 127, 0, TC_DH / 8,
                        q + ((size_t)(t_begin + r_base + (ok ? r : 0)) * H + h) * TC_DH, ok);
+        cp_async_commit();
+        cp_async_wait<0>();
+        fence_async_smem();
     }
-    cp_async_commit();
-    cp_async_wait<0>();
-    fence_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = tail.tmem_base;
-    const unsigned tmem_row = tmem + ((unsigned)((warp & 3) * 32) << 16);      // this warp's 32 lanes
-    const unsigned q_addr = smem_u32(smem + TC_OFF_Q), p_addr = smem_u32(smem + TC_OFF_P);
     constexpr unsigned IDESC_QK = instr_desc(TC_BM, TC_BN, 0);
     constexpr unsigned IDESC_PV = instr_desc(TC_BM, TC_DH, 1);
-    constexpr int OW = TC_DH / 2;                                  // output elements per thread
-    constexpr int SW = TC_BN / 2;                                  // scores per thread (32)
 
-    // Four threads of four different warps share the side work, so that no warp falls far behind the others:
-    // thread 0 issues Q K^T, thread 32 P V, thread 64 copies keys, thread 96 copies values.  The copying threads
-    // look the pages up one block before they need them.
-    const bool qk_thread = tid == 0, pv_thread = tid == 32, k_thread = tid == 64, v_thread = tid == 96;
-    TcPages ahead;                                                 // k_thread: pages of block kb + 2; v_thread: of block kb + 1
-    ahead.id[0] = ahead.id[1] = -1;
-    if (k_thread && kb_lo + 1 < kb_hi) ahead = tc_pages(table, kb_lo + 2, len, num_pages, err);
-    if (v_thread && kb_lo < kb_hi) ahead = tc_pages(table, kb_lo + 1, len, num_pages, err);
-
-    // qk_thread: S[j & 1] = Q K^T for the j-th block of this tile, once its keys have arrived
-    auto issue_qk = [&](int j) {
-        if (!tc_mbar_wait(&tail.k_bar[j & 1], (unsigned)((j >> 1) & 1))) { atomicExch(err, 5); tail.dead = 1; }
-        tc_fence_after();
-        const unsigned k_addr = smem_u32(k_tiles + (j & 1) * TC_KV_BYTES);
-#pragma unroll
-        for (int i = 0; i < TC_DH / 16; i++) {
-            unsigned qo = (unsigned)((i >> 2) * TC_Q_SLAB + (i & 3) * 32), ko = (unsigned)((i >> 2) * TC_KV_SLAB + (i & 3) * 32);
-            umma_bf16(tmem + (j & 1) * TC_BN, smem_desc(q_addr + qo, 16, 1024), smem_desc(k_addr + ko, 16, 1024), IDESC_QK, i > 0);
-        }
-        umma_commit(&tail.s_bar);
-    };
-    if (qk_thread) issue_qk(0);
-
-    float m = -FLT_MAX, l = 0.0f;                                  // m: in units of scaled log2 scores
-    bool dead = false;
-    int it = 0;                                                    // blocks done
-    for (int kb = kb_lo; kb <= kb_hi; kb++, it++) {
-        const int buf = it & 1;
-        unsigned char* v_tile = v_tiles + buf * TC_KV_BYTES;
-        // ---- S of this block is done (its key tile is free) ------------------------------------------------
-        if (!tc_mbar_wait(&tail.s_bar, (unsigned)buf)) { atomicExch(err, 5); tail.dead = 1; }
-        tc_fence_after();
-        // the keys of the block after the next go into the tile that S of this block has just finished with
-        if (k_thread && kb + 1 < kb_hi) {
-            tc_load_tile(k_tiles + buf * TC_KV_BYTES, &map_k, ahead, kvh, KV, &tail.k_bar[buf]);
-            if (kb + 2 < kb_hi) ahead = tc_pages(table, kb + 3, len, num_pages, err);
-        }
-        // ---- my 32 scores of the row: mask, maximum ------------------------------------------------------
-        const int k0 = kb * TC_BN + half * SW;                     // my first key
-        const bool edge = (kb * TC_BN + TC_BN - 1 > pos_first) || (window > 0 && kb * TC_BN < pos_last - window + 1);
-        float s[SW];
-        tmem_ld32(tmem_row + buf * TC_BN + half * SW, s);
-        if (edge) {
-#pragma unroll
-            for (int i = 0; i < SW; i++) {
-                int key = k0 + i;
-                bool vis = key <= my_pos && (window <= 0 || key > my_pos - window);
-                s[i] = vis ? s[i] : -FLT_MAX;
+    if (tma_warp) {
+        if (lane == 0) {
+            // the first blocks are on their way; block j goes into the buffers of block j - TC_STAGES once they are free
+            bool dead = false;
+            for (int j = TC_STAGES; j < n_blocks && !dead; j++) {
+                const int buf = j % TC_STAGES;
+                const unsigned parity = (unsigned)((j / TC_STAGES - 1) & 1);
+                const TcPages pg = tc_pages(table, kb_lo + j, len, num_pages, err);       // under the wait below
+                if (!tc_mbar_wait(&tail.k_empty[buf], parity)) { atomicExch(err, 5); tail.dead = 1; dead = true; }
+                tc_load_tile(k_tiles + buf * TC_KV_BYTES, &map_k, pg, kvh, KV, &tail.k_full[buf]);
+                if (!dead && !tc_mbar_wait(&tail.v_empty[buf], parity)) { atomicExch(err, 5); tail.dead = 1; dead = true; }
+                tc_load_tile(v_tiles + buf * TC_KV_BYTES, &map_v, pg, kvh, KV, &tail.v_full[buf]);
             }
         }
-        float mx4[4] = {-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX};   // four chains instead of one of 32 steps
+    } else if (mma_warp) {
+        const int t = warp - 4 * TC_TILES;                          // one issuing lane per query tile
+        if (lane == 0 && t < n_tiles) {
+            // the operand descriptors, made once (a descriptor holds the address in units of 16 bytes)
+            const unsigned long long q_base = smem_desc(smem_u32(smem + TC_OFF_Q + t * TC_Q_TILE_BYTES), 16, 1024);
+            const unsigned long long k_base = smem_desc(smem_u32(k_tiles), 16, 1024);
+            const unsigned long long p_base = smem_desc(smem_u32(smem + TC_OFF_P + t * 2 * TC_P_BYTES), 16, 1024);
+            const unsigned long long v_base = smem_desc(smem_u32(v_tiles), TC_KV_SLAB, 1024);
+            unsigned long long qd[TC_DH / 16], kd[TC_DH / 16], pd[TC_BN / 16], vd[TC_BN / 16];      // kd, vd: stage 0
 #pragma unroll
-        for (int i = 0; i < SW; i++) mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
-        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        mx = mx == -FLT_MAX ? -FLT_MAX : mx * scale_log2;          // scale > 0: the maximum of the scaled scores
-        // every thread has read S; does any row have to raise its maximum?
-        tc_fence_before();
-        const bool raise = sync_or(mx > m + TC_LAZY || (m == -FLT_MAX && mx != -FLT_MAX));
-        // a wait that ran out (this block's by any thread, thread 0's of the block before) is known to all here
-        dead = tail.dead != 0;
-        if (dead) break;
-        // S of the next block goes into the other S buffer, which every thread has read by now.  It is started
-        // only here, behind the block-wide barrier: every thread has then seen this block's phase of the S
-        // barrier, so that barrier is never two phases ahead of a thread that waits on it by parity.
-        if (qk_thread && kb < kb_hi) issue_qk(it + 1);
-        // ---- P V of the block before is done: P, its value tile and the output are free -------------------
-        if (it > 0) {
-            if (!tc_mbar_wait(&tail.pv_bar, (unsigned)((it - 1) & 1))) { atomicExch(err, 5); tail.dead = 1; }
-            tc_fence_after();
-        }
-        if (v_thread && kb < kb_hi) {
-            tc_load_tile(v_tiles + (buf ^ 1) * TC_KV_BYTES, &map_v, ahead, kvh, KV, &tail.v_bar[buf ^ 1]);
-            if (kb + 1 < kb_hi) ahead = tc_pages(table, kb + 2, len, num_pages, err);
-        }
-        if (raise) {
-            // the row's two threads agree on its maximum: the second tells the first, the first answers
-            if (half) tail.rowmax[row] = mx;
-            __syncthreads();
-            float m_new = 0.0f;
-            if (!half) {
-                m_new = fmaxf(m, fmaxf(mx, tail.rowmax[row]));
-                tail.rowmax[row] = m_new;
+            for (int i = 0; i < TC_DH / 16; i++) {
+                qd[i] = q_base + (unsigned)(((i >> 2) * TC_Q_SLAB + (i & 3) * 32) >> 4);
+                kd[i] = k_base + (unsigned)(((i >> 2) * TC_KV_SLAB + (i & 3) * 32) >> 4);
             }
-            __syncthreads();
-            if (half) m_new = tail.rowmax[row];
-            const float corr = m_new == m ? 1.0f : ((m == -FLT_MAX) ? 0.0f : ex2_approx(m - m_new));
-            m = m_new;
-            l *= corr;
-            // the output so far, in tensor memory: the loads and stores are the whole warp's, so all its rows go along
-            if (it > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll
-                for (int c = 0; c < OW / 32; c++) {
-                    float ob[32];
-                    tmem_ld32(tmem_row + TC_O_COL + half * OW + c * 32, ob);
+            for (int i = 0; i < TC_BN / 16; i++) {
+                pd[i] = p_base + (unsigned)((i * 32) >> 4);
+                vd[i] = v_base + (unsigned)((i * 16 * 128) >> 4);
+            }
+            const unsigned o_col = tmem + TC_O_COL(t);
+            bool dead = false;
+            auto wait = [&](unsigned long long* bar, unsigned parity) {
+                if (!dead && !tc_mbar_wait(bar, parity)) { atomicExch(err, 5); tail.dead = 1; dead = true; }
+            };
+            // S_t of block jb = Q_t K^T into S buffer jb & 1, once its keys have landed
+            auto issue_qk = [&](int jb) {
+                const int st = jb % TC_STAGES;
+                wait(&tail.k_full[st], (unsigned)((jb / TC_STAGES) & 1));
+                tc_fence_after();
+                const unsigned long long off = (unsigned long long)(st * (TC_KV_BYTES >> 4));
+                const unsigned s_col = tmem + TC_S_COL(t, jb & 1);
 #pragma unroll
-                    for (int i = 0; i < 32; i++) ob[i] *= corr;
-                    tmem_st32(tmem_row + TC_O_COL + half * OW + c * 32, ob);
+                for (int i = 0; i < TC_DH / 16; i++) umma_bf16(s_col, qd[i], kd[i] + off, IDESC_QK, i > 0);
+                umma_commit(&tail.s_full[t][jb & 1]);
+                umma_commit(&tail.k_empty[st]);                          // this tile is done with the keys of block jb
+            };
+            issue_qk(0);
+            if (n_blocks > 1) issue_qk(1);
+            for (int j = 0; j < n_blocks && !dead; j++) {
+                const int st = j % TC_STAGES;
+                // as soon as the tile's threads hold S_t of block j in their registers, its buffer takes S_t of block
+                // j + 2: the tensor core's answer has two blocks' time to come back
+                if (j + 2 < n_blocks) {
+                    wait(&tail.s_read[t][j & 1], (unsigned)((j >> 1) & 1));
+                    issue_qk(j + 2);
                 }
-                tmem_st_wait();
+                // P_t of block j is written: O_t += P_t V
+                wait(&tail.p_ready[t][j & 1], (unsigned)((j >> 1) & 1));
+                wait(&tail.v_full[st], (unsigned)((j / TC_STAGES) & 1));
+                tc_fence_after();
+                {
+                    const unsigned long long off = (unsigned long long)(st * (TC_KV_BYTES >> 4));
+                    const unsigned long long poff = (unsigned long long)((j & 1) * (TC_P_BYTES >> 4));
+#pragma unroll
+                    for (int i = 0; i < TC_BN / 16; i++) umma_bf16(o_col, pd[i] + poff, vd[i] + off, IDESC_PV, (j > 0 || i > 0) ? 1u : 0u);
+                }
+                umma_commit(&tail.pv_done[t][j & 1]);
+                umma_commit(&tail.v_empty[st]);                           // this tile is done with the values of block j
             }
         }
-        // ---- P = exp2(S * scale - m) as bfloat16 into the operand layout; sum --------------------------
-        {
+    } else if (warp < 4 * n_tiles) {
+        // ---- a query row ------------------------------------------------------------------------------------
+        const int t = warp >> 2, row = tid & (TC_BM - 1);
+        const int my_pos = pos_first + t * TC_BM + row;
+        const unsigned tmem_row = tmem + ((unsigned)((warp & 3) * 32) << 16);
+        unsigned char* p_rows = smem + TC_OFF_P + t * 2 * TC_P_BYTES + row * 128;
+        float m = -FLT_MAX, l = 0.0f;
+        bool dead = false;
+        for (int j = 0; j < n_blocks; j++) {
+            const int kb = kb_lo + j;
+            if (!dead && !tc_mbar_wait(&tail.s_full[t][j & 1], (unsigned)((j >> 1) & 1))) { atomicExch(err, 5); tail.dead = 1; }
+            dead = dead || tail.dead != 0;
+            tc_fence_after();
+            float s[TC_BN];
+            {
+                unsigned a[32], c[32];
+                tmem_ld32_start(tmem_row + TC_S_COL(t, j & 1), a);
+                tmem_ld32_start(tmem_row + TC_S_COL(t, j & 1) + 32, c);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    s[i] = __uint_as_float(a[i]);
+                    s[32 + i] = __uint_as_float(c[i]);
+                }
+            }
+            // S_t is in my registers: the next S_t may be written
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&tail.s_read[t][j & 1])) : "memory");
+            const bool edge = (kb * TC_BN + TC_BN - 1 > pos_first) || (window > 0 && kb * TC_BN < pos_last - window + 1);
+            if (edge) {
+#pragma unroll
+                for (int i = 0; i < TC_BN; i++) {
+                    int key = kb * TC_BN + i;
+                    bool vis = key <= my_pos && (window <= 0 || key > my_pos - window);
+                    s[i] = vis ? s[i] : -FLT_MAX;
+                }
+            }
+            float mx4[4];                                         // four chains of three-way maxima
+#pragma unroll
+            for (int c = 0; c < 4; c++) mx4[c] = max3(s[c * 16], s[c * 16 + 1], s[c * 16 + 2]);
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+#pragma unroll
+                for (int i = 3; i < 15; i += 2) mx4[c] = max3(mx4[c], s[c * 16 + i], s[c * 16 + i + 1]);
+                mx4[c] = fmaxf(mx4[c], s[c * 16 + 15]);
+            }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            mx = mx == -FLT_MAX ? -FLT_MAX : mx * scale_log2;      // scale > 0
+            unsigned char* p_row = p_rows + (j & 1) * TC_P_BYTES;       // P_t has two buffers that take turns
+            const bool raise = mx > m + TC_LAZY || (m == -FLT_MAX && mx != -FLT_MAX);
+            if (__any_sync(0xffffffffu, raise)) {
+                // some row of this warp moves its maximum far: every row of the warp takes its true maximum
+                const float m_new = fmaxf(m, mx);
+                const float corr = m_new == m ? 1.0f : ((m == -FLT_MAX) ? 0.0f : ex2_approx(m - m_new));
+                m = m_new;
+                l *= corr;
+                if (j > 0) {
+                    // the output is rescaled in tensor memory: P V of the block before must be done
+                    if (!dead && !tc_mbar_wait(&tail.pv_done[t][(j - 1) & 1], (unsigned)(((j - 1) >> 1) & 1))) { atomicExch(err, 5); tail.dead = 1; dead = true; }
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < TC_DH / 32; c++) {
+                        float ob[32];
+                        tmem_ld32(tmem_row + TC_O_COL(t) + c * 32, ob);
+#pragma unroll
+                        for (int i = 0; i < 32; i++) ob[i] *= corr;
+                        tmem_st32(tmem_row + TC_O_COL(t) + c * 32, ob);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            // this P buffer was read by P V of the block before the last: long done, as a rule
+            if (j > 1) {
+                if (!dead && !tc_mbar_wait(&tail.pv_done[t][j & 1], (unsigned)(((j - 2) >> 1) & 1))) { atomicExch(err, 5); tail.dead = 1; dead = true; }
+            }
             const float neg_m = (m == -FLT_MAX) ? 0.0f : -m;
-            unsigned char* p_row = smem + TC_OFF_P + row * 128;
-            float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (edge) {
+                float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int c = 0; c < SW / 8; c++) {
-                float p[8];
+                for (int c = 0; c < TC_BN / 8; c++) {
+                    float p[8];
 #pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    float x = s[c * 8 + e];
-                    p[e] = (edge && x == -FLT_MAX) ? 0.0f : ex2_approx(fmaf(x, scale_log2, neg_m));
-                    l4[e & 3] += p[e];
+                    for (int e = 0; e < 8; e++) {
+                        float x = s[c * 8 + e];
+                        p[e] = x == -FLT_MAX ? 0.0f : ex2_approx(fmaf(x, scale_log2, neg_m));
+                        l4[e & 3] += p[e];
+                    }
+                    *(uint4*)(p_row + ((c ^ (row & 7)) << 4)) =
+                        make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
                 }
-                const int chunk = half * (SW / 8) + c;             // 16-byte chunk of the 64-key row
-                *(uint4*)(p_row + ((chunk ^ (row & 7)) << 4)) =
-                    make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
-            }
-            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-        }
-        // the values of this block have arrived (asked for a whole block ago)
-        if (!tc_mbar_wait(&tail.v_bar[buf], (unsigned)((it >> 1) & 1))) { atomicExch(err, 5); tail.dead = 1; }
-        if (kb * TC_BN + TC_BN > len) {
-            // rows past the sequence's end hold whatever the pool holds there (or what the tile held before):
-            // zero them, a weight of zero times not-a-number would still be not-a-number
-            const int r = tid >> 2, first_bad = len - kb * TC_BN;
-            if (r >= first_bad) {
+                l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+            } else {
+                // no key of the block is masked: pairs of float32 for the scaling and the sum
+                const unsigned long long sc2 = pack2(scale_log2, scale_log2), nm2 = pack2(neg_m, neg_m);
+                unsigned long long l2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
 #pragma unroll
-                for (int sl = 0; sl < TC_SLABS; sl++)
+                for (int c = 0; c < TC_BN / 8; c++) {
+                    unsigned w[4];
 #pragma unroll
-                    for (int c = 0; c < 2; c++)
-                        *(uint4*)(v_tile + sl * TC_KV_SLAB + r * 128 + (((tid & 3) * 2 + c) << 4)) = make_uint4(0, 0, 0, 0);
+                    for (int e = 0; e < 4; e++) {
+                        float x0, x1;
+                        unpack2(ffma2(pack2(s[c * 8 + 2 * e], s[c * 8 + 2 * e + 1]), sc2, nm2), x0, x1);
+                        const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+                        l2[e & 1] = fadd2(l2[e & 1], pack2(p0, p1));
+                        w[e] = pack_bf16_alu(p0, p1);
+                    }
+                    *(uint4*)(p_row + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+                float a0, a1, b0, b1;
+                unpack2(l2[0], a0, a1);
+                unpack2(l2[1], b0, b1);
+                l += (a0 + a1) + (b0 + b1);
             }
-        }
-        // my part of P (and of the value tile) is written: tell the thread that issues P V and go on; nobody
-        // waits here, the next block-wide barrier is the vote on the maximum of the next block
-        fence_async_smem();
-        tc_fence_before();
-        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&tail.p_bar)) : "memory");
-        // ---- O += P V --------------------------------------------------------------------------------------
-        if (pv_thread) {
-            if (!tc_mbar_wait(&tail.p_bar, (unsigned)buf)) { atomicExch(err, 5); tail.dead = 1; }
-            tc_fence_after();
-            const unsigned v_addr = smem_u32(v_tile);
+            if (kb * TC_BN + TC_BN > len) {
+                // value rows past the sequence's end may hold anything: the first tile's threads zero them (the tile has
+                // landed: the control lane waits for it before the product, but these writes must come before that too)
+                if (t == 0) {
+                    if (!dead && !tc_mbar_wait(&tail.v_full[j % TC_STAGES], (unsigned)((j / TC_STAGES) & 1))) { atomicExch(err, 5); tail.dead = 1; dead = true; }
+                    unsigned char* v_tile = v_tiles + (j % TC_STAGES) * TC_KV_BYTES;
+                    const int first_bad = len - kb * TC_BN;
+                    for (int r = first_bad + (row >> 3); r < TC_BN; r += TC_BM / 8)
 #pragma unroll
-            for (int j = 0; j < TC_BN / 16; j++) {
-                umma_bf16(tmem + TC_O_COL, smem_desc(p_addr + j * 32, 16, 1024),
-                          smem_desc(v_addr + j * 16 * 128, TC_KV_SLAB, 1024), IDESC_PV, (it > 0 || j > 0) ? 1u : 0u);
+                        for (int sl = 0; sl < TC_SLABS; sl++)
+                            *(uint4*)(v_tile + sl * TC_KV_SLAB + r * 128 + ((row & 7) << 4)) = make_uint4(0, 0, 0, 0);
+                }
             }
-            umma_commit(&tail.pv_bar);
+            fence_async_smem();
+            tc_fence_before();
+            __syncwarp();                                            // one arrival per warp
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&tail.p_ready[t][j & 1])) : "memory");
         }
-    }
-    // ---- the last product is done: out = O / l (l: both halves of the row) --------------------------------
-    if (!dead && it > 0 && !tc_mbar_wait(&tail.pv_bar, (unsigned)((it - 1) & 1))) { atomicExch(err, 5); tail.dead = 1; }
-    tc_fence_after();
-    __syncthreads();
-    dead = tail.dead != 0;
-    if (half) tail.rowmax[row] = l;
-    __syncthreads();
-    if (!half) {
-        l += tail.rowmax[row];
-        tail.rowmax[row] = l;
-    }
-    __syncthreads();
-    if (half) l = tail.rowmax[row];
-    {
-        // every lane of a warp takes part in the loads from tensor memory, whether its row is one of the tile's or not
-        const bool mine = row < rows && !dead;
+        // ---- out = O / l ----------------------------------------------------------------------------------------
+        if (!dead && !tc_mbar_wait(&tail.pv_done[t][(n_blocks - 1) & 1], (unsigned)(((n_blocks - 1) >> 1) & 1))) { atomicExch(err, 5); tail.dead = 1; dead = true; }
+        tc_fence_after();
+        const bool mine = t * TC_BM + row < rows && !dead;
         const float inv = 1.0f / l;
-        bf16* dst = out + ((size_t)(t_begin + r_base + (mine ? row : 0)) * H + h) * TC_DH + half * OW;
+        bf16* dst = out + ((size_t)(t_begin + r_base + (mine ? t * TC_BM + row : 0)) * H + h) * TC_DH;
 #pragma unroll
-        for (int c = 0; c < OW / 32; c++) {
+        for (int c = 0; c < TC_DH / 32; c++) {
             float o[32];
-            tmem_ld32(tmem_row + TC_O_COL + half * OW + c * 32, o);
+            tmem_ld32(tmem_row + TC_O_COL(t) + c * 32, o);        // the whole warp, whether the row is a query or not
             if (mine) {
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {
@@ -518,13 +619,7 @@ extern "C" int ri_attention_prefill_tc(const void* q, const void* k_pool, const 
     RI_REQUIRE(scale > 0.0f, "attention_prefill_tc: the score scale must be positive");
     RI_REQUIRE((((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15) == 0,
                "attention_prefill_tc: q, out and the pools must be 16-byte aligned");
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES);
-        if (e != cudaSuccess) RI_FAIL((int)e, "attention_prefill_tc: %s", cudaGetErrorString(e));
-        configured = true;
-    }
-    dim3 grid(H, (max_new + TC_BM - 1) / TC_BM, seqs);
+    dim3 grid(H, (max_new + TC_TILES * TC_BM - 1) / (TC_TILES * TC_BM), seqs);
     RI_REQUIRE(grid.y <= 65535, "attention_prefill_tc: too many tokens in one sequence of a step");
     RI_REQUIRE((long long)num_pages * KV * TC_PAGE < (1ll << 31), "attention_prefill_tc: a pool of %d pages", num_pages);
     CUtensorMap map_k, map_v;
@@ -532,6 +627,12 @@ extern "C" int ri_attention_prefill_tc(const void* q, const void* k_pool, const 
     if (rc) return rc;
     rc = tc_pool_tensor_map(&map_v, v_pool, (long long)num_pages * KV * TC_PAGE);
     if (rc) return rc;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES);
+        if (e != cudaSuccess) RI_FAIL((int)e, "attention_prefill_tc: %s", cudaGetErrorString(e));
+        configured = true;
+    }
     attention_prefill_tc_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(
         (const bf16*)q, map_k, map_v, (bf16*)out, page_table, seq_slot, seq_start, seq_len,
         H, KV, mpps, num_pages, scale * 1.4426950408889634f, window, err_flag);
