@@ -186,11 +186,6 @@ __device__ __forceinline__ unsigned long long fadd2(unsigned long long a, unsign
     asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
-// two non-negative finite floats to bfloat16 (round to nearest, ties up) with integer instructions: the
-// conversion instruction shares a pipe with ex2, which is the busiest one here
-__device__ __forceinline__ unsigned pack_bf16_alu(float lo, float hi) {
-    return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
-}
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
@@ -520,7 +515,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
                         unpack2(ffma2(pack2(s[c * 8 + 2 * e], s[c * 8 + 2 * e + 1]), sc2, nm2), x0, x1);
                         const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
                         l2[e & 1] = fadd2(l2[e & 1], pack2(p0, p1));
-                        w[e] = pack_bf16_alu(p0, p1);
+                        w[e] = pack_bf16(p0, p1);
                     }
                     *(uint4*)(p_row + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }

@@ -95,13 +95,8 @@ __device__ __forceinline__ bool ri_mbar_wait(unsigned long long* bar, unsigned p
     unsigned long long start = 0;
     for (int i = 0;; i++) {
         unsigned ok;
-#ifdef RI_MBAR_TEST_WAIT
-        asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(ok) : "r"(a), "r"(parity) : "memory");
-#else
         asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
                      : "=r"(ok) : "r"(a), "r"(parity) : "memory");
-#endif
         if (ok) return true;
         if ((i & 63) == 63) {
             unsigned long long now = ri_globaltimer();
