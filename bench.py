@@ -226,14 +226,18 @@ def main() -> int:
     e2e = None
     if not a.skip_e2e:
         llm = ri.LLM(engine=engine)                 # the loaded model and its cache, through the public entry point
+        # one call: the prompts, then Wm decode steps that are not counted and K that are (their times are the
+        # host's, from one step's ids on the host to the next step's), the last at the full context length
         prompts = torch.randint(0, V, (B, ctx0), generator=gen).tolist()
         t_a = time.time()
         res = llm.generate(prompts, max_new_tokens=K + Wm, ignore_eos=True, return_result=True)
         windows.append((t_a, time.time()))
         st = res.stats
-        e2e = {"value": round(st.decode_tokens / st.decode_s, 1), "unit": "tok/s",
+        timed = st.decode_step_s[-K:]
+        e2e = {"value": round(sum(n for _, n in timed) / sum(t for t, _ in timed), 1), "unit": "tok/s",
                "h2d_bytes_per_step": (7 * B + 1) * 4, "d2h_bytes_per_step": B * 4,
-               "prefill_tok_s": round(st.prefill_tokens / st.prefill_s, 1), "steps": st.decode_steps}
+               "prefill_tok_s": round(st.prefill_tokens / st.prefill_s, 1), "steps": len(timed),
+               "warmup_steps": st.decode_steps - len(timed)}
     clocks.stop()
 
     line = {

@@ -28,6 +28,8 @@ class GenerationStats:
     decode_steps: int = 0
     decode_s: float = 0.0
     batches: int = 0
+    # one entry per decode step: (seconds from the end of the step before to this step's ids on the host, tokens)
+    decode_step_s: List[tuple] = field(default_factory=list)
 
 
 @dataclass
@@ -153,6 +155,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int = 64,
                         stats.decode_s += now - t0
                         stats.decode_steps += 1
                         stats.decode_tokens += len(live)
+                        stats.decode_step_s.append((now - t0, len(live)))
                     t0 = now
                     live = [s for s, t in zip(live, toks) if accept(s, t)]
                     if not live:
@@ -189,7 +192,9 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int = 64,
                         now = time.perf_counter()
                         stats.decode_s += now - t0
                         stats.decode_steps += 1
-                        stats.decode_tokens += sum(1 for s in handle.seqs if s.slot >= 0)
+                        n_live = sum(1 for s in handle.seqs if s.slot >= 0)
+                        stats.decode_tokens += n_live
+                        stats.decode_step_s.append((now - t0, n_live))
                         t0 = now
                     for s, t in zip(handle.seqs, toks):
                         if s.slot >= 0:               # else: it had ended, this was its step too many
