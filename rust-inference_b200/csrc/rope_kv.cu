@@ -198,6 +198,125 @@ __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, T* __r
     }
 }
 
+// bfloat16 with 16 bytes per lane: a head of DH elements takes DH / 8 lanes, a warp works on 32 / (DH / 8) heads
+// at a time; the rotation partner of a lane's eight elements sits DH / 16 lanes away.  Used for many tokens
+// (prefill), where the 8-byte loads of the kernel above leave half of the memory bandwidth unused.
+template <int DH>
+__global__ void qk_norm_rope_append_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+                                                  __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool,
+                                                  const int* __restrict__ page_table, const int* __restrict__ tok_seq,
+                                                  const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
+                                                  const float* __restrict__ q_gain, const float* __restrict__ k_gain,
+                                                  float eps, const float2* __restrict__ rope, int rope_rows, int H, int KV,
+                                                  int mpps, int page_size, int num_pages, int write_kv,
+                                                  int* __restrict__ err) {
+    constexpr int LPH = DH / 8;                  // lanes per head
+    constexpr int HPW = 32 / LPH;                // heads per warp at a time
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = lane / LPH, ln = lane % LPH; // which of the warp's heads, which part of it
+    const int heads_total = H + 2 * KV;
+    const __nv_bfloat16* row = qkv + (size_t)t * heads_total * DH;
+    const int d0 = ln * 8;
+    // the loads of the first batch of heads start before anything else is known
+    const int stride = RK_WARPS * HPW * gridDim.y;
+    const int h_first = (blockIdx.y * RK_WARPS + warp) * HPW + sub;
+    uint4 in[RK_UNROLL];
+#pragma unroll
+    for (int u = 0; u < RK_UNROLL; u++) {
+        const int h = h_first + u * stride;
+        if (h < heads_total) in[u] = *(const uint4*)(row + (size_t)h * DH + d0);
+    }
+    const int pos = tok_pos[t];
+    const int slot = seq_slot[tok_seq[t]];
+    int page = -1;
+    if (write_kv) {
+        page = page_table[(size_t)slot * mpps + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicExch(err, 2);
+            page = -1;
+        }
+    }
+    if (rope && (pos < 0 || pos >= rope_rows)) {
+        if (threadIdx.x == 0) atomicExch(err, 3);
+        return;
+    }
+    float cs_c[8], cs_s[8];
+    if (rope) {
+        const float2* cs = rope + (size_t)pos * (DH / 2) + (d0 % (DH / 2));
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+            const float4 c = *(const float4*)(cs + j);           // two (cos, sin) pairs
+            cs_c[j] = c.x;
+            cs_s[j] = (d0 < DH / 2) ? -c.y : c.y;                // low half: a*c - b*s; high half: b*c + a*s
+            cs_c[j + 1] = c.z;
+            cs_s[j + 1] = (d0 < DH / 2) ? -c.w : c.w;
+        }
+    }
+    for (int h0 = h_first, first = 1; h0 < heads_total; h0 += stride * RK_UNROLL, first = 0) {
+        if (!first) {
+#pragma unroll
+            for (int u = 0; u < RK_UNROLL; u++) {
+                const int h = h0 + u * stride;
+                if (h < heads_total) in[u] = *(const uint4*)(row + (size_t)h * DH + d0);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < RK_UNROLL; u++) {
+            const int h = h0 + u * stride;
+            // the lanes of one head go together; a head past the end still takes part in the shuffles below
+            const bool live = h < heads_total;
+            const int which = !live ? 3 : (h < H ? 0 : (h < H + KV ? 1 : 2));
+            __nv_bfloat16* dst = nullptr;
+            if (which == 0) {
+                dst = q_out + ((size_t)t * H + h) * DH;
+            } else if (which < 3 && write_kv && page >= 0) {
+                const int kvh = which == 1 ? h - H : h - H - KV;
+                dst = (which == 1 ? k_pool : v_pool) + (((size_t)page * KV + kvh) * page_size + pos % page_size) * DH;
+            }
+            // (no lane leaves early: the shuffles below are the whole warp's, and its heads may be of different kinds)
+            float x[8];
+            {
+                const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&in[u]);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float2 f = __bfloat1622float2(live ? p2[j] : __nv_bfloat162());
+                    x[2 * j] = f.x;
+                    x[2 * j + 1] = f.y;
+                }
+            }
+            const float* gain = which == 0 ? q_gain : (which == 1 ? k_gain : nullptr);
+            float ss = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) ss += x[j] * x[j];
+#pragma unroll
+            for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (gain) {
+                const float inv = 1.0f / sqrtf(ss / (float)DH + eps);
+#pragma unroll
+                for (int j = 0; j < 8; j++) x[j] = x[j] * inv * gain[d0 + j];
+            }
+            uint4 o;
+            unsigned* ow = reinterpret_cast<unsigned*>(&o);
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                float v0 = x[j], v1 = x[j + 1];
+                if (rope) {
+                    const float o0 = __shfl_xor_sync(0xffffffffu, x[j], LPH / 2);
+                    const float o1 = __shfl_xor_sync(0xffffffffu, x[j + 1], LPH / 2);
+                    v0 = x[j] * cs_c[j] + o0 * cs_s[j];
+                    v1 = x[j + 1] * cs_c[j + 1] + o1 * cs_s[j + 1];
+                }
+                const __nv_bfloat162 pk = __floats2bfloat162_rn(v0, v1);
+                ow[j / 2] = *reinterpret_cast<const unsigned*>(&pk);
+            }
+            if (dst) *(uint4*)(dst + d0) = which == 2 ? in[u] : o;      // values are copied as they are
+        }
+    }
+}
+
 template <typename T, int VEC>
 static void launch_rope_vec(dim3 grid, cudaStream_t stream, const void* qkv, void* q_out, void* k_pool, void* v_pool,
                             const int* page_table, const int* tok_seq, const int* tok_pos, const int* seq_slot,
@@ -234,6 +353,19 @@ extern "C" int ri_qk_norm_rope_append(const void* qkv, void* q_out, void* k_pool
                                                 page_size, num_pages, write_kv, err_flag)
         if (dtype == RI_DTYPE_F32) {
             if (Dh == 64) RI_ROPE_VEC(float, 2); else if (Dh == 128) RI_ROPE_VEC(float, 4); else RI_ROPE_VEC(float, 8);
+        } else if (tokens >= 64) {
+            // many tokens: 16 bytes per lane, several heads per warp at a time
+            const int hpw = 32 / (Dh / 8);
+            int hb = (H + 2 * KV + RK_WARPS * hpw - 1) / (RK_WARPS * hpw);
+            if ((long long)tokens * hb > 2048) hb = 1 > 2048 / tokens ? 1 : 2048 / tokens;    // few blocks per token: the rotary table is read once per warp
+            dim3 grid8(tokens, hb);
+#define RI_ROPE_X8(D) ri_launch_pdl(qk_norm_rope_append_bf16x8_kernel<D>, grid8, dim3(32 * RK_WARPS), 0, stream,            \
+                                    (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,              \
+                                    (__nv_bfloat16*)v_pool, page_table, tok_seq, tok_pos, seq_slot, q_gain, k_gain, eps,   \
+                                    (const float2*)rope_table, rope_rows, H, KV, mpps, page_size, num_pages, write_kv,     \
+                                    err_flag)
+            if (Dh == 64) RI_ROPE_X8(64); else if (Dh == 128) RI_ROPE_X8(128); else RI_ROPE_X8(256);
+#undef RI_ROPE_X8
         } else {
             if (Dh == 64) RI_ROPE_VEC(__nv_bfloat16, 2); else if (Dh == 128) RI_ROPE_VEC(__nv_bfloat16, 4); else RI_ROPE_VEC(__nv_bfloat16, 8);
         }
