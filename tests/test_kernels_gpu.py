@@ -504,3 +504,58 @@ def test_attention_decode_many_sequences(H, KV, Dh, window, seqs, longest):
         close(out[b:b + 1], want, 2e-2, f"decode attention, sequence {b} of length {n}")
     again = ops.attention_decode(dev(q, bt), *args, 2048)           # another grid, the same bits
     assert torch.equal(again, out)
+
+
+def _take_error(ops):
+    flag = ops.error_flag("cuda")
+    torch.cuda.synchronize()
+    code = int(flag.item())
+    flag.zero_()
+    return code
+
+
+def test_kernels_report_indices_they_must_not_follow():
+    """An id outside the vocabulary, a position beyond the rotary table, an unmapped or impossible page: the
+    kernel leaves the access out, sets the error word (1, 3, 2, 4) and goes on; nothing faults."""
+    from rust_inference_b200 import ops
+    from rust_inference_b200.config import RopeSpec
+    from rust_inference_b200.parts import BuildEnv, build_part
+    rng = np.random.default_rng(3)
+    bt = torch.bfloat16
+    assert _take_error(ops) == 0
+    # 1: token id == vocabulary size
+    table = dev(rnd(rng, 50, 64, dtype="bfloat16"), bt)
+    ops.embed(dev(np.array([3, 50, 7]), torch.int32), table)
+    assert _take_error(ops) == 1
+    for Dh, H, KV in ((128, 8, 2), (32, 4, 2)):
+        lens = [70, 33]
+        pt, slots, k, v, k_pool, v_pool = _fill_pools(rng, lens, KV, Dh, "bfloat16", scale=0.5)
+        kp, vp = dev(k_pool, bt), dev(v_pool, bt)
+        i32 = lambda a: dev(np.asarray(a), torch.int32)
+        rope = build_part("position", RopeSpec(head_dim=Dh, theta=1e4), BuildEnv(bt, torch.device("cuda")))
+        rope.prepare(80)
+        qkv = dev(rnd(rng, 2, (H + 2 * KV) * Dh, dtype="bfloat16"), bt)
+        meta = (i32(pt), i32([0, 1]), i32([69, 32]), i32(slots))
+        # 3: a position beyond the rotary table (the table has 80 rows)
+        ops.qk_norm_rope_append(qkv, H, KV, Dh, None, None, 0.0, rope.fused_table(), Dh, kp, vp, i32(pt), i32([0, 1]),
+                                i32([69, 95]), i32(slots))
+        assert _take_error(ops) == 3
+        # 2: append to a page that is not mapped, and to one that cannot exist
+        for bad in (-1, k_pool.shape[0] + 5):
+            broken = pt.copy()
+            broken[slots[0], 69 // 32] = bad
+            ops.qk_norm_rope_append(qkv, H, KV, Dh, None, None, 0.0, rope.fused_table(), Dh, kp, vp, i32(broken), *meta[1:])
+            assert _take_error(ops) == 2
+        # 4: attention that meets such a page: decode (one token each), prefill (several), the plain kernel
+        q1 = dev(rnd(rng, 2, H, Dh, dtype="bfloat16"), bt)
+        qn = dev(rnd(rng, 10, H, Dh, dtype="bfloat16"), bt)
+        for bad in (-1, k_pool.shape[0] + 5):
+            broken = pt.copy()
+            broken[slots[0], 1] = bad
+            out = ops.attention_decode(q1, kp, vp, i32(broken), i32(slots), i32(lens), 0.1, 0, max(lens))
+            assert _take_error(ops) == 4 and out.shape == q1.shape
+            out = ops.attention_prefill(qn, kp, vp, i32(broken), i32(slots), i32([0, 5, 10]), i32(lens), 5, 0.1, 0)
+            assert _take_error(ops) == 4 and out.shape == qn.shape
+            out = ops.attention(q1, kp, vp, i32(broken), i32([0, 1]), i32([69, 32]), i32(slots), 0.1, 0)
+            assert _take_error(ops) == 4 and out.shape == q1.shape
+    assert _take_error(ops) == 0
