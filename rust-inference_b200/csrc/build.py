@@ -37,6 +37,7 @@ SOURCES: Dict[str, Tuple[str, ...]] = {
     "attention_decode": ("attention_decode.cu", "common.cuh", "mma_helpers.cuh"),
     "attention_prefill": ("attention_prefill.cu", "common.cuh", "mma_helpers.cuh"),
     "linear_skinny": ("linear_skinny.cu", "common.cuh", "mma_helpers.cuh"),
+    "linear_stream_tc": ("linear_stream_tc.cu", "common.cuh", "mma_helpers.cuh"),
     "attention_prefill_tc": ("attention_prefill_tc.cu", "common.cuh", "mma_helpers.cuh"),
     "attention_decode_noalloc": ("attention_decode_noalloc.cu", "attention_decode_noalloc.h", "attention_decode.cu",
                                  "common.cuh", "mma_helpers.cuh"),

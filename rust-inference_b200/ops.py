@@ -33,6 +33,7 @@ _SIGNATURES = {
     ("sampling", "ri_mark_seen"): [_P, _L, _P, _P, _I, _I, _P],
     ("attention_decode", "ri_attention_decode"): [_P] * 9 + [_I] * 8 + [_F, _I, _P, _P],
     ("linear_skinny", "ri_linear_skinny"): [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+    ("linear_stream_tc", "ri_linear_stream_tc"): [_P, _P, _P, _I, _I, _I, _I, _P, _P],
     ("attention_prefill_tc", "ri_attention_prefill_tc"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _P],
     ("attention_prefill", "ri_attention_prefill"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _P],
 }
@@ -44,6 +45,12 @@ _NO_TCGEN05 = __import__("os").environ.get("RUST_INFERENCE_B200_NO_TCGEN05") == 
 # Qwen3-8B shapes, 0.3 % at batch 8); RUST_INFERENCE_B200_FUSED_SWIGLU=0 takes the separate kernel, for comparisons
 _FUSED_SWIGLU = __import__("os").environ.get("RUST_INFERENCE_B200_FUSED_SWIGLU", "1") != "0"
 SKINNY_MAX_TOKENS = 16      # up to here the bfloat16 linear is this package's weight-streaming kernel
+# For 17 to 128 tokens there is a tcgen05 weight-streaming kernel of this package as well (linear_stream_tc).  Measured
+# at 64 tokens and Qwen3-8B shapes, replayed from a graph: 14.6 / 12.0 / 37.1 / 22.6 us for the four linears of a layer
+# against cuBLAS's 11.5 / 9.6 / 37.9 / 22.3 us, the output head 192 against 213 us, and the whole batch-64 step
+# 3 % slower: so it is taken only when RUST_INFERENCE_B200_STREAM_TC=1 asks for it.
+STREAM_TC_MAX_TOKENS = 128
+_STREAM_TC = __import__("os").environ.get("RUST_INFERENCE_B200_STREAM_TC") == "1"
 _fn_cache = {}
 
 
@@ -209,7 +216,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     """y = x w^T for x [M, K], w [N, K].
 
     float32: this package's own FMA kernel (no tensor cores, no TF32).
-    bfloat16, up to 16 tokens: this package's weight-streaming tensor-core kernel.
+    bfloat16, up to 16 tokens: this package's weight-streaming tensor-core kernel (mma.sync).
     bfloat16, more tokens: the library GEMM (cuBLAS through torch), as the
     reference engine uses cuBLAS for its linears (src/cuda/mod.rs:186-232 there).
     ``out_dtype`` float32 keeps the float32 accumulator (used for the logits)."""
@@ -231,9 +238,26 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         _call("linear_skinny", "ri_linear_skinny", x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K,
               1 if out_dtype == torch.float32 else 0, 0, error_flag(x.device).data_ptr(), _stream())
         return y
+    if M <= STREAM_TC_MAX_TOKENS and K % 8 == 0 and _STREAM_TC:
+        return linear_stream_tc(x, w, out_dtype)
     if out_dtype == torch.float32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
     return torch.mm(x, w.t())
+
+
+def linear_stream_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """y = x w^T in bfloat16 for up to 128 tokens on tcgen05: weight rows as the M side of the product, tokens as N,
+    K split over a thread-block cluster whose partial tiles are added through distributed shared memory."""
+    _need(x, "x", torch.bfloat16)
+    _need(w, "w", torch.bfloat16)
+    M, K = x.shape
+    if M > STREAM_TC_MAX_TOKENS or K % 8 or w.shape[1] != K:
+        raise KernelError(f"linear_stream_tc: x {tuple(x.shape)}, w {tuple(w.shape)}: at most {STREAM_TC_MAX_TOKENS} tokens, K a multiple of 8")
+    N = w.shape[0]
+    y = torch.empty((M, N), dtype=torch.float32 if out_dtype == torch.float32 else torch.bfloat16, device=x.device)
+    _call("linear_stream_tc", "ri_linear_stream_tc", x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K,
+          1 if out_dtype == torch.float32 else 0, error_flag(x.device).data_ptr(), _stream())
+    return y
 
 
 def qk_norm_rope_append(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,

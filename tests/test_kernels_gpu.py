@@ -127,6 +127,29 @@ def test_linear_swiglu_fused(shape):
     assert torch.equal(alone[0], got[M - 1])
 
 
+@pytest.mark.parametrize("shape", [(17, 100, 72), (40, 257, 1544), (64, 4096, 4096), (128, 1000, 12288), (65, 24576, 512),
+                                   (33, 130, 8)])
+def test_linear_stream_tc(shape):
+    """The tcgen05 weight-streaming linear (up to 128 tokens): widths and depths that end inside a tile or a
+    stage, splits of K over a cluster with the partial tiles added in a fixed order, twice in a row."""
+    from rust_inference_b200 import ops
+    M, N, K = shape
+    rng = np.random.default_rng(N)
+    x, w = rnd(rng, M, K, dtype="bfloat16"), rnd(rng, N, K, dtype="bfloat16")
+    want = plain.linear(x, w)
+    xd, wd = dev(x, torch.bfloat16), dev(w, torch.bfloat16)
+    full = ops.linear_stream_tc(xd, wd, out_dtype=torch.float32)
+    close(full, want, 2e-5, f"linear_stream_tc {shape} -> f32")
+    close(ops.linear_stream_tc(xd, wd), want, 5e-3, f"linear_stream_tc {shape}")
+    again = ops.linear_stream_tc(xd, wd, out_dtype=torch.float32)
+    assert torch.equal(again, full)
+    assert int(ops.error_flag("cuda").item()) == 0
+    # a token's result does not depend on the tokens around it (as long as the kernel is the same)
+    if M > 17:
+        fewer = ops.linear_stream_tc(dev(x[:17], torch.bfloat16), wd, out_dtype=torch.float32)
+        assert torch.equal(fewer, full[:17])
+
+
 def _paged(rng, lens, KV, Dh, P, dtype, extra_pages=3):
     """Random pools with a shuffled page table for sequences of the given lengths."""
     pages_per = [-(-n // P) for n in lens]
