@@ -48,8 +48,10 @@ SKINNY_MAX_TOKENS = 16      # up to here the bfloat16 linear is this package's w
 # For 17 to 128 tokens there is a tcgen05 weight-streaming kernel of this package as well (linear_stream_tc).  Measured
 # at 64 tokens and Qwen3-8B shapes, replayed from a graph: 14.6 / 12.0 / 37.1 / 22.6 us for the four linears of a layer
 # against cuBLAS's 11.5 / 9.6 / 37.9 / 22.3 us, the output head 192 against 213 us, and the whole batch-64 step
-# 3 % slower: so it is taken only when RUST_INFERENCE_B200_STREAM_TC=1 asks for it.
+# 3 % slower: so it is taken for wide matrices only (the output head: 65,536 outputs and more), or for all of them
+# when RUST_INFERENCE_B200_STREAM_TC=1 asks for it.
 STREAM_TC_MAX_TOKENS = 128
+STREAM_TC_WIDE = int(__import__("os").environ.get("RUST_INFERENCE_B200_STREAM_TC_WIDE", "65536"))   # from this many outputs on it is taken anyway
 _STREAM_TC = __import__("os").environ.get("RUST_INFERENCE_B200_STREAM_TC") == "1"
 _fn_cache = {}
 
@@ -238,7 +240,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         _call("linear_skinny", "ri_linear_skinny", x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K,
               1 if out_dtype == torch.float32 else 0, 0, error_flag(x.device).data_ptr(), _stream())
         return y
-    if M <= STREAM_TC_MAX_TOKENS and K % 8 == 0 and _STREAM_TC:
+    if M <= STREAM_TC_MAX_TOKENS and K % 8 == 0 and (_STREAM_TC or N >= STREAM_TC_WIDE):
         return linear_stream_tc(x, w, out_dtype)
     if out_dtype == torch.float32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
