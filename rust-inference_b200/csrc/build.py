@@ -29,14 +29,14 @@ BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"
 
 # every kernel source of the package, with the headers it includes
 SOURCES: Dict[str, Tuple[str, ...]] = {
-    "elementwise": ("elementwise.cu", "common.cuh"),
+    "elementwise": ("elementwise.cu", "common.cuh", "linear_skinny_geometry.cuh"),
     "rope_kv": ("rope_kv.cu", "common.cuh"),
     "attention_plain": ("attention_plain.cu", "common.cuh"),
     "linear_f32": ("linear_f32.cu", "common.cuh"),
     "sampling": ("sampling.cu", "common.cuh"),
     "attention_decode": ("attention_decode.cu", "common.cuh", "mma_helpers.cuh"),
     "attention_prefill": ("attention_prefill.cu", "common.cuh", "mma_helpers.cuh"),
-    "linear_skinny": ("linear_skinny.cu", "common.cuh", "mma_helpers.cuh"),
+    "linear_skinny": ("linear_skinny.cu", "common.cuh", "mma_helpers.cuh", "linear_skinny_geometry.cuh"),
     "linear_stream_tc": ("linear_stream_tc.cu", "common.cuh", "mma_helpers.cuh"),
     "attention_prefill_tc": ("attention_prefill_tc.cu", "common.cuh", "mma_helpers.cuh"),
     "attention_decode_noalloc": ("attention_decode_noalloc.cu", "attention_decode_noalloc.h", "attention_decode.cu",

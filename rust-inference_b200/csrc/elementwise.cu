@@ -7,6 +7,7 @@
 // Formulas: thanhauco/rust-inference src/ops/embedding.rs:10-42,
 // src/ops/norm.rs:7-62, src/ops/elementwise.rs:10-52 (kernels.cu:89-148 there).
 #include "common.cuh"
+#include "linear_skinny_geometry.cuh"
 
 // ---------------------------------------------------------------------------
 // out[t, :] = float(table[ids[t], :])
@@ -92,13 +93,23 @@ __device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
     *(uint2*)p = u;
 }
 
+#ifndef RMS_HINT_PER_THREAD
+#define RMS_HINT_PER_THREAD 2
+#endif
+
 template <typename T, int NV>
 __global__ void rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta, const int* __restrict__ rows,
                                    const float* __restrict__ gain, T* __restrict__ out, int dim, float eps,
-                                   int write_back) {
+                                   int write_back, int n_rows, WeightHint next) {
     __shared__ float red[33];
     pdl_trigger();
     pdl_wait();
+    if ((int)blockIdx.x >= n_rows) {
+        // the blocks beyond the rows ask for the weights that the linear after this norm reads
+        weight_hint_prefetch(next, ((int)blockIdx.x - n_rows) * (int)blockDim.x + (int)threadIdx.x,
+                             ((int)gridDim.x - n_rows) * (int)blockDim.x);
+        return;
+    }
     size_t r = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
     float* rp = resid + r * dim;
     const T* dp = delta ? delta + r * dim : nullptr;
@@ -137,7 +148,7 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restric
 
 template <typename T>
 static bool launch_rmsnorm_vec(float* resid, const void* delta, const int* rows, const float* gain, void* out,
-                               int n_rows, int dim, float eps, int write_back, cudaStream_t stream) {
+                               int n_rows, int dim, float eps, int write_back, const WeightHint& next, cudaStream_t stream) {
     if (dim % 4) return false;
     uintptr_t al = (uintptr_t)resid | (uintptr_t)gain | (uintptr_t)out | (uintptr_t)delta;
     if (al & 15) return false;
@@ -146,23 +157,44 @@ static bool launch_rmsnorm_vec(float* resid, const void* delta, const int* rows,
     int nv = (nvec + threads - 1) / threads;
     const T* d = (const T*)delta;
     T* o = (T*)out;
-    if (nv == 1) ri_launch_pdl(rmsnorm_vec_kernel<T, 1>, dim3(n_rows), dim3(threads), 0, stream, resid, d, rows, gain, o, dim, eps, write_back);
-    else if (nv == 2) ri_launch_pdl(rmsnorm_vec_kernel<T, 2>, dim3(n_rows), dim3(threads), 0, stream, resid, d, rows, gain, o, dim, eps, write_back);
-    else if (nv <= 4) ri_launch_pdl(rmsnorm_vec_kernel<T, 4>, dim3(n_rows), dim3(threads), 0, stream, resid, d, rows, gain, o, dim, eps, write_back);
-    else return false;
+    if (nv > 4) return false;
+    // with a hint: as many more blocks as give each thread a few requests
+    int extra = 0;
+    if (next.base) {
+        const long long lines = (long long)next.rows * SK_WARPS * (SK_HINT_STAGES * SK_STAGE_K * 2 / SK_HINT_LINE);
+        const int want = (int)((lines + (long long)threads * RMS_HINT_PER_THREAD - 1) / ((long long)threads * RMS_HINT_PER_THREAD));
+        extra = want < 1 ? 1 : (want > 256 ? 256 : want);
+    }
+    const dim3 grid(n_rows + extra);
+    if (nv == 1) ri_launch_pdl(rmsnorm_vec_kernel<T, 1>, grid, dim3(threads), 0, stream, resid, d, rows, gain, o, dim, eps, write_back, n_rows, next);
+    else if (nv == 2) ri_launch_pdl(rmsnorm_vec_kernel<T, 2>, grid, dim3(threads), 0, stream, resid, d, rows, gain, o, dim, eps, write_back, n_rows, next);
+    else ri_launch_pdl(rmsnorm_vec_kernel<T, 4>, grid, dim3(threads), 0, stream, resid, d, rows, gain, o, dim, eps, write_back, n_rows, next);
     return true;
 }
 
+// next_w [next_n, next_k] (bfloat16, or null): the weights of the skinny linear that reads this norm's output;
+// the kernel asks for the part of them that the linear wants first after what it holds itself.
 extern "C" int ri_rmsnorm(float* resid, const void* delta, const int* rows, const float* gain, void* out, int n_rows,
-                          int dim, float eps, int write_back, int dtype, cudaStream_t stream) {
+                          int dim, float eps, int write_back, int dtype, const void* next_w, int next_n, int next_k,
+                          cudaStream_t stream) {
     if (n_rows == 0) return 0;
     RI_REQUIRE(n_rows > 0 && dim > 0, "rmsnorm: bad sizes rows=%d dim=%d", n_rows, dim);
     if (rows) write_back = 0;
-    if (dtype == RI_DTYPE_F32 && launch_rmsnorm_vec<float>(resid, delta, rows, gain, out, n_rows, dim, eps, write_back, stream)) {
+    WeightHint next = make_weight_hint(nullptr, 0, 0, 0);
+    if (next_w) {
+        static int sms = 0;
+        if (!sms) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        }
+        next = make_weight_hint(next_w, next_n, next_k, sms);
+    }
+    if (dtype == RI_DTYPE_F32 && launch_rmsnorm_vec<float>(resid, delta, rows, gain, out, n_rows, dim, eps, write_back, next, stream)) {
         RI_CHECK_LAUNCH("rmsnorm");
         return 0;
     }
-    if (dtype == RI_DTYPE_BF16 && launch_rmsnorm_vec<__nv_bfloat16>(resid, delta, rows, gain, out, n_rows, dim, eps, write_back, stream)) {
+    if (dtype == RI_DTYPE_BF16 && launch_rmsnorm_vec<__nv_bfloat16>(resid, delta, rows, gain, out, n_rows, dim, eps, write_back, next, stream)) {
         RI_CHECK_LAUNCH("rmsnorm");
         return 0;
     }

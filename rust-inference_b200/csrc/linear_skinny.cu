@@ -25,25 +25,13 @@
 // runs out the kernel sets the error word (5) and finishes.
 #include "common.cuh"
 #include "mma_helpers.cuh"
+#include "linear_skinny_geometry.cuh"
 #include <cuda.h>
 
-#ifndef SK_WARPS
-#define SK_WARPS 4
-#endif
-#define SK_ROWS 16
-#ifndef SK_STAGE_K
-#define SK_STAGE_K 256                       // k per stage
-#endif
 #define SK_GROUPS (SK_STAGE_K / 32)          // groups of 32 k in a stage
 #define SK_BOXES (SK_STAGE_K / 64)           // copies per stage: 16 rows x 64 k (128 bytes) each
 #define SK_BOX_BYTES (SK_ROWS * 128)
 #define SK_STAGE_TOTAL (SK_BOXES * SK_BOX_BYTES)
-#ifndef SK_STAGES
-#define SK_STAGES 2
-#endif
-#ifndef SK_MIN_BLOCKS
-#define SK_MIN_BLOCKS 3
-#endif
 
 __device__ __forceinline__ uint4 ld_ca16(const void* p) { return __ldg((const uint4*)p); }
 __device__ __forceinline__ uint4 lds16(const void* p) {

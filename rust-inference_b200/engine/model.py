@@ -149,5 +149,8 @@ class Model:
         delta = None
         for e in self.spec.schedule:
             resid, delta = self.blocks[e.layer](resid, delta, ctx, cache.layer(e.cache, e.writes))
-        x = self.final_norm(resid, delta, rows=want_rows)
+        if self.final_norm.takes_hint:
+            x = self.final_norm(resid, delta, want_rows, self.head)
+        else:
+            x = self.final_norm(resid, delta, rows=want_rows)
         return ops.linear(x, self.head, out_dtype=torch.float32)

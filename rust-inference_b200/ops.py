@@ -22,7 +22,7 @@ _F = ctypes.c_float
 
 _SIGNATURES = {
     ("elementwise", "ri_embed_rows"): [_P, _P, _P, _I, _I, _I, _I, _P, _P],
-    ("elementwise", "ri_rmsnorm"): [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _P],
+    ("elementwise", "ri_rmsnorm"): [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _P, _I, _I, _P],
     ("elementwise", "ri_add_rows"): [_P, _P, _L, _I, _P],
     ("elementwise", "ri_silu_mul"): [_P, _P, _I, _I, _I, _I, _P],
     ("rope_kv", "ri_qk_norm_rope_append"): [_P] * 10 + [_F, _P, _I, _I] + [_I] * 9 + [_P, _P],
@@ -44,6 +44,7 @@ _NO_TCGEN05 = __import__("os").environ.get("RUST_INFERENCE_B200_NO_TCGEN05") == 
 # the skinny linear applies the SiLU gate in its epilogue (one kernel less per layer: 2 % faster at batch 1 of
 # Qwen3-8B shapes, 0.3 % at batch 8); RUST_INFERENCE_B200_FUSED_SWIGLU=0 takes the separate kernel, for comparisons
 _FUSED_SWIGLU = __import__("os").environ.get("RUST_INFERENCE_B200_FUSED_SWIGLU", "1") != "0"
+_WEIGHT_HINTS = __import__("os").environ.get("RUST_INFERENCE_B200_WEIGHT_HINTS", "1") != "0"
 SKINNY_MAX_TOKENS = 16      # up to here the bfloat16 linear is this package's weight-streaming kernel
 # For 17 to 128 tokens there is a tcgen05 weight-streaming kernel of this package as well (linear_stream_tc).  Measured
 # at 64 tokens and Qwen3-8B shapes, replayed from a graph: 14.6 / 12.0 / 37.1 / 22.6 us for the four linears of a layer
@@ -154,13 +155,25 @@ def embed(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def _weight_hint(then: Optional[torch.Tensor], tokens: int) -> Optional[torch.Tensor]:
+    """``then`` if the linear over it will be the weight-streaming kernel for ``tokens`` rows."""
+    if (_WEIGHT_HINTS and then is not None and tokens <= SKINNY_MAX_TOKENS and then.dtype == torch.bfloat16
+            and then.dim() == 2 and then.is_contiguous()):
+        return then
+    return None
+
+
 def rmsnorm(resid: torch.Tensor, gain: torch.Tensor, eps: float, out_dtype: torch.dtype,
-            delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+            delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+            then: Optional[torch.Tensor] = None) -> torch.Tensor:
     """RMSNorm of the float32 residual stream ``resid`` [n, dim].
 
     With ``delta`` (compute dtype, same shape) the sum resid + delta is normed,
     and written back into ``resid`` unless ``rows`` is given.  With ``rows``
-    (int32 indices) only those rows are normed, in that order."""
+    (int32 indices) only those rows are normed, in that order.  ``then`` names the
+    weight matrix [N, K] of the linear that reads the result next: for a handful of
+    rows in bfloat16 the kernel asks for the start of it to be brought into L2 (a
+    hint; it changes no result)."""
     _need(resid, "resid", torch.float32)
     n, dim = resid.shape
     _need(gain, "gain", torch.float32, (dim,))
@@ -170,8 +183,10 @@ def rmsnorm(resid: torch.Tensor, gain: torch.Tensor, eps: float, out_dtype: torc
         _need(rows, "rows", torch.int32)
     n_out = n if rows is None else rows.numel()
     out = torch.empty((n_out, dim), dtype=out_dtype, device=resid.device)
+    hint = _weight_hint(then, n_out)
     _call("elementwise", "ri_rmsnorm", resid.data_ptr(), _ptr(delta), _ptr(rows), gain.data_ptr(), out.data_ptr(),
-          n_out, dim, float(eps), 1, _code(out_dtype), _stream())
+          n_out, dim, float(eps), 1, _code(out_dtype), _ptr(hint), hint.shape[0] if hint is not None else 0,
+          hint.shape[1] if hint is not None else 0, _stream())
     return out
 
 

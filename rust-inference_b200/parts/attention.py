@@ -50,6 +50,9 @@ class Attention(Mixer):
     def weight_bytes(self):
         return (self.qkv.numel() + self.o.numel()) * self.qkv.element_size()
 
+    def reads_first(self):
+        return self.qkv
+
     def cache_request(self):
         s = self.spec
         return CacheRequest(kv_heads=s.num_kv_heads, head_dim=s.head_dim, window=s.window)

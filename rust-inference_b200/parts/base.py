@@ -115,8 +115,17 @@ class Part:
     def weight_bytes(self) -> int:
         return 0
 
+    def reads_first(self) -> Optional[torch.Tensor]:
+        """The weight matrix [N, K] of the linear with which this part starts, if it starts
+        with one: the norm before it may warm the cache for it (see ``Norm.takes_hint``)."""
+        return None
+
 
 class Norm(Part):
+    """``takes_hint``: the norm's ``__call__`` has a fourth argument ``then``, the weight matrix
+    that the following part reads first (a performance hint that changes no result)."""
+    takes_hint = False
+
     def __call__(self, resid, delta=None, rows=None):
         raise NotImplementedError
 

@@ -28,7 +28,13 @@ class Block:
                 ("ffn_norm", self.ffn_norm, "norm", s.ffn_norm), ("ffn", self.ffn, "ffn", s.ffn))
 
     def __call__(self, resid, delta, ctx, cache):
-        x = self.mixer_norm(resid, delta)
+        x = _norm(self.mixer_norm, resid, delta, self.mixer)
         a = self.mixer(x, ctx, cache)
-        x = self.ffn_norm(resid, a)
+        x = _norm(self.ffn_norm, resid, a, self.ffn)
         return resid, self.ffn(x, ctx)
+
+
+def _norm(norm, resid, delta, reader):
+    if norm.takes_hint:
+        return norm(resid, delta, None, reader.reads_first())
+    return norm(resid, delta)

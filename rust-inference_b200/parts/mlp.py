@@ -34,5 +34,8 @@ class SwiGLU(FeedForward):
     def weight_bytes(self):
         return (self.gate_up.numel() + self.down.numel()) * self.gate_up.element_size()
 
+    def reads_first(self):
+        return self.gate_up
+
     def __call__(self, x, ctx):
         return ops.linear(ops.linear_swiglu(x, self.gate_up, self.block), self.down)

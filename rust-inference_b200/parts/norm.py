@@ -12,6 +12,8 @@ from .registry import ParamInfo, register_norm
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
     graph_safe = True
+    takes_hint = True
+
     @classmethod
     def param_infos(cls, spec):
         return {"weight": ParamInfo((spec.size,), "gain")}
@@ -22,5 +24,5 @@ class RMSNorm(Norm):
     def weight_bytes(self):
         return self.gain.numel() * 4
 
-    def __call__(self, resid, delta=None, rows=None):
-        return ops.rmsnorm(resid, self.gain, self.spec.eps, self.env.dtype, delta=delta, rows=rows)
+    def __call__(self, resid, delta=None, rows=None, then=None):
+        return ops.rmsnorm(resid, self.gain, self.spec.eps, self.env.dtype, delta=delta, rows=rows, then=then)

@@ -20,7 +20,7 @@ def embed(ids, table):
     return table[ids.long()].float()
 
 
-def rmsnorm(resid, gain, eps, out_dtype, delta=None, rows=None):
+def rmsnorm(resid, gain, eps, out_dtype, delta=None, rows=None, then=None):
     if rows is not None:
         x = resid[rows.long()]
         if delta is not None:

@@ -66,6 +66,25 @@ def test_rmsnorm(dtype, dim):
     close(r2, resid.astype(np.float64), 0, "gathered norm leaves the stream alone")
 
 
+@pytest.mark.parametrize("n,k", [(40, 1024), (7200, 2048), (24, 256), (9, 24)])
+def test_rmsnorm_with_a_weight_hint(n, k):
+    """Naming the matrix that the next linear reads changes no result (the kernel only asks for a
+    part of it to be brought into L2), whether the matrix has fewer rows than the hint covers, more,
+    rows of a single stage or rows that the hint does not take."""
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(n)
+    dim = 72
+    resid, delta = rnd(rng, 5, dim), rnd(rng, 5, dim, dtype="bfloat16")
+    gain = dev((1 + 0.1 * rng.standard_normal(dim)).astype(np.float32))
+    w = torch.zeros((n, k), dtype=torch.bfloat16, device="cuda")
+    r1, r2 = dev(resid), dev(resid)
+    want = ops.rmsnorm(r1, gain, 1e-6, torch.bfloat16, delta=dev(delta, torch.bfloat16))
+    got = ops.rmsnorm(r2, gain, 1e-6, torch.bfloat16, delta=dev(delta, torch.bfloat16), then=w)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want) and torch.equal(r1, r2)
+    assert not w.any()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_silu_mul(dtype):
     from rust_inference_b200 import ops
