@@ -114,7 +114,8 @@ def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
-    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=32,
+                    help="untimed decode steps before the timed ones (right behind the prompt step the clock sits lower under the power cap)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the 36 of the configuration (named in config)")
     ap.add_argument("--batch", type=int, default=8)
