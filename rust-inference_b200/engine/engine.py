@@ -112,7 +112,10 @@ class Engine:
 
     # ---- one step --------------------------------------------------------------------------
     def step(self, entries: Sequence[Entry]) -> torch.Tensor:
-        """Run the step; float32 logits [wanted places in entry order, vocab] on the device."""
+        """Run the step; float32 logits [wanted places in entry order, vocab] on the device.
+
+        A step replayed from a graph returns the graph's own output buffer: the logits are
+        valid until the next step of the same batch size runs; a caller that keeps them copies."""
         if not entries:
             raise StepError("a step needs at least one sequence")
         V = self.model.spec.vocab_size

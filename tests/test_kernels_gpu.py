@@ -169,6 +169,24 @@ def test_linear_stream_tc(shape):
         assert torch.equal(fewer, full[:17])
 
 
+def test_linear_takes_the_streaming_kernel_for_wide_outputs(monkeypatch):
+    """`ops.linear` for 17 to 128 tokens hands matrices with many outputs (an output head) to the tcgen05
+    streaming kernel and the others to the library; the threshold lowered, both ways give the same product."""
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(5)
+    x, w = rnd(rng, 40, 200, dtype="bfloat16"), rnd(rng, 333, 200, dtype="bfloat16")
+    xd, wd = dev(x, torch.bfloat16), dev(w, torch.bfloat16)
+    want = plain.linear(x, w)
+    library = ops.linear(xd, wd, out_dtype=torch.float32)
+    n0 = ops.launch_count()
+    monkeypatch.setattr(ops, "STREAM_TC_WIDE", 300)
+    own = ops.linear(xd, wd, out_dtype=torch.float32)
+    assert ops.launch_count() == n0 + 1, "the streaming kernel counts as a launch of this package, the library does not"
+    close(own, want, 2e-5, "linear (streaming kernel)")
+    close(library, want, 2e-5, "linear (library)")
+    assert torch.equal(own, ops.linear_stream_tc(xd, wd, out_dtype=torch.float32))
+
+
 def _paged(rng, lens, KV, Dh, P, dtype, extra_pages=3):
     """Random pools with a shuffled page table for sequences of the given lengths."""
     pages_per = [-(-n // P) for n in lens]
