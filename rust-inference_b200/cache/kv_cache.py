@@ -18,7 +18,7 @@ import numpy as np
 import torch
 
 from ..parts.base import CacheRequest
-from .allocator import CacheError, PageTable, SlotAllocator
+from .allocator import CacheError, HostCache, PageTable
 
 PAGE_SIZE = 32          # tokens per page, as in the reference (src/kvcache.rs:12)
 
@@ -36,10 +36,10 @@ class LayerCache:
 
 
 class _Group:
-    def __init__(self, req: CacheRequest, entries: List[int], num_slots, num_pages, max_pages_per_seq, page_size,
-                 dtype, device):
+    def __init__(self, req: CacheRequest, entries: List[int], pages: PageTable, num_slots, num_pages,
+                 max_pages_per_seq, page_size, dtype, device):
         self.req, self.entries = req, entries
-        self.pages = PageTable(num_slots, num_pages, max_pages_per_seq, page_size, req.window)
+        self.pages = pages
         shape = (len(entries), num_pages, req.kv_heads, page_size, req.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
         self.v = torch.zeros(shape, dtype=dtype, device=device)
@@ -47,14 +47,14 @@ class _Group:
 
     def upload(self) -> None:
         pt = self.pages
-        if not pt.dirty:
+        dirty = pt.take_dirty()
+        if not len(dirty):
             return
-        if pt.table.nbytes <= (1 << 20) or len(pt.dirty) * 4 >= pt.num_slots:
+        if pt.table.nbytes <= (1 << 20) or len(dirty) * 4 >= pt.num_slots:
             self.table_dev.copy_(torch.from_numpy(pt.table.copy()))
         else:
-            for s in sorted(pt.dirty):
+            for s in dirty.tolist():
                 self.table_dev[s].copy_(torch.from_numpy(pt.table[s].copy()))
-        pt.dirty.clear()
 
 
 class Cache:
@@ -67,7 +67,6 @@ class Cache:
         self.page_size = page_size
         self.num_pages = num_pages
         self.max_pages_per_seq = min(max_pages_per_seq, num_pages)
-        self.slots = SlotAllocator(num_slots)
         self.requests = list(requests)
         self.groups: List[_Group] = []
         self._where: Dict[int, tuple] = {}
@@ -75,9 +74,14 @@ class Cache:
         for i, r in enumerate(self.requests):
             if r is not None and r.kv_heads > 0:
                 by_need.setdefault((r.kv_heads, r.head_dim, r.window), []).append(i)
-        for need, entries in by_need.items():
-            g = _Group(self.requests[entries[0]], entries, num_slots, num_pages, self.max_pages_per_seq, page_size,
-                       dtype, self.device)
+        # the bookkeeping of slots, pages and lengths is one C++ object (csrc/host_cache.cpp)
+        self.host = HostCache(num_slots, num_pages, self.max_pages_per_seq, page_size,
+                              [need[2] for need in by_need])
+        self.slots = self.host.slots
+        self._any_window = any(need[2] > 0 for need in by_need)
+        for (need, entries), pages in zip(by_need.items(), self.host.groups):
+            g = _Group(self.requests[entries[0]], entries, pages, num_slots, num_pages, self.max_pages_per_seq,
+                       page_size, dtype, self.device)
             for j, e in enumerate(entries):
                 self._where[e] = (len(self.groups), j)
             self.groups.append(g)
@@ -85,61 +89,33 @@ class Cache:
         for i, r in enumerate(self.requests):
             if r is not None and r.state_shape:
                 self.state[i] = torch.zeros((num_slots,) + tuple(r.state_shape), dtype=r.state_dtype, device=self.device)
-        self._lens = [0] * num_slots
 
     # ---- slots ---------------------------------------------------------------------------
     def alloc_slot(self) -> int:
-        s = self.slots.alloc()
-        self._lens[s] = 0
+        s = self.host.alloc_slot()
         for t in self.state.values():
             t[s].zero_()
         return s
 
     def free_slot(self, slot: int) -> None:
-        self.slots.free(slot)
-        for g in self.groups:
-            g.pages.release(slot)
-        self._lens[slot] = 0
+        self.host.free_slot(slot)
 
     def length(self, slot: int) -> int:
-        self.slots.require_live(slot)
-        return self._lens[slot]
+        return self.host.length(slot)
 
     @property
     def max_seq_len(self) -> int:
         return self.max_pages_per_seq * self.page_size
 
     def free_pages(self) -> int:
-        return min((g.pages.free_pages for g in self.groups), default=self.num_pages)
+        return self.host.free_pages()
 
     # ---- growth ----------------------------------------------------------------------------
     def extend(self, growth: Sequence[tuple]) -> List[int]:
         """``growth``: (slot, new_tokens) for every sequence of a step.  Maps the
         pages in every group and returns each sequence's length before.  Either
         all of it happens or none."""
-        seen = set()
-        for slot, n in growth:
-            self.slots.require_live(slot)
-            if slot in seen:
-                raise CacheError(f"slot {slot} appears twice in one step")
-            seen.add(slot)
-            if n <= 0:
-                raise CacheError("every sequence of a step brings at least one token")
-            if self._lens[slot] + n > self.max_seq_len:
-                raise CacheError(f"slot {slot} would reach {self._lens[slot] + n} tokens, "
-                                 f"the cache holds {self.max_seq_len} per sequence")
-        for g in self.groups:
-            need = sum(g.pages.pages_needed(slot, n) for slot, n in growth)
-            if need > g.pages.free_pages:
-                raise CacheError(f"cache out of pages: this step needs {need}, {g.pages.free_pages} of "
-                                 f"{g.pages.num_pages} are free")
-        before = []
-        for slot, n in growth:
-            for g in self.groups:
-                g.pages.extend(slot, n)
-            before.append(self._lens[slot])
-            self._lens[slot] += n
-        return before
+        return self.host.extend([g[0] for g in growth], [g[1] for g in growth])
 
     def upload(self) -> None:
         """Bring the device page tables up to date (before the step's kernels)."""
@@ -148,10 +124,8 @@ class Cache:
 
     def after_step(self, slots: Sequence[int]) -> None:
         """Release what no later step can read (pages behind a window)."""
-        for g in self.groups:
-            if g.req.window > 0:
-                for s in slots:
-                    g.pages.release_behind_window(s)
+        if self._any_window:
+            self.host.after_step(slots)
 
     # ---- views -----------------------------------------------------------------------------
     def layer(self, entry: int, writes: bool = True) -> LayerCache:
@@ -167,9 +141,4 @@ class Cache:
         return sum(2 * len(g.entries) * g.req.kv_heads * g.req.head_dim * es for g in self.groups)
 
     def check(self) -> None:
-        self.slots.check()
-        for g in self.groups:
-            g.pages.check()
-            for s in range(self.slots.num_slots):
-                if not self.slots.is_live(s) and (g.pages.table[s] >= 0).any():
-                    raise AssertionError(f"free slot {s} still maps pages")
+        self.host.check()

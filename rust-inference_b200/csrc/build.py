@@ -41,7 +41,10 @@ SOURCES: Dict[str, Tuple[str, ...]] = {
     "attention_prefill_tc": ("attention_prefill_tc.cu", "common.cuh", "mma_helpers.cuh"),
     "attention_decode_noalloc": ("attention_decode_noalloc.cu", "attention_decode_noalloc.h", "attention_decode.cu",
                                  "common.cuh", "mma_helpers.cuh"),
+    # host code only (the cache's bookkeeping): built with the host compiler
+    "host_cache": ("host_cache.cpp",),
 }
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC"]
 
 # sources that are compiled once per value of a macro (the model's head size);
 # the build check compiles these values, a model with another one compiles its own
@@ -71,6 +74,13 @@ def _nvcc() -> str:
         if cand and os.path.exists(cand):
             return cand
     raise KernelBuildError("nvcc was not found (PATH, $NVCC, /usr/local/cuda/bin): the CUDA kernels cannot be built")
+
+
+def _host_compiler() -> Optional[str]:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++")):
+        if cand and (os.path.exists(cand) or shutil.which(cand)):
+            return cand
+    return None
 
 
 def build_dir() -> str:
@@ -115,7 +125,7 @@ def _fingerprint(name: str, defines: Optional[Dict[str, object]]) -> str:
         with open(os.path.join(HERE, fn), "rb") as f:
             h.update(fn.encode())
             h.update(f.read())
-    h.update(repr(ARCH_FLAGS + BASE_FLAGS).encode())
+    h.update(repr(HOST_FLAGS if SOURCES[name][0].endswith(".cpp") else ARCH_FLAGS + BASE_FLAGS).encode())
     h.update(repr(sorted((defines or {}).items())).encode())
     return h.hexdigest()[:12]
 
@@ -148,11 +158,18 @@ def compile_library(name: str, defines: Optional[Dict[str, object]] = None, verb
     out = library_path(name, defines)
     src = os.path.join(HERE, SOURCES[name][0])
     tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
-    cmd = [_nvcc()] + ARCH_FLAGS + BASE_FLAGS + [f"-D{k}={v}" for k, v in sorted((defines or {}).items())]
-    if verbose:
-        cmd += ["-Xptxas", "-v"]
+    macros = [f"-D{k}={v}" for k, v in sorted((defines or {}).items())]
+    if src.endswith(".cpp"):
+        # host code: the host compiler, or nvcc (which hands the file to it) where none is on the path
+        cxx = _host_compiler()
+        cmd = ([cxx] + HOST_FLAGS if cxx else [_nvcc(), "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"]) + macros
+        _log(f"compiling {_variant_name(name, defines)} (host code) ...")
+    else:
+        cmd = [_nvcc()] + ARCH_FLAGS + BASE_FLAGS + macros
+        if verbose:
+            cmd += ["-Xptxas", "-v"]
+        _log(f"compiling {_variant_name(name, defines)} for sm_100a ...")
     cmd += ["-I", HERE, "-o", tmp, src]
-    _log(f"compiling {_variant_name(name, defines)} for sm_100a ...")
     t0 = time.time()
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, cwd=build_dir())
     while True:

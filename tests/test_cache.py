@@ -103,6 +103,8 @@ def test_random_walk_keeps_every_invariant():
                 assert b == live[s]
                 live[s] += n
             c.upload()
+            for g in c.groups:            # the copy for the kernels holds every row that changed, freed slots' too
+                assert np.array_equal(g.table_dev.numpy(), g.pages.table)
             c.after_step([s for s, _ in grow])
         c.check()
         for s, n in live.items():
