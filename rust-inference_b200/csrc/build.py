@@ -43,6 +43,8 @@ SOURCES: Dict[str, Tuple[str, ...]] = {
                                  "common.cuh", "mma_helpers.cuh"),
     # host code only (the cache's bookkeeping): built with the host compiler
     "host_cache": ("host_cache.cpp",),
+    # host code only: the check of a step's entries and its int32 tables
+    "host_step": ("host_step.cpp",),
 }
 HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC"]
 

@@ -15,6 +15,7 @@ the captured kernels read them from there.
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass
 from typing import List, Optional, Sequence, Union
 
@@ -23,6 +24,7 @@ import torch
 
 from .. import ops
 from ..cache import Cache, CacheError, PAGE_SIZE
+from ..csrc import build as _build
 from ..parts.base import StepContext
 from .model import Model
 
@@ -38,6 +40,32 @@ class Entry:
 
 class StepError(ValueError):
     pass
+
+
+_P, _I, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+_HOST_SIGNATURES = {
+    "ri_step_check": (_I, [_I, _P, _P, _P, _L, _P, _P, _P, _P]),
+    "ri_step_fill": (None, [_I, _P, _P, _P, _P, _P, _P, _L, _L, _P, _P, _P]),
+    "ri_step_check_decode": (_I, [_I, _P, _L]),
+    "ri_step_fill_decode": (None, [_I, _P, _P, _P, _I, _P, _P]),
+}
+_host_lib = None
+
+
+def _host():
+    """The C++ side of a step (csrc/host_step.cpp): the check of the entries and the tables."""
+    global _host_lib
+    if _host_lib is None:
+        lib = _build.library("host_step")
+        for name, (res, args) in _HOST_SIGNATURES.items():
+            f = getattr(lib, name)
+            f.restype, f.argtypes = res, args
+        _host_lib = lib
+    return _host_lib
+
+
+def _i32(values) -> np.ndarray:
+    return np.ascontiguousarray(values, dtype=np.int32)
 
 
 class _Tables:
@@ -125,53 +153,47 @@ class Engine:
         news, wants = [], []
         for e in entries:
             toks = np.asarray(e.tokens, dtype=np.int64).reshape(-1)
-            if toks.size == 0:
-                raise StepError(f"slot {e.slot} brings no token")
-            if toks.min() < 0 or toks.max() >= V:
-                raise StepError(f"slot {e.slot}: token id outside the vocabulary of {V}")
             news.append(toks)
             if isinstance(e.want, str):
                 if e.want == "last":
                     w = [toks.size - 1]
                 elif e.want == "all":
-                    w = list(range(toks.size))
+                    w = range(toks.size)
                 else:
                     raise StepError(f"want must be 'last', 'all' or a list of places, got {e.want!r}")
             else:
-                w = [int(i) for i in e.want]
-                if any(i < 0 or i >= toks.size for i in w):
-                    raise StepError(f"slot {e.slot}: wanted place outside its {toks.size} tokens")
-            wants.append(w)
-        slots = [int(e.slot) for e in entries]
-        before = self.cache.extend([(s, len(t)) for s, t in zip(slots, news)])
+                w = e.want
+            wants.append(_i32(w).reshape(-1))
+        B = len(entries)
+        slots = _i32([int(e.slot) for e in entries])
+        n_new, n_want = _i32([t.size for t in news]), _i32([w.size for w in wants])
+        tokens = np.ascontiguousarray(np.concatenate(news))
+        want_flat = np.ascontiguousarray(np.concatenate(wants))
+        host = _host()
+        T_, W_ = _L(0), _L(0)
+        if host.ri_step_check(B, slots.ctypes.data, n_new.ctypes.data, tokens.ctypes.data, V, n_want.ctypes.data,
+                              want_flat.ctypes.data, ctypes.byref(T_), ctypes.byref(W_)):
+            raise StepError(host.ri_last_error().decode(errors="replace"))
+        T, W = T_.value, W_.value
+        before = _i32(self.cache.extend(list(zip(slots.tolist(), n_new.tolist()))))
         self.cache.upload()
 
-        B = len(entries)
-        T = sum(len(t) for t in news)
-        W = sum(len(w) for w in wants)
-        decode = all(len(t) == 1 for t in news)
-        graphable = self.use_graphs and decode and W == B and all(w == [0] for w in wants)
+        decode = T == B
+        graphable = self.use_graphs and decode and bool((n_want == 1).all()) and bool((want_flat == 0).all())
         tables = self._tables_for(T, B, W, graphable)
         tables.wait_host_free()
-        ids, tok_seq, tok_pos, want_rows = (tables.part(i, host=True) for i in range(4))
-        seq_slot, seq_start, seq_len = (tables.part(i, host=True) for i in range(4, 7))
-        t0 = w0 = 0
-        for b, (toks, w, s, L) in enumerate(zip(news, wants, slots, before)):
-            n = len(toks)
-            ids[t0:t0 + n] = toks
-            tok_seq[t0:t0 + n] = b
-            tok_pos[t0:t0 + n] = np.arange(L, L + n)
-            want_rows[w0:w0 + len(w)] = [t0 + i for i in w]
-            seq_slot[b], seq_start[b], seq_len[b] = s, t0, L + n
-            t0 += n
-            w0 += len(w)
-        seq_start[B] = T
+        max_new, max_len = _I(0), _I(0)
+        host.ri_step_fill(B, slots.ctypes.data, before.ctypes.data, n_new.ctypes.data, tokens.ctypes.data,
+                          n_want.ctypes.data, want_flat.ctypes.data, T, W, tables.host_np.ctypes.data,
+                          ctypes.byref(max_new), ctypes.byref(max_len))
+        tables.decode_constants = False            # the general path writes every column
         tables.upload()
+        after = before + n_new
         ctx = StepContext(
             tok_seq=tables.part(1), tok_pos=tables.part(2), seq_slot=tables.part(4), seq_start=tables.part(5),
-            seq_len=tables.part(6), num_tokens=T, num_seqs=B, max_new=max(len(t) for t in news),
-            max_len=max(L + len(t) for L, t in zip(before, news)), host_seq_slot=tuple(slots),
-            host_new=tuple(len(t) for t in news), host_len=tuple(L + len(t) for L, t in zip(before, news)))
+            seq_len=tables.part(6), num_tokens=T, num_seqs=B, max_new=max_new.value, max_len=max_len.value,
+            host_seq_slot=tuple(slots.tolist()), host_new=tuple(n_new.tolist()), host_len=tuple(after.tolist()))
+        slots = slots.tolist()
         if W == 0:
             want_dev = tables.part(2)[:0]
         else:
@@ -194,35 +216,30 @@ class Engine:
     def _step_one_token_each(self, entries, V, slots=None, ids_dev=None) -> torch.Tensor:
         """The decode step: every sequence brings one token and wants its logits.  Same
         result as the general path, with the host work cut to a few array writes."""
+        host = _host()
+        toks = None
         if ids_dev is None:
-            toks = [int(e.tokens[0]) for e in entries]
-            if min(toks) < 0 or max(toks) >= V:
-                raise StepError(f"token id outside the vocabulary of {V}")
+            toks = np.ascontiguousarray([int(e.tokens[0]) for e in entries], dtype=np.int64)
+            if host.ri_step_check_decode(len(toks), toks.ctypes.data, V):
+                raise StepError(host.ri_last_error().decode(errors="replace"))
             slots = [int(e.slot) for e in entries]
-        else:
-            toks = 0                                      # filled in on the device below
         B = len(slots)
-        before = self.cache.extend([(s, 1) for s in slots])
+        before = _i32(self.cache.extend([(s, 1) for s in slots]))
         self.cache.upload()
         tables = self._tables_for(B, B, B, self.use_graphs)
         tables.wait_host_free()
-        h = tables.host_np
-        if not tables.decode_constants:
-            h[B:2 * B] = np.arange(B)                     # tok_seq
-            h[3 * B:4 * B] = np.arange(B)                 # want_rows
-            h[5 * B:6 * B + 1] = np.arange(B + 1)         # seq_start
-            tables.decode_constants = True
-        h[0:B] = toks
-        h[2 * B:3 * B] = before                           # tok_pos
-        h[4 * B:5 * B] = slots
-        after = [L + 1 for L in before]
-        h[6 * B + 1:7 * B + 1] = after                    # seq_len
+        slots_np = _i32(slots)
+        max_len = _I(0)
+        host.ri_step_fill_decode(B, slots_np.ctypes.data, before.ctypes.data, None if toks is None else toks.ctypes.data,
+                                 0 if tables.decode_constants else 1, tables.host_np.ctypes.data, ctypes.byref(max_len))
+        tables.decode_constants = True
+        after = (before + 1).tolist()
         tables.upload()
         if ids_dev is not None:
             tables.part(0).copy_(ids_dev)                 # device to device, after the upload in stream order
         ctx = StepContext(
             tok_seq=tables.part(1), tok_pos=tables.part(2), seq_slot=tables.part(4), seq_start=tables.part(5),
-            seq_len=tables.part(6), num_tokens=B, num_seqs=B, max_new=1, max_len=max(after),
+            seq_len=tables.part(6), num_tokens=B, num_seqs=B, max_new=1, max_len=max_len.value,
             host_seq_slot=tuple(slots), host_new=(1,) * B, host_len=tuple(after))
         if self.use_graphs:
             logits = self._decode_step(tables, ctx, tables.part(3))
