@@ -8,6 +8,7 @@ libraries (or without nvcc to make them) they raise.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -40,11 +41,11 @@ _SIGNATURES = {
 DECODE_CHUNK = 128          # keys per partial result of the decode attention kernel
 MAX_FAST_HEAD_DIM = 256
 TCGEN05_HEAD_DIMS = (64, 128)   # head sizes the tcgen05 prefill attention kernel is built for
-_NO_TCGEN05 = __import__("os").environ.get("RUST_INFERENCE_B200_NO_TCGEN05") == "1"   # for comparisons
+_NO_TCGEN05 = os.environ.get("RUST_INFERENCE_B200_NO_TCGEN05") == "1"   # for comparisons
 # the skinny linear applies the SiLU gate in its epilogue (one kernel less per layer: 2 % faster at batch 1 of
 # Qwen3-8B shapes, 0.3 % at batch 8); RUST_INFERENCE_B200_FUSED_SWIGLU=0 takes the separate kernel, for comparisons
-_FUSED_SWIGLU = __import__("os").environ.get("RUST_INFERENCE_B200_FUSED_SWIGLU", "1") != "0"
-_WEIGHT_HINTS = __import__("os").environ.get("RUST_INFERENCE_B200_WEIGHT_HINTS", "1") != "0"
+_FUSED_SWIGLU = os.environ.get("RUST_INFERENCE_B200_FUSED_SWIGLU", "1") != "0"
+_WEIGHT_HINTS = os.environ.get("RUST_INFERENCE_B200_WEIGHT_HINTS", "1") != "0"
 SKINNY_MAX_TOKENS = 16      # up to here the bfloat16 linear is this package's weight-streaming kernel
 # For 17 to 128 tokens there is a tcgen05 weight-streaming kernel of this package as well (linear_stream_tc).  Measured
 # at 64 tokens and Qwen3-8B shapes, replayed from a graph: 14.6 / 12.0 / 37.1 / 22.6 us for the four linears of a layer
@@ -52,8 +53,8 @@ SKINNY_MAX_TOKENS = 16      # up to here the bfloat16 linear is this package's w
 # 3 % slower: so it is taken for wide matrices only (the output head: 65,536 outputs and more), or for all of them
 # when RUST_INFERENCE_B200_STREAM_TC=1 asks for it.
 STREAM_TC_MAX_TOKENS = 128
-STREAM_TC_WIDE = int(__import__("os").environ.get("RUST_INFERENCE_B200_STREAM_TC_WIDE", "65536"))   # from this many outputs on it is taken anyway
-_STREAM_TC = __import__("os").environ.get("RUST_INFERENCE_B200_STREAM_TC") == "1"
+STREAM_TC_WIDE = int(os.environ.get("RUST_INFERENCE_B200_STREAM_TC_WIDE", "65536"))   # from this many outputs on it is taken anyway
+_STREAM_TC = os.environ.get("RUST_INFERENCE_B200_STREAM_TC") == "1"
 _fn_cache = {}
 
 
