@@ -42,6 +42,12 @@ QWEN3_8B = {
     "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
     "max_position_embeddings": 40960,
 }
+# the other sizes the reference's measurements name (the same family, other widths and depths): --model
+SHAPES = {
+    "8b": {},
+    "14b": {"num_hidden_layers": 40, "hidden_size": 5120, "num_attention_heads": 40, "intermediate_size": 17408},
+    "32b": {"num_hidden_layers": 64, "hidden_size": 5120, "num_attention_heads": 64, "intermediate_size": 25600},
+}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 METRIC = "decode tok/s at batch 8, context 4096 (Qwen3-8B shapes, bf16)"
@@ -119,6 +125,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the 36 of the configuration (named in config)")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--model", default="8b", choices=sorted(SHAPES), help="layer sizes: Qwen3-8B (the default), 14B or 32B")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
     a = ap.parse_args()
@@ -141,7 +148,8 @@ def main() -> int:
 
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
-    cfg = dict(QWEN3_8B)
+    cfg = dict(QWEN3_8B, **SHAPES[a.model])
+    name = f"Qwen3-{a.model.upper()}"
     full_layers = cfg["num_hidden_layers"]
     if a.layers:
         cfg["num_hidden_layers"] = a.layers
@@ -242,10 +250,10 @@ def main() -> int:
     clocks.stop()
 
     line = {
-        "metric": METRIC, "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": Wm,
+        "metric": METRIC.replace("batch 8", f"batch {B}").replace("Qwen3-8B", name), "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": Wm,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random-init weights N(0,0.02), uniform random token ids",
-        "config": {"model": "Qwen3-8B shapes", "layers": L, "layers_full": full_layers, "hidden": D, "heads": H,
+        "config": {"model": name + " shapes", "layers": L, "layers_full": full_layers, "hidden": D, "heads": H,
                    "kv_heads": KV, "head_dim": Dh, "intermediate": I, "vocab": V, "global_batch": B,
                    "seq_len": CONTEXT, "ctx_start": ctx0, "prefill_tokens": T, "parallelism": "1 GPU",
                    "l2": "inputs larger than L2 (weights read per step >> 126 MB)", "page_size": engine.cache.page_size,
