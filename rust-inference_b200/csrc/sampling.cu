@@ -29,6 +29,12 @@
 #define SP_BINS (1 << SP_DIGIT)
 #define SP_IDX_BITS 24
 #define SP_PASSES 5            // 5 * 12 = 60 >= 32 + 24 key bits
+// The histogram of a pass is kept SP_SUBS times, one copy per residue of the lane number: logits crowd into few
+// bins of the top digits (sign, exponent), and additions to one address of shared memory run one after another.
+#ifndef SP_SUBS
+#define SP_SUBS 4
+#endif
+#define SP_SMEM_BYTES (SP_SUBS * SP_BINS * 8)
 
 typedef unsigned long long u64;
 
@@ -90,16 +96,25 @@ __device__ u64 radix_select(const RowView& r, float zmax, int counting, u64 floo
     __syncthreads();
     for (int pass = SP_PASSES - 1; pass >= 0; pass--) {
         int shift = pass * SP_DIGIT;
-        for (int b = threadIdx.x; b < SP_BINS; b += blockDim.x) bins[b] = 0;
+        for (int b = threadIdx.x; b < SP_SUBS * SP_BINS; b += blockDim.x) bins[b] = 0;
         __syncthreads();
         u64 prefix = s_prefix;
+        u64* my_bins = bins + (threadIdx.x % SP_SUBS) * SP_BINS;
         for (int i = threadIdx.x; i < r.vocab; i += blockDim.x) {
             float zi = r.z(i);
             u64 k = r.key(i, zi);
             if (k < floor_key) continue;
             if (pass < SP_PASSES - 1 && (k >> (shift + SP_DIGIT)) != (prefix >> (shift + SP_DIGIT))) continue;
             u64 w = weight_of(zi, zmax, counting);
-            if (w) atomicAdd(&bins[(unsigned)(k >> shift) & (SP_BINS - 1)], w);
+            if (w) atomicAdd(&my_bins[(unsigned)(k >> shift) & (SP_BINS - 1)], w);
+        }
+        __syncthreads();
+        // the copies are added into the first (integer sums: the order does not matter)
+        for (int b = threadIdx.x; b < SP_BINS; b += blockDim.x) {
+            u64 t = bins[b];
+#pragma unroll
+            for (int c = 1; c < SP_SUBS; c++) t += bins[c * SP_BINS + b];
+            bins[b] = t;
         }
         __syncthreads();
         if (threadIdx.x < 32) {
@@ -159,7 +174,8 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, const unsi
               const int* __restrict__ seen_rows, long long seen_stride, int vocab, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ penalty,
               const float* __restrict__ uniform, int* __restrict__ out) {
-    __shared__ u64 bins[SP_BINS];
+    extern __shared__ __align__(16) unsigned char sp_smem[];
+    u64* bins = reinterpret_cast<u64*>(sp_smem);              // SP_SUBS copies of SP_BINS bins
     __shared__ u64 red[33];
     __shared__ float fred[33];
     __shared__ int ired[33];
@@ -248,7 +264,13 @@ extern "C" int ri_sample(const float* logits, long long row_stride, int rows, in
     RI_REQUIRE(rows > 0 && vocab > 0, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
     RI_REQUIRE(vocab <= (1 << SP_IDX_BITS), "sample: vocabulary %d exceeds the limit %d", vocab, 1 << SP_IDX_BITS);
     RI_REQUIRE(temperature && uniform && out, "sample: temperature, uniform and out are required");
-    sample_kernel<<<rows, SP_THREADS, 0, stream>>>(logits, row_stride, seen, seen_rows, seen_stride, vocab,
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SP_SMEM_BYTES);
+        if (e != cudaSuccess) RI_FAIL((int)e, "sample: shared memory limit: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    sample_kernel<<<rows, SP_THREADS, SP_SMEM_BYTES, stream>>>(logits, row_stride, seen, seen_rows, seen_stride, vocab,
                                                    temperature, top_k, top_p, penalty, uniform, out);
     RI_CHECK_LAUNCH("sample");
     return 0;

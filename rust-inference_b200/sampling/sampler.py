@@ -70,6 +70,42 @@ def request_seed(seed: int, request_index: int) -> int:
     return (seed ^ ((request_index * 0x9E3779B97F4A7C15) & _MASK)) & _MASK
 
 
+class _Staging:
+    """Small host arrays on their way to the device without stalling the host.
+
+    A copy from ordinary host memory waits for everything the stream holds, which would make
+    the host wait for the whole step it has just launched.  So the arrays go through a ring of
+    pinned buffers, each guarded by an event that says its last copy is done."""
+
+    def __init__(self, device, entries: int = 12):
+        self.device = torch.device(device)
+        self.cuda = self.device.type == "cuda"
+        self.bufs: List[Optional[torch.Tensor]] = [None] * entries
+        self.events = [None] * entries
+        self.next = 0
+
+    def put(self, arr: np.ndarray) -> torch.Tensor:
+        arr = np.ascontiguousarray(arr)
+        if not self.cuda:
+            return torch.from_numpy(arr.copy())
+        i = self.next
+        self.next = (i + 1) % len(self.bufs)
+        buf = self.bufs[i]
+        if buf is None or buf.numel() < arr.nbytes:
+            buf = self.bufs[i] = torch.empty(max(256, 2 * arr.nbytes), dtype=torch.uint8, pin_memory=True)
+            self.events[i] = torch.cuda.Event()
+        else:
+            self.events[i].synchronize()                      # its last copy (several steps ago) is done
+        host = buf[:arr.nbytes].view(_TORCH_OF[arr.dtype.type])
+        host.numpy()[...] = arr.reshape(-1)
+        dev = host.to(self.device, non_blocking=True).view(arr.shape)
+        self.events[i].record()
+        return dev
+
+
+_TORCH_OF = {np.float32: torch.float32, np.int32: torch.int32, np.int64: torch.int64}
+
+
 class Sampler:
     """Samples for the rows of one batch.  ``rows`` are the batch's own row numbers
     (0..n-1, fixed for a sequence's life); they index the random streams and the
@@ -83,6 +119,7 @@ class Sampler:
         self.rngs: List[XorShiftRng] = []
         self.seen: Optional[torch.Tensor] = None
         self._const = None
+        self._staging = _Staging(self.device)
 
     @property
     def uses_context(self) -> bool:
@@ -111,11 +148,11 @@ class Sampler:
         ``tokens`` may be a device tensor."""
         if self.seen is None or len(rows) == 0:
             return
-        r = torch.as_tensor(np.asarray(rows, dtype=np.int32), device=self.device)
+        r = self._staging.put(np.asarray(rows, dtype=np.int32))
         if isinstance(tokens, torch.Tensor):
             t = tokens.to(device=self.device, dtype=torch.int32).contiguous()
         else:
-            t = torch.as_tensor(np.asarray(tokens, dtype=np.int32), device=self.device)
+            t = self._staging.put(np.asarray(tokens, dtype=np.int32))
         ops.mark_seen(self.seen, r, t)
 
     def sample(self, logits: torch.Tensor, rows: Sequence[int]) -> List[int]:
@@ -131,14 +168,14 @@ class Sampler:
             return ops.argmax(logits)
         c = self._const
         contiguous = list(rows) == list(range(n))
-        idx = None if contiguous else torch.as_tensor(np.asarray(rows, dtype=np.int64), device=self.device)
+        idx = None if contiguous else self._staging.put(np.asarray(rows, dtype=np.int64))
 
         def take(t):
             return t[:n] if contiguous else t[idx].contiguous()
         # the reference draws a number only when it does not take the greedy path
         u = [0.0 if p.greedy else self.rngs[r].next_f32() for r in rows]
-        uniform = torch.as_tensor(np.asarray(u, dtype=np.float32), device=self.device)
-        seen_rows = torch.as_tensor(np.asarray(rows, dtype=np.int32), device=self.device) if self.seen is not None else None
+        uniform = self._staging.put(np.asarray(u, dtype=np.float32))
+        seen_rows = self._staging.put(np.asarray(rows, dtype=np.int32)) if self.seen is not None else None
         out = ops.sample(logits, take(c["temperature"]), uniform, top_k=take(c["top_k"]), top_p=take(c["top_p"]),
                          penalty=take(c["penalty"]), seen=self.seen, seen_rows=seen_rows)
         return out
