@@ -256,14 +256,344 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, const unsi
     }
 }
 
+// ---------------------------------------------------------------------------
+// The same selection with several blocks per row, for large vocabularies: a row of 150,000 logits
+// keeps one block busy for more than a millisecond.  The row is cut into slices, a block per slice
+// and row; what the one-block kernel keeps in shared memory between its passes lies in global
+// memory (SpRow, and a histogram of SP_BINS 64-bit sums per row), and every pass is a kernel of
+// its own, so no block ever waits for another.  Sums are integers, so their order does not matter:
+// the token is the one-block kernel's, bit for bit.
+//
+//   sp_max -> sp_begin -> [top-k: select] -> sp_total -> [top-p: select -> sp_total] -> select (the draw)
+//   select = sp_select_begin -> SP_PASSES x (sp_hist -> sp_pick) -> sp_select_end
+// ---------------------------------------------------------------------------
+#define SPW_THREADS 256
+#define SPW_MAX_SLICES 64
+enum { SP_MODE_TOPK = 0, SP_MODE_TOPP = 1, SP_MODE_DRAW = 2 };
+
+struct __align__(16) SpRow {
+    u64 floor_key;       // tokens with a smaller key are out (top-k, top-p)
+    u64 total;           // weight of the tokens that are in
+    u64 prefix, remaining, target;       // the radix search
+    float best, zmax;    // maximum of x; of z
+    int best_idx;        // first index of the maximum: the greedy answer
+    int found, active, counting, done;
+    int pad[5];
+};
+
+struct SpArgs {
+    const float* logits;
+    long long row_stride;
+    const unsigned char* seen;
+    const int* seen_rows;
+    long long seen_stride;
+    int vocab, slices, per_slice;
+    const float* temperature;
+    const int* top_k;
+    const float* top_p;
+    const float* penalty;
+    const float* uniform;
+    int* out;
+    SpRow* st;           // [rows]
+    u64* hist;           // [rows][SP_BINS]
+    float* part_val;     // [rows][slices]
+    int* part_idx;       // [rows][slices]
+};
+
+__device__ __forceinline__ RowView spw_row(const SpArgs& a, int row) {
+    RowView r;
+    r.logits = a.logits + (size_t)row * a.row_stride;
+    r.penalty = a.penalty ? a.penalty[row] : 1.0f;
+    r.seen = (a.seen && r.penalty != 1.0f) ? a.seen + (size_t)(a.seen_rows ? a.seen_rows[row] : row) * a.seen_stride : nullptr;
+    r.temperature = a.temperature[row];
+    r.vocab = a.vocab;
+    return r;
+}
+
+// maximum of x over a slice, with the first index among equals
+__global__ void __launch_bounds__(SPW_THREADS) sp_max_kernel(SpArgs a) {
+    __shared__ float fred[SPW_THREADS / 32];
+    __shared__ int ired[SPW_THREADS / 32];
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.y, s = blockIdx.x;
+    const RowView r = spw_row(a, row);
+    const int lo = s * a.per_slice, hi = min(a.vocab, lo + a.per_slice);
+    float best = -FLT_MAX;
+    int bi = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += SPW_THREADS) {
+        float v = r.x(i);
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { fred[warp] = best; ired[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < SPW_THREADS / 32; w++)
+            if (fred[w] > best || (fred[w] == best && ired[w] < bi)) { best = fred[w]; bi = ired[w]; }
+        a.part_val[(size_t)row * a.slices + s] = best;
+        a.part_idx[(size_t)row * a.slices + s] = bi;
+    }
+}
+
+// one block per row: the row's maximum from the slices', the greedy answer, a clean state and histogram
+__global__ void __launch_bounds__(SPW_THREADS) sp_begin_kernel(SpArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x;
+    u64* hist = a.hist + (size_t)row * SP_BINS;
+    for (int b = threadIdx.x; b < SP_BINS; b += SPW_THREADS) hist[b] = 0;
+    if (threadIdx.x == 0) {
+        float best = -FLT_MAX;
+        int bi = 0x7fffffff;
+        for (int s = 0; s < a.slices; s++) {
+            const float v = a.part_val[(size_t)row * a.slices + s];
+            const int i = a.part_idx[(size_t)row * a.slices + s];
+            if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+        }
+        if (bi == 0x7fffffff) bi = 0;          // a row of NaN: the reference's loop also ends at index 0
+        SpRow& st = a.st[row];
+        const float t = a.temperature[row];
+        st.best = best;
+        st.best_idx = bi;
+        st.floor_key = 0;
+        st.total = 0;
+        st.done = !(t > 0.0f);
+        st.zmax = st.done ? 0.0f : best / t;
+        st.found = 0;
+        st.active = 0;
+        st.counting = 0;
+        if (st.done) a.out[row] = bi;          // temperature <= 0: greedy
+    }
+}
+
+// weight of the slice's tokens that are in, added to the row's total
+__global__ void __launch_bounds__(SPW_THREADS) sp_total_kernel(SpArgs a) {
+    __shared__ u64 red[33];
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.y, s = blockIdx.x;
+    const SpRow& st = a.st[row];
+    if (st.done) return;
+    const RowView r = spw_row(a, row);
+    const float zmax = st.zmax;
+    const u64 floor_key = st.floor_key;
+    const int lo = s * a.per_slice, hi = min(a.vocab, lo + a.per_slice);
+    u64 part = 0;
+    for (int i = lo + threadIdx.x; i < hi; i += SPW_THREADS) {
+        float zi = r.z(i);
+        if (r.key(i, zi) >= floor_key) part += weight_of(zi, zmax, 0);
+    }
+    part = block_sum_u64(part, red);
+    if (threadIdx.x == 0 && part) atomicAdd(&a.st[row].total, part);
+}
+
+
+// one thread per row: whether this search applies to the row, and its target
+__global__ void sp_select_begin_kernel(SpArgs a, int mode, int rows) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= rows) return;
+    SpRow& st = a.st[row];
+    st.active = 0;
+    if (st.done) return;
+    if (mode == SP_MODE_TOPK) {
+        const int k = a.top_k ? a.top_k[row] : 0;
+        if (k > 0 && k < a.vocab) {
+            st.active = 1;
+            st.counting = 1;
+            st.target = (u64)k;
+        }
+    } else if (mode == SP_MODE_TOPP) {
+        const float tp = a.top_p ? a.top_p[row] : 1.0f;
+        if (tp < 1.0f) {
+            const double want = (double)tp * (double)st.total;
+            u64 target = (u64)want;
+            if ((double)target < want) target += 1;           // ceil
+            if (target < 1) target = 1;
+            st.active = 1;
+            st.counting = 0;
+            st.target = target;
+        }
+    } else {
+        const double ru = (double)a.uniform[row] * (double)st.total;
+        u64 target = (u64)ru + 1;                             // running sum > u * total
+        if (target > st.total) target = st.total;
+        st.active = 1;
+        st.counting = 0;
+        st.target = target;
+    }
+    if (st.active) {
+        st.prefix = 0;
+        st.remaining = st.target;
+        st.found = 1;
+    }
+}
+
+// one digit of the search: the slice's histogram of that digit, added to the row's
+__global__ void __launch_bounds__(SPW_THREADS) sp_hist_kernel(SpArgs a, int pass) {
+    __shared__ u64 bins[SP_BINS];
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.y, s = blockIdx.x;
+    const SpRow& st = a.st[row];
+    if (!st.active || !st.found) return;
+    const RowView r = spw_row(a, row);
+    const float zmax = st.zmax;
+    const u64 floor_key = st.floor_key, prefix = st.prefix;
+    const int counting = st.counting, shift = pass * SP_DIGIT;
+    for (int b = threadIdx.x; b < SP_BINS; b += SPW_THREADS) bins[b] = 0;
+    __syncthreads();
+    const int lo = s * a.per_slice, hi = min(a.vocab, lo + a.per_slice);
+    for (int i = lo + threadIdx.x; i < hi; i += SPW_THREADS) {
+        float zi = r.z(i);
+        u64 k = r.key(i, zi);
+        if (k < floor_key) continue;
+        if (pass < SP_PASSES - 1 && (k >> (shift + SP_DIGIT)) != (prefix >> (shift + SP_DIGIT))) continue;
+        u64 w = weight_of(zi, zmax, counting);
+        if (w) atomicAdd(&bins[(unsigned)(k >> shift) & (SP_BINS - 1)], w);
+    }
+    __syncthreads();
+    u64* hist = a.hist + (size_t)row * SP_BINS;
+    for (int b = threadIdx.x; b < SP_BINS; b += SPW_THREADS)
+        if (bins[b]) atomicAdd(&hist[b], bins[b]);
+}
+
+// one block per row: the bin of this digit in which the target is reached; the histogram is left clean
+__global__ void __launch_bounds__(SPW_THREADS) sp_pick_kernel(SpArgs a, int pass) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x;
+    SpRow& st = a.st[row];
+    __shared__ int go;                     // read once for the block: a lane below may clear `found`
+    if (threadIdx.x == 0) go = st.active && st.found;
+    __syncthreads();
+    if (!go) return;
+    u64* hist = a.hist + (size_t)row * SP_BINS;
+    const int shift = pass * SP_DIGIT;
+    if (threadIdx.x < 32) {
+        // lane l owns bins [128 l, 128 l + 127]; walk from the top bin down
+        const int lane = threadIdx.x;
+        const int per = SP_BINS / 32;
+        u64 mine = 0;
+        for (int b = 0; b < per; b++) mine += hist[lane * per + b];
+        u64 above = 0;                                        // weight of all bins above this lane's range
+        for (int l = 31; l > 0; l--) {
+            u64 v = __shfl_sync(0xffffffffu, mine, l);
+            if (lane < l) above += v;
+        }
+        const u64 remaining = st.remaining, prefix = st.prefix;
+        const int owner = (above < remaining && above + mine >= remaining) ? 1 : 0;
+        const unsigned ballot = __ballot_sync(0xffffffffu, owner);
+        if (ballot == 0) {
+            if (lane == 0) st.found = 0;
+        } else if (owner) {
+            u64 acc = above;
+            int chosen = lane * per;
+            for (int b = per - 1; b >= 0; b--) {
+                u64 w = hist[lane * per + b];
+                if (acc + w >= remaining) { chosen = lane * per + b; break; }
+                acc += w;
+            }
+            st.prefix = prefix | ((u64)chosen << shift);
+            st.remaining = remaining - acc;
+        }
+    }
+    __syncthreads();
+    for (int b = threadIdx.x; b < SP_BINS; b += SPW_THREADS) hist[b] = 0;
+}
+
+// one thread per row: what the search found becomes the new floor (top-k, top-p) or the token (the draw)
+__global__ void sp_select_end_kernel(SpArgs a, int mode, int rows) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= rows) return;
+    SpRow& st = a.st[row];
+    if (st.done) return;
+    if (mode == SP_MODE_DRAW) {
+        int tok = st.best_idx;                                // cannot happen for total > 0; stay in range
+        if (st.active && st.found && st.total != 0)
+            tok = (int)(((1u << SP_IDX_BITS) - 1u) - (unsigned)(st.prefix & ((1u << SP_IDX_BITS) - 1u)));
+        a.out[row] = tok;
+        return;
+    }
+    if (st.active && st.found) st.floor_key = st.prefix;
+    st.total = 0;                                             // the kernel after this one sums what is in now
+}
+
+static size_t spw_align(size_t n) { return (n + 255) & ~(size_t)255; }
+static int spw_slices(int vocab) {
+    int s = (vocab + 2047) / 2048;
+    return s < 1 ? 1 : (s > SPW_MAX_SLICES ? SPW_MAX_SLICES : s);
+}
+
+// bytes of scratch memory the several-blocks-per-row selection needs
+extern "C" long long ri_sample_work_bytes(int rows, int vocab) {
+    const int slices = spw_slices(vocab);
+    return (long long)(spw_align((size_t)rows * sizeof(SpRow)) + spw_align((size_t)rows * SP_BINS * sizeof(u64)) +
+                       2 * spw_align((size_t)rows * slices * 4));
+}
+
+static int launch_sample_wide(SpArgs a, int rows, void* work, int use_top_k, int use_top_p, cudaStream_t stream) {
+    unsigned char* w = (unsigned char*)work;
+    a.slices = spw_slices(a.vocab);
+    a.per_slice = (a.vocab + a.slices - 1) / a.slices;
+    a.st = (SpRow*)w;
+    w += spw_align((size_t)rows * sizeof(SpRow));
+    a.hist = (u64*)w;
+    w += spw_align((size_t)rows * SP_BINS * sizeof(u64));
+    a.part_val = (float*)w;
+    w += spw_align((size_t)rows * a.slices * 4);
+    a.part_idx = (int*)w;
+    const dim3 wide(a.slices, rows), per_row(rows), few((rows + 127) / 128);
+    auto select = [&](int mode) {
+        ri_launch_pdl(sp_select_begin_kernel, few, dim3(128), 0, stream, a, mode, rows);
+        for (int pass = SP_PASSES - 1; pass >= 0; pass--) {
+            ri_launch_pdl(sp_hist_kernel, wide, dim3(SPW_THREADS), 0, stream, a, pass);
+            ri_launch_pdl(sp_pick_kernel, per_row, dim3(SPW_THREADS), 0, stream, a, pass);
+        }
+        ri_launch_pdl(sp_select_end_kernel, few, dim3(128), 0, stream, a, mode, rows);
+    };
+    ri_launch_pdl(sp_max_kernel, wide, dim3(SPW_THREADS), 0, stream, a);
+    ri_launch_pdl(sp_begin_kernel, per_row, dim3(SPW_THREADS), 0, stream, a);
+    if (use_top_k && a.top_k) select(SP_MODE_TOPK);
+    ri_launch_pdl(sp_total_kernel, wide, dim3(SPW_THREADS), 0, stream, a);
+    if (use_top_p && a.top_p) {
+        select(SP_MODE_TOPP);
+        ri_launch_pdl(sp_total_kernel, wide, dim3(SPW_THREADS), 0, stream, a);
+    }
+    select(SP_MODE_DRAW);
+    RI_CHECK_LAUNCH("sample (several blocks per row)");
+    return 0;
+}
+
 extern "C" int ri_sample(const float* logits, long long row_stride, int rows, int vocab, const unsigned char* seen,
                          const int* seen_rows, long long seen_stride, const float* temperature, const int* top_k,
                          const float* top_p, const float* penalty, const float* uniform, int* out,
-                         cudaStream_t stream) {
+                         void* work, long long work_bytes, int use_top_k, int use_top_p, cudaStream_t stream) {
     if (rows == 0) return 0;
     RI_REQUIRE(rows > 0 && vocab > 0, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
     RI_REQUIRE(vocab <= (1 << SP_IDX_BITS), "sample: vocabulary %d exceeds the limit %d", vocab, 1 << SP_IDX_BITS);
     RI_REQUIRE(temperature && uniform && out, "sample: temperature, uniform and out are required");
+    if (work) {
+        // several blocks per row (the caller gives scratch memory for it): large vocabularies
+        RI_REQUIRE(work_bytes >= ri_sample_work_bytes(rows, vocab), "sample: %lld bytes of scratch memory, %lld needed",
+                   work_bytes, ri_sample_work_bytes(rows, vocab));
+        RI_REQUIRE(rows <= 65535, "sample: %d rows", rows);
+        SpArgs a{};
+        a.logits = logits; a.row_stride = row_stride; a.seen = seen; a.seen_rows = seen_rows; a.seen_stride = seen_stride;
+        a.vocab = vocab; a.temperature = temperature; a.top_k = top_k; a.top_p = top_p; a.penalty = penalty;
+        a.uniform = uniform; a.out = out;
+        return launch_sample_wide(a, rows, work, use_top_k, use_top_p, stream);
+    }
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SP_SMEM_BYTES);

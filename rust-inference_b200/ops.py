@@ -29,7 +29,8 @@ _SIGNATURES = {
     ("rope_kv", "ri_qk_norm_rope_append"): [_P] * 10 + [_F, _P, _I, _I] + [_I] * 9 + [_P, _P],
     ("attention_plain", "ri_attention_plain"): [_P] * 8 + [_I] * 7 + [_F, _I, _I, _P, _P],
     ("linear_f32", "ri_linear_f32"): [_P, _P, _P, _I, _I, _I, _P],
-    ("sampling", "ri_sample"): [_P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P],
+    ("sampling", "ri_sample"): [_P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _P],
+    ("sampling", "ri_sample_work_bytes"): [_I, _I],
     ("sampling", "ri_argmax"): [_P, _L, _I, _I, _P, _P, _P, _P],
     ("sampling", "ri_mark_seen"): [_P, _L, _P, _P, _I, _I, _P],
     ("attention_decode", "ri_attention_decode"): [_P] * 9 + [_I] * 8 + [_F, _I, _P, _P],
@@ -55,6 +56,9 @@ SKINNY_MAX_TOKENS = 16      # up to here the bfloat16 linear is this package's w
 STREAM_TC_MAX_TOKENS = 128
 STREAM_TC_WIDE = int(os.environ.get("RUST_INFERENCE_B200_STREAM_TC_WIDE", "65536"))   # from this many outputs on it is taken anyway
 _STREAM_TC = os.environ.get("RUST_INFERENCE_B200_STREAM_TC") == "1"
+# the selection of a token other than the greedy one: from this many logits a row on, several blocks per row
+SAMPLE_WIDE_VOCAB = 16384
+_SAMPLE_WIDE = os.environ.get("RUST_INFERENCE_B200_SAMPLE_WIDE", "1") != "0"
 _fn_cache = {}
 
 
@@ -69,7 +73,7 @@ def _fn(lib_name: str, fn_name: str, defines=None):
         lib = _build.library(lib_name, defines)
         f = getattr(lib, fn_name)
         f.argtypes = _SIGNATURES[(lib_name, fn_name)]
-        f.restype = _I
+        f.restype = _L if fn_name.endswith("_bytes") else _I
         _fn_cache[key] = f = (f, lib)
     return f
 
@@ -430,10 +434,14 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
 def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
            top_k: Optional[torch.Tensor] = None, top_p: Optional[torch.Tensor] = None,
            penalty: Optional[torch.Tensor] = None, seen: Optional[torch.Tensor] = None,
-           seen_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+           seen_rows: Optional[torch.Tensor] = None, uses_top_k: bool = True, uses_top_p: bool = True) -> torch.Tensor:
     """One token per row of float32 ``logits`` [rows, vocab]; the options are
     per-row device tensors (temperature float32, top_k int32, top_p float32,
-    penalty float32), ``uniform`` the per-row number in [0, 1)."""
+    penalty float32), ``uniform`` the per-row number in [0, 1).
+
+    From ``SAMPLE_WIDE_VOCAB`` logits a row on, several blocks work on each row (the same
+    token, bit for bit); a caller that knows that no row has a top-k or a top-p says so
+    with ``uses_top_k`` / ``uses_top_p`` and saves those searches."""
     _need(logits, "logits", torch.float32)
     rows, vocab = logits.shape
     _need(temperature, "temperature", torch.float32, (rows,))
@@ -453,9 +461,17 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
         if seen_rows is not None:
             _need(seen_rows, "seen_rows", torch.int32, (rows,))
     out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    work, work_bytes = None, 0
+    if _SAMPLE_WIDE and vocab >= SAMPLE_WIDE_VOCAB:
+        f, _ = _fn("sampling", "ri_sample_work_bytes")
+        work_bytes = int(f(rows, vocab))
+        work = torch.empty(work_bytes, dtype=torch.uint8, device=logits.device)
+    k_on, p_on = bool(uses_top_k and top_k is not None), bool(uses_top_p and top_p is not None)
     _call("sampling", "ri_sample", logits.data_ptr(), logits.stride(0), rows, vocab, _ptr(seen), _ptr(seen_rows),
           seen_stride, temperature.data_ptr(), _ptr(top_k), _ptr(top_p), _ptr(penalty), uniform.data_ptr(),
-          out.data_ptr(), _stream())
+          out.data_ptr(), _ptr(work), work_bytes, int(k_on), int(p_on), _stream())
+    if work is not None:
+        add_launches(2 + 12 * (1 + k_on + p_on) + p_on)          # one was counted by the call
     return out
 
 

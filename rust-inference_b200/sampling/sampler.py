@@ -177,5 +177,6 @@ class Sampler:
         uniform = self._staging.put(np.asarray(u, dtype=np.float32))
         seen_rows = self._staging.put(np.asarray(rows, dtype=np.int32)) if self.seen is not None else None
         out = ops.sample(logits, take(c["temperature"]), uniform, top_k=take(c["top_k"]), top_p=take(c["top_p"]),
-                         penalty=take(c["penalty"]), seen=self.seen, seen_rows=seen_rows)
+                         penalty=take(c["penalty"]), seen=self.seen, seen_rows=seen_rows,
+                         uses_top_k=p.top_k > 0, uses_top_p=p.top_p < 1.0)
         return out

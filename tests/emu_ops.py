@@ -113,7 +113,8 @@ def argmax(logits):
     return torch.argmax(logits, dim=-1).to(torch.int32)      # torch returns the first maximum on the CPU
 
 
-def sample(logits, temperature, uniform, top_k=None, top_p=None, penalty=None, seen=None, seen_rows=None):
+def sample(logits, temperature, uniform, top_k=None, top_p=None, penalty=None, seen=None, seen_rows=None,
+           uses_top_k=True, uses_top_p=True):
     from plain_qwen3 import plain_sample
 
     class _Fixed:

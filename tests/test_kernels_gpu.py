@@ -361,6 +361,44 @@ def test_sample_matches_plain(vocab):
             assert sum(int(g != w) for g, w in zip(got, want)) <= 1, f"{c}: device {got}, plain {want}"
 
 
+@pytest.mark.parametrize("vocab", [16384, 40001, 151936])
+def test_sample_with_several_blocks_per_row_picks_the_same_token(vocab, monkeypatch):
+    """Large vocabularies are sampled by several blocks per row; the token is the one the one-block kernel
+    picks, for every mix of options within a batch (rows with and without top-k, top-p, a penalty, greedy rows)."""
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(vocab)
+    rows = 37
+    logits = (rng.standard_normal((rows, vocab)) * 3).astype(np.float32)
+    logits[5, 100] = logits[5, 9000] = logits[5].max() + 0.5             # equal logits at the top
+    logits[6, :] = 0.25                                                   # a flat row
+    temperature = rng.choice([0.0, 0.5, 0.8, 1.0, 1.7], size=rows).astype(np.float32)
+    top_k = rng.choice([0, 0, 1, 7, 50, 3000], size=rows).astype(np.int32)
+    top_p = rng.choice([1.0, 1.0, 0.95, 0.6, 0.1], size=rows).astype(np.float32)
+    penalty = rng.choice([1.0, 1.0, 1.3, 2.5], size=rows).astype(np.float32)
+    seen = (rng.random((rows, vocab)) < 0.01).astype(np.uint8)
+    seen_rows = rng.permutation(rows).astype(np.int32)
+    args = dict(top_k=dev(top_k, torch.int32), top_p=dev(top_p), penalty=dev(penalty), seen=dev(seen, torch.uint8),
+                seen_rows=dev(seen_rows, torch.int32))
+    for trial in range(6):
+        u = rng.random(rows).astype(np.float32)
+        if trial == 0:
+            u[:4] = [0.0, 0.99999994, 0.5, 1e-7]
+        monkeypatch.setattr(ops, "_SAMPLE_WIDE", True)
+        wide = ops.sample(dev(logits), dev(temperature), dev(u), **args).cpu().numpy()
+        monkeypatch.setattr(ops, "_SAMPLE_WIDE", False)
+        one = ops.sample(dev(logits), dev(temperature), dev(u), **args).cpu().numpy()
+        assert wide.tolist() == one.tolist(), trial
+    # without the searches that a caller rules out: plain temperature rows
+    monkeypatch.setattr(ops, "_SAMPLE_WIDE", True)
+    u = rng.random(rows).astype(np.float32)
+    t = dev(np.full(rows, 0.7, dtype=np.float32))
+    wide = ops.sample(dev(logits), t, dev(u), uses_top_k=False, uses_top_p=False).cpu().numpy()
+    monkeypatch.setattr(ops, "_SAMPLE_WIDE", False)
+    one = ops.sample(dev(logits), t, dev(u)).cpu().numpy()
+    assert wide.tolist() == one.tolist()
+    assert int(ops.error_flag("cuda").item()) == 0
+
+
 def _ideal_sample(logits, history, u, dp=0.0, temperature=0.0, top_k=0, top_p=1.0, repetition_penalty=1.0):
     """The reference's rule (src/sampling.rs:73-128 there) with exact sums."""
     x = np.array(logits, dtype=np.float32)
