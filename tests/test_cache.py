@@ -128,3 +128,13 @@ def test_misuse():
         c.extend([(s, 1), (s, 1)])
     with pytest.raises(CacheError):
         c.extend([(s, 4 * 32 + 1)])
+
+
+def test_sizes_that_make_no_cache_are_refused():
+    with pytest.raises(CacheError):
+        SlotAllocator(0)
+    with pytest.raises(CacheError):
+        PageTable(num_slots=2, num_pages=0, max_pages_per_seq=3, page_size=32)
+    with pytest.raises(CacheError):
+        Cache([CacheRequest(kv_heads=1, head_dim=16)], num_slots=0, num_pages=4, max_pages_per_seq=2,
+              dtype=torch.float32, device="cpu")
