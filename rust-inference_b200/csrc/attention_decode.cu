@@ -106,7 +106,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     const bool page_live = key0 < len && key0 + AD_PAGE > first_key;
     int page = -1;
     if (page_live) {
-        page = page_table[(size_t)slot * mpps + key0 / AD_PAGE];
+        page = key0 / AD_PAGE < mpps ? page_table[(size_t)slot * mpps + key0 / AD_PAGE] : -1;    // past the row: as unmapped
         if (page < 0 || page >= num_pages) {
             if (lane == 0) atomicExch(err, 4);
             page = -1;
@@ -342,14 +342,14 @@ struct StreamArgs {
     const int* page_table;
     const int* seq_slot;
     const int* seq_len;
-    int seqs, KV, mpps, num_pages, n_items, chunk_pages, window, stride;
+    int seqs, KV, mpps, num_pages, n_items, chunk_pages, window, stride, max_pages;
     int* err;
 };
 
 __device__ __forceinline__ void stream_load_ids(StreamCursor& c, const StreamArgs& a, int lane) {
     c.ids_base = c.p;
     int pg = c.p + lane;
-    int id = (pg < c.p_end) ? a.page_table[(size_t)c.slot_row * a.mpps + pg] : 0;
+    int id = (pg < c.p_end) ? (pg < a.mpps ? a.page_table[(size_t)c.slot_row * a.mpps + pg] : -1) : 0;
     if (id < 0 || id >= a.num_pages) {
         atomicExch(a.err, 4);
         id = 0;
@@ -370,6 +370,7 @@ __device__ __forceinline__ bool stream_open(StreamCursor& c, const StreamArgs& a
         c.first_key = (a.window > 0 && c.len - a.window > 0) ? c.len - a.window : 0;
         int p_lo = c.chunk * a.chunk_pages, p_hi = p_lo + a.chunk_pages;
         int p_first = c.first_key / AD_PAGE, p_last = (c.len + AD_PAGE - 1) / AD_PAGE;
+        p_last = p_last < a.max_pages ? p_last : a.max_pages;     // no partial result has a place beyond (the merge reports it)
         c.p = p_lo > p_first ? p_lo : p_first;
         c.p_end = p_hi < p_last ? p_hi : p_last;
         if (c.p < c.p_end) {
@@ -669,7 +670,7 @@ static int pool_tensor_map(CUtensorMap* map, const void* pool, long long rows) {
 __global__ void __launch_bounds__(AD_MERGE_THREADS)
 attention_decode_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
                               bf16* __restrict__ out, const int* __restrict__ seq_len, int H, int max_chunks,
-                              int window) {
+                              int window, int* __restrict__ err) {
     constexpr int MW = AD_MERGE_THREADS / 32;            // warps
     constexpr int PER = (AD_DH + 127) / 128;             // float4 per lane
     const int h = blockIdx.x, b = blockIdx.y;
@@ -678,7 +679,14 @@ attention_decode_merge_kernel(const float* __restrict__ o_part, const float* __r
     pdl_wait();
     const int len = seq_len[b];
     const int first_key = (window > 0 && len - window > 0) ? len - window : 0;
-    const int c_lo = first_key / AD_CHUNK, c_hi = (len + AD_CHUNK - 1) / AD_CHUNK;     // [c_lo, c_hi)
+    int c_lo = first_key / AD_CHUNK, c_hi = (len + AD_CHUNK - 1) / AD_CHUNK;           // [c_lo, c_hi)
+    if (c_hi > max_chunks) {
+        // the caller's scratch memory has no partial results for the keys past max_chunks * 128: they are left
+        // out (nothing is read past the sequence's rows) and the mistake is reported
+        if (threadIdx.x == 0) atomicExch(err, 7);
+        c_hi = max_chunks;
+        c_lo = c_lo < c_hi ? c_lo : c_hi;
+    }
     const float* ml = ml_part + ((size_t)b * H + h) * max_chunks * 2;
     const float* op = o_part + ((size_t)b * H + h) * max_chunks * AD_DH;
     __shared__ float s_w[AD_MERGE_TILE], s_red[MW], s_l[MW];
@@ -738,23 +746,29 @@ attention_decode_merge_kernel(const float* __restrict__ o_part, const float* __r
         float a = s_acc[0][d];
 #pragma unroll
         for (int w = 1; w < MW; w++) a += s_acc[w][d];
-        out[((size_t)b * H + h) * AD_DH + d] = __float2bfloat16_rn(a / L);
+        out[((size_t)b * H + h) * AD_DH + d] = __float2bfloat16_rn(L > 0.0f ? a / L : 0.0f);
     }
 }
 
 extern "C" int ri_attention_decode_head_dim() { return AD_DH; }
 extern "C" int ri_attention_decode_chunk() { return AD_CHUNK; }
 
-// shared memory of a launch with G query heads per kv head; raises the kernel's limit when it grows
+// shared memory of a launch with G query heads per kv head; on a device's first call the kernel's limit is set to
+// the most any group size needs, so that no later call (of either entry point of this library) has to touch it
+#define AD_MAX_DEVICES 64
 static int decode_configure(int G, size_t* smem_out) {
-    static size_t configured = 0;
-    size_t smem = decode_smem_bytes(G < AD_ROWS ? G : AD_ROWS);
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static bool configured[AD_MAX_DEVICES];
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) RI_FAIL((int)e, "attention_decode: cudaGetDevice: %s", cudaGetErrorString(e));
+    RI_REQUIRE(device >= 0 && device < AD_MAX_DEVICES, "attention_decode: device %d", device);
+    if (!configured[device]) {
+        e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)decode_smem_bytes(AD_ROWS));
         if (e != cudaSuccess) RI_FAIL((int)e, "attention_decode: shared memory limit: %s", cudaGetErrorString(e));
-        configured = smem;
+        configured[device] = true;
     }
-    *smem_out = smem;
+    *smem_out = decode_smem_bytes(G < AD_ROWS ? G : AD_ROWS);
     return 0;
 }
 
@@ -828,6 +842,7 @@ extern "C" int ri_attention_decode(const void* q, const void* k_pool, const void
         RI_REQUIRE(n_items < (1ll << 30), "attention_decode: %lld items", n_items);
         a.n_items = (int)n_items;
         a.chunk_pages = chunk_pages;
+        a.max_pages = max_pages;
         a.window = window;
         a.err = err_flag;
         const long long smallest = (long long)seqs * KV * ((max_pages + 3) / 4);       // items of four pages
@@ -842,7 +857,7 @@ extern "C" int ri_attention_decode(const void* q, const void* k_pool, const void
             rc = launch_stream<ADS_WARPS, ADS_SLOTS>(blocks, stream, (const bf16*)q, map_k, map_v, o_part, ml_part, a, H, max_chunks, scale_log2);
         if (rc) return rc;
         ri_launch_pdl(attention_decode_merge_kernel, dim3(H, seqs), dim3(AD_MERGE_THREADS), 0, stream,
-                      (const float*)o_part, (const float*)ml_part, (bf16*)out, seq_len, H, max_chunks, window);
+                      (const float*)o_part, (const float*)ml_part, (bf16*)out, seq_len, H, max_chunks, window, err_flag);
         RI_CHECK_LAUNCH("attention_decode_merge");
         return 0;
     }
@@ -856,7 +871,7 @@ extern "C" int ri_attention_decode(const void* q, const void* k_pool, const void
                   H, KV, mpps, num_pages, max_chunks, scale * 1.4426950408889634f, window, err_flag);
     RI_CHECK_LAUNCH("attention_decode");
     ri_launch_pdl(attention_decode_merge_kernel, dim3(H, seqs), dim3(AD_MERGE_THREADS), 0, stream,
-                  (const float*)o_part, (const float*)ml_part, (bf16*)out, seq_len, H, max_chunks, window);
+                  (const float*)o_part, (const float*)ml_part, (bf16*)out, seq_len, H, max_chunks, window, err_flag);
     RI_CHECK_LAUNCH("attention_decode_merge");
     return 0;
 }

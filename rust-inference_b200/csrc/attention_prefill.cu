@@ -39,12 +39,14 @@ struct __align__(16) PrefillSmem {
 // keys [kb*64, kb*64+63] of one kv head into buffer `buf`: two pages, 16 bytes per copy
 __device__ __forceinline__ void load_kv_block(PrefillSmem& sm, int buf, int kb, const bf16* __restrict__ k_pool,
                                               const bf16* __restrict__ v_pool, const int* __restrict__ table, int kvh,
-                                              int KV, int num_pages, int len, int* err) {
+                                              int KV, int num_pages, int len, int key_lo, int* err) {
     constexpr int VEC = PF_DH / 8;
     for (int i = threadIdx.x; i < PF_BN * VEC; i += blockDim.x) {
         int r = i / VEC, c = (i % VEC) * 8;
         int key = kb * PF_BN + r;
-        bool ok = key < len;
+        // a page that lies wholly before the first key any query of the tile sees may have been given back by a
+        // window group already: it is not looked up, its rows are zeros (and masked)
+        bool ok = key < len && (key / PF_PAGE + 1) * PF_PAGE > key_lo;
         size_t off = 0;
         if (ok) {
             int page = table[key / PF_PAGE];
@@ -90,7 +92,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
         const bf16* src = q + ((size_t)(t_begin + r_base + (ok ? r : 0)) * H + h) * PF_DH + c;
         cp_async16(&sm.q[r][c], src, ok);
     }
-    load_kv_block(sm, 0, kb_lo, k_pool, v_pool, table, kvh, KV, num_pages, len, err);
+    load_kv_block(sm, 0, kb_lo, k_pool, v_pool, table, kvh, KV, num_pages, len, key_lo, err);
     cp_async_commit();
 
     float o[PF_DH / 8][4];
@@ -103,7 +105,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
 
     for (int kb = kb_lo; kb <= kb_hi; kb++) {
         const int buf = (kb - kb_lo) & 1;
-        if (kb < kb_hi) load_kv_block(sm, buf ^ 1, kb + 1, k_pool, v_pool, table, kvh, KV, num_pages, len, err);
+        if (kb < kb_hi) load_kv_block(sm, buf ^ 1, kb + 1, k_pool, v_pool, table, kvh, KV, num_pages, len, key_lo, err);
         cp_async_commit();
         cp_async_wait<1>();              // everything but the block just asked for has arrived
         __syncthreads();

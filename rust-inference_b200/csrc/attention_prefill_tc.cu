@@ -192,17 +192,19 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
-// The places in the pool of the two pages that hold keys 64 kb .. 64 kb + 63 (-1: the sequence has no such page)
+// The places in the pool of the two pages that hold keys 64 kb .. 64 kb + 63 (-1: the sequence has no such page,
+// or the page lies wholly before key_lo, the first key any query of the block sees: a window group may have
+// given such a page back already, so it is not looked up)
 struct TcPages {
     int id[2];
 };
-__device__ __forceinline__ TcPages tc_pages(const int* __restrict__ table, int kb, int len, int num_pages, int* err) {
+__device__ __forceinline__ TcPages tc_pages(const int* __restrict__ table, int kb, int len, int key_lo, int num_pages, int* err) {
     TcPages r;
 #pragma unroll
     for (int j = 0; j < 2; j++) {
         const int pg = kb * (TC_BN / TC_PAGE) + j;
         int id = -1;
-        if (pg * TC_PAGE < len) {
+        if (pg * TC_PAGE < len && (pg + 1) * TC_PAGE > key_lo) {
             id = table[pg];
             if (id < 0 || id >= num_pages) {
                 atomicExch(err, 4);
@@ -314,7 +316,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
         tail.dead = 0;
         // the first blocks of keys and values, one per stage
         for (int j = 0; j < TC_STAGES && j < n_blocks; j++) {
-            const TcPages pg = tc_pages(table, kb_lo + j, len, num_pages, err);
+            const TcPages pg = tc_pages(table, kb_lo + j, len, key_lo, num_pages, err);
             tc_load_tile(k_tiles + j * TC_KV_BYTES, &map_k, pg, kvh, KV, &tail.k_full[j]);
             tc_load_tile(v_tiles + j * TC_KV_BYTES, &map_v, pg, kvh, KV, &tail.v_full[j]);
         }
@@ -343,7 +345,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
             for (int j = TC_STAGES; j < n_blocks && !dead; j++) {
                 const int buf = j % TC_STAGES;
                 const unsigned parity = (unsigned)((j / TC_STAGES - 1) & 1);
-                const TcPages pg = tc_pages(table, kb_lo + j, len, num_pages, err);       // under the wait below
+                const TcPages pg = tc_pages(table, kb_lo + j, len, key_lo, num_pages, err);       // under the wait below
                 if (!tc_mbar_wait(&tail.k_empty[buf], parity)) { atomicExch(err, 5); tail.dead = 1; dead = true; }
                 tc_load_tile(k_tiles + buf * TC_KV_BYTES, &map_k, pg, kvh, KV, &tail.k_full[buf]);
                 if (!dead && !tc_mbar_wait(&tail.v_empty[buf], parity)) { atomicExch(err, 5); tail.dead = 1; dead = true; }
@@ -532,6 +534,20 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
                     unsigned char* v_tile = v_tiles + (j % TC_STAGES) * TC_KV_BYTES;
                     const int first_bad = len - kb * TC_BN;
                     for (int r = first_bad + (row >> 3); r < TC_BN; r += TC_BM / 8)
+#pragma unroll
+                        for (int sl = 0; sl < TC_SLABS; sl++)
+                            *(uint4*)(v_tile + sl * TC_KV_SLAB + r * 128 + ((row & 7) << 4)) = make_uint4(0, 0, 0, 0);
+                }
+            }
+            if (kb * TC_BN < key_lo) {
+                // value rows before the first key that any query of the block sees: their page may not have been
+                // copied at all (given back by a window group), so the stage may hold anything there, and P = 0
+                // times a NaN is a NaN: the first tile's threads zero them, as above
+                if (t == 0) {
+                    if (!dead && !tc_mbar_wait(&tail.v_full[j % TC_STAGES], (unsigned)((j / TC_STAGES) & 1))) { atomicExch(err, 5); tail.dead = 1; dead = true; }
+                    unsigned char* v_tile = v_tiles + (j % TC_STAGES) * TC_KV_BYTES;
+                    const int head_bad = min(TC_BN, key_lo - kb * TC_BN);
+                    for (int r = row >> 3; r < head_bad; r += TC_BM / 8)
 #pragma unroll
                         for (int sl = 0; sl < TC_SLABS; sl++)
                             *(uint4*)(v_tile + sl * TC_KV_SLAB + r * 128 + ((row & 7) << 4)) = make_uint4(0, 0, 0, 0);

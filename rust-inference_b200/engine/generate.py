@@ -90,12 +90,14 @@ def plan_batches(prompt_lens: Sequence[int], max_new_tokens: int, max_seqs: int,
 
 def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int = 64,
              sampling: Optional[SamplingParams] = None, stop_ids: Optional[Iterable[int]] = None,
-             ignore_eos: bool = False, batch_size: Optional[int] = None, sampler=None) -> GenerationResult:
+             ignore_eos: bool = False, batch_size: Optional[int] = None, sampler=None,
+             pipelined: Optional[bool] = None) -> GenerationResult:
     """Generate for every prompt; ``tokens[i]`` are the new tokens of request i.
 
     ``stop_ids`` default to the model's (config.json ``eos_token_id``); with
     ``ignore_eos`` they are not looked at.  A sequence also ends when it fills
-    the longest sequence the cache holds."""
+    the longest sequence the cache holds.  ``pipelined`` chooses between the two
+    loops below (default: the pipelined one on a GPU); both give the same tokens."""
     sampling = sampling or SamplingParams()
     spec = engine.model.spec
     stops = frozenset(spec.stop_ids if stop_ids is None else stop_ids)
@@ -108,7 +110,8 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int = 64,
     batches = plan_batches([len(p) for p in prompts], max_new_tokens, cache.slots.num_slots, cache.page_size,
                            cache.num_pages, engine.max_seq_len, batch_size)
     stats = result.stats
-    pipelined = hasattr(engine, "step_device_ids") and engine.device.type == "cuda"
+    can_pipeline = hasattr(engine, "step_device_ids") and engine.device.type == "cuda"
+    pipelined = can_pipeline if pipelined is None else (bool(pipelined) and can_pipeline)
     for batch in batches:
         stats.batches += 1
         live = [_Seq(req, row, engine.new_sequence(), prompts[req]) for row, req in enumerate(batch)]

@@ -145,7 +145,9 @@ ERROR_TEXT = {1: "token id outside the vocabulary", 2: "cache write to an unmapp
               3: "position beyond the rotary table", 4: "attention read from an unmapped page",
               5: "a bounded wait inside a kernel ran out (copy or tensor-core completion never arrived)",
               6: "the tcgen05 attention kernel's shared memory does not start on a multiple of 1024 bytes "
-                 "(set RUST_INFERENCE_B200_NO_TCGEN05=1 to use the mma.sync kernel)"}
+                 "(set RUST_INFERENCE_B200_NO_TCGEN05=1 to use the mma.sync kernel)",
+              7: "a sequence is longer than the scratch memory given to the decode attention covers "
+                 "(max_chunks x 128 keys): the keys beyond were left out"}
 
 
 # ---------------------------------------------------------------------------------------

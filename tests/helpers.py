@@ -173,3 +173,18 @@ def first_wrong(rows, want_by_request, rid, rel, ab):
         if np.abs(rows[(r, p)] - want).max() > rel * np.abs(want).max() + ab:
             return p
     return None
+
+
+def assert_rows_identical(rows_by_cutting, what=""):
+    """float32: the logits of a (request, position) are the same bits however the work was cut
+    (the reference holds `Last` bit-equal to the row of `All`, tests/model_parity.rs:86-98)."""
+    labels = list(rows_by_cutting)
+    base = rows_by_cutting[labels[0]]
+    for label in labels[1:]:
+        other = rows_by_cutting[label]
+        assert set(other) == set(base), f"{what}: {label} and {labels[0]} hold different places"
+        for key in sorted(base):
+            if not np.array_equal(base[key], other[key]):
+                diff = np.abs(base[key].astype(np.float64) - other[key]).max()
+                raise AssertionError(f"{what}: request {key[0]} position {key[1]}: {labels[0]} and {label} differ "
+                                     f"(max {diff:.3e}); float32 logits must not depend on the cutting")

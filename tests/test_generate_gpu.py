@@ -137,7 +137,60 @@ def test_stop_tokens_and_command_line(dirs):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stderr
     lines = r.stdout.strip().split("\n")
+    assert len(lines) == 2
     assert [int(t) for t in lines[0].split()] == want
+    assert [int(t) for t in lines[1].split()] == plain.generate_plain(pcfg, W, [1, 2, 3], 10, stop_ids=[stop])
     assert "prefill: 7 tokens" in r.stderr and "decode:" in r.stderr and "kernel launches" in r.stderr
     bad = subprocess.run(cmd[:3] + ["--prompt", "99999"], capture_output=True, text=True, timeout=600)
     assert bad.returncode == 1 and "vocabulary" in bad.stderr
+
+
+@pytest.mark.parametrize("temperature", [0.0, 0.8])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sequences_of_a_batch_end_at_different_steps(dirs, dtype, temperature):
+    """Batches whose members end in different steps: by a stop token, by the token limit, by the longest
+    sequence the cache holds.  In the loop that a GPU takes (the next step is launched from the device's ids
+    before the host has read them) a stopped sequence runs one step too many on a slot that is given back
+    right after; the others go on in a smaller batch.  Every request's tokens and reason: in float32 the plain
+    model's, and in both dtypes those of the loop that reads every step's ids first."""
+    import rust_inference_b200 as ri
+    from rust_inference_b200.engine.generate import generate
+    from rust_inference_b200.sampling import SamplingParams, request_seed
+    cfg, _ = ALL["B"]
+    rng = np.random.default_rng(17)
+    lens = [1, 17, 6, 40, 3, 9, 22]
+    prompts = [[int(t) for t in rng.integers(0, cfg["vocab_size"], size=n)] for n in lens]
+    pcfg, W = plain.load_model_dir(dirs["B"], round_to_bf16=(dtype == "bfloat16"))
+    max_new, seed, max_len = 30, 77, 64
+    sampling = dict(temperature=temperature) if temperature else {}
+
+    def plain_run(i, limit, stops):
+        return plain.generate_plain(pcfg, W, prompts[i], limit, stop_ids=stops, ignore_eos=not stops,
+                                    rng=plain.PlainRng(request_seed(seed, i)), **sampling)
+    # stop tokens taken from what the requests generate when nothing stops them, at different depths
+    free = [plain_run(i, 12, ()) for i in range(len(prompts))]
+    stops = {free[0][5], free[2][9], free[4][2], free[5][7]}
+    llm = ri.LLM(dirs["B"], dtype=dtype, max_seqs=3, max_pages=6, pages_per_seq=max_len // 32)
+    params = SamplingParams(temperature, 0, 1.0, 1.0, seed)
+    results = {}
+    for pipelined in (True, False):
+        res = generate(llm.engine, prompts, max_new, params, stop_ids=stops, pipelined=pipelined)
+        results[pipelined] = res
+        llm.engine.cache.check()
+        assert llm.engine.cache.slots.live_count == 0 and llm.engine.cache.free_pages() == 6
+        assert res.stats.batches == 3
+    assert results[True].tokens == results[False].tokens
+    assert results[True].finish_reasons == results[False].finish_reasons
+    reasons = results[True].finish_reasons
+    assert len(set(reasons)) > 1
+    if dtype == "float32":
+        # (what the plain model does with these prompts and seeds; bfloat16 may choose otherwise somewhere)
+        assert reasons[3] == "cache" and len(results[True].tokens[3]) == max_len - lens[3] + 1
+        assert {"stop", "length", "cache"} <= set(reasons)
+        for batch in ([0, 1, 2], [3, 4, 5]):
+            assert len({len(results[True].tokens[i]) for i in batch}) > 1, "the batch's members ended together"
+        for i in range(len(prompts)):
+            limit = min(max_new, max_len - lens[i] + 1)
+            want = plain_run(i, limit, stops)
+            assert results[True].tokens[i] == want, f"request {i}"
+            assert reasons[i] == ("stop" if len(want) < limit else "cache" if limit < max_new else "length")

@@ -614,7 +614,7 @@ def _take_error(ops):
 
 def test_kernels_report_indices_they_must_not_follow():
     """An id outside the vocabulary, a position beyond the rotary table, an unmapped or impossible page: the
-    kernel leaves the access out, sets the error word (1, 3, 2, 4) and goes on; nothing faults."""
+    kernel leaves the access out, sets the error word (1, 3, 2, 4, 7) and goes on; nothing faults."""
     from rust_inference_b200 import ops
     from rust_inference_b200.config import RopeSpec
     from rust_inference_b200.parts import BuildEnv, build_part
@@ -634,9 +634,9 @@ def test_kernels_report_indices_they_must_not_follow():
         rope.prepare(80)
         qkv = dev(rnd(rng, 2, (H + 2 * KV) * Dh, dtype="bfloat16"), bt)
         meta = (i32(pt), i32([0, 1]), i32([69, 32]), i32(slots))
-        # 3: a position beyond the rotary table (the table has 80 rows)
+        # 3: a position beyond the rotary table (80 rows, or more if a part with the same sizes made a longer one)
         ops.qk_norm_rope_append(qkv, H, KV, Dh, None, None, 0.0, rope.fused_table(), Dh, kp, vp, i32(pt), i32([0, 1]),
-                                i32([69, 95]), i32(slots))
+                                i32([69, rope.fused_table().shape[0] + 15]), i32(slots))
         assert _take_error(ops) == 3
         # 2: append to a page that is not mapped, and to one that cannot exist
         for bad in (-1, k_pool.shape[0] + 5):
@@ -656,4 +656,10 @@ def test_kernels_report_indices_they_must_not_follow():
             assert _take_error(ops) == 4 and out.shape == qn.shape
             out = ops.attention(q1, kp, vp, i32(broken), i32([0, 1]), i32([69, 32]), i32(slots), 0.1, 0)
             assert _take_error(ops) == 4 and out.shape == q1.shape
+        # 7: a sequence longer than the decode attention's scratch memory covers (`max_len` sizes it): the keys
+        # beyond are left out, nothing is read or written past the partial results
+        lens = [300, 33]
+        pt, slots, k, v, k_pool, v_pool = _fill_pools(rng, lens, KV, Dh, "bfloat16", scale=0.5)
+        out = ops.attention_decode(q1, dev(k_pool, bt), dev(v_pool, bt), i32(pt), i32(slots), i32(lens), 0.1, 0, 128)
+        assert _take_error(ops) == 7 and bool(torch.isfinite(out.float()).all())
     assert _take_error(ops) == 0

@@ -42,7 +42,7 @@ def large(request, tmp_path_factory):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_replay_three_ways_at_large_layer_shapes(tmp_path, large, dtype):
     LARGE_LAYERS, d, reqs, want = large
-    worst = {}
+    worst, by_cutting = {}, {}
     for label, steps in (("whole", H.trace_whole(reqs)), ("tail", H.trace_tail(reqs, tail=32)),
                          ("batches", H.trace_batches(reqs, 3, [9, 32, 0]))):
         out = str(tmp_path / f"out_{label}")
@@ -50,5 +50,8 @@ def test_replay_three_ways_at_large_layer_shapes(tmp_path, large, dtype):
         rows = H.collect(steps, out, LARGE_LAYERS["vocab_size"])
         assert len(rows) == sum(LENGTHS)
         worst[label] = H.assert_rows_close(rows, want, dtype, f"large layers {dtype} {label}")
+        by_cutting[label] = rows
+    if dtype == "float32":
+        H.assert_rows_identical(by_cutting, "large layers float32")
         shutil.rmtree(out, ignore_errors=True)
     print(f"large layers {dtype}: worst error / bound = {worst}")

@@ -28,7 +28,7 @@ def test_replay_three_ways(tmp_path, model_dirs, name, dtype):
     rng = np.random.default_rng(7)
     reqs = H.random_requests(rng, cfg["vocab_size"], LENGTHS[name])
     want = H.plain_logits(d, reqs, dtype)
-    worst = {}
+    worst, by_cutting = {}, {}
     for label, steps in (("whole", H.trace_whole(reqs)), ("tail", H.trace_tail(reqs, tail=32)),
                          ("batches", H.trace_batches(reqs, 3, [8, 3, 12, 0, 33]))):
         out = str(tmp_path / f"out_{label}")
@@ -36,4 +36,7 @@ def test_replay_three_ways(tmp_path, model_dirs, name, dtype):
         rows = H.collect(steps, out, cfg["vocab_size"])
         assert len(rows) == sum(len(t) for t in reqs.values())
         worst[label] = H.assert_rows_close(rows, want, dtype, f"{name} {dtype} {label}")
+        by_cutting[label] = rows
+    if dtype == "float32":
+        H.assert_rows_identical(by_cutting, f"{name} float32")
     print(f"{name} {dtype}: worst error / bound = {worst}")
