@@ -41,12 +41,16 @@ SOURCES: Dict[str, Tuple[str, ...]] = {
     "attention_prefill_tc": ("attention_prefill_tc.cu", "common.cuh", "mma_helpers.cuh"),
     "attention_decode_noalloc": ("attention_decode_noalloc.cu", "attention_decode_noalloc.h", "attention_decode.cu",
                                  "common.cuh", "mma_helpers.cuh"),
+    "random_fill": ("random_fill.cu", "common.cuh", "random_fill.cuh"),
+    # host code only: the same random values as random_fill.cu gives on the device
+    "host_random": ("host_random.cpp", "random_fill.cuh"),
     # host code only (the cache's bookkeeping): built with the host compiler
     "host_cache": ("host_cache.cpp",),
     # host code only: the check of a step's entries and its int32 tables
     "host_step": ("host_step.cpp",),
 }
-HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC"]
+# no fused multiply-adds: host_random.cpp must give the bits that the device gives
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-ffp-contract=off", "-pthread"]
 
 # sources that are compiled once per value of a macro (the model's head size);
 # the build check compiles these values, a model with another one compiles its own
@@ -164,7 +168,8 @@ def compile_library(name: str, defines: Optional[Dict[str, object]] = None, verb
     if src.endswith(".cpp"):
         # host code: the host compiler, or nvcc (which hands the file to it) where none is on the path
         cxx = _host_compiler()
-        cmd = ([cxx] + HOST_FLAGS if cxx else [_nvcc(), "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"]) + macros
+        cmd = ([cxx] + HOST_FLAGS if cxx else [_nvcc(), "-O2", "-std=c++17", "-shared", "-Xcompiler",
+                                               "-fPIC,-ffp-contract=off,-pthread"]) + macros
         _log(f"compiling {_variant_name(name, defines)} (host code) ...")
     else:
         cmd = [_nvcc()] + ARCH_FLAGS + BASE_FLAGS + macros

@@ -1,14 +1,19 @@
 """Random-weights mode: a model folder (config.json, model.safetensors) from a
-configuration and a seed.
+configuration and a seed, or the same tensors made on the device without a file.
 
 Matrices and the embedding are N(0, 0.02), norm gains (the per-head q/k norms
-included) 1 + U(-0.1, 0.1), integer tables zero.  Every tensor has a generator
-of its own, seeded from (seed, tensor name), so a tensor's values do not depend
-on which other tensors exist.  The tensor list comes from the parts the
+included) 1 + U(-0.1, 0.1), integer tables zero.  A value is a function of
+(seed, tensor name, element index) and of nothing else (``csrc/random_fill.cuh``):
+the host code and the device kernel give the same bits, a tensor's values do not
+depend on which other tensors exist, and any part of a tensor (a few rows of an
+embedding, say) can be made alone.  So a model of tens of gigabytes can be made on
+the device for the engine and, tensor by tensor, on the host for a comparison,
+without ever being written.  The tensor list comes from the parts the
 architecture is made of, so this works for any registered architecture.
 """
 from __future__ import annotations
 
+import ctypes
 import hashlib
 import json
 import os
@@ -19,23 +24,65 @@ import torch
 from ..config.registry import config_from_dict
 from .safetensors_io import save_safetensors
 
-
-def _generator(seed: int, name: str, device="cpu") -> torch.Generator:
-    h = hashlib.sha256(f"{seed}:{name}".encode()).digest()
-    g = torch.Generator(device=device)
-    g.manual_seed(int.from_bytes(h[:8], "little") & ((1 << 63) - 1))
-    return g
+_MASK = (1 << 64) - 1
+MATRIX_STD = 0.02          # linears and the embedding (scripts/synthetic_checkpoint.py:135-152 of the reference)
+GAIN_SPREAD = 0.2          # norm gains: 1 + U(-0.1, 0.1)
 
 
-def random_tensor(seed: int, name: str, shape, role: str, dtype: torch.dtype, device="cpu") -> torch.Tensor:
-    g = _generator(seed, name, device)
-    if role == "matrix":
-        return (torch.randn(shape, generator=g, dtype=torch.float32, device=device) * 0.02).to(dtype)
-    if role == "gain":
-        return (1.0 + (torch.rand(shape, generator=g, dtype=torch.float32, device=device) * 0.2 - 0.1)).to(dtype)
+def _mix64(z: int) -> int:
+    z &= _MASK
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _MASK
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _MASK
+    return z ^ (z >> 31)
+
+
+def tensor_key(seed: int, name: str) -> int:
+    """The 64-bit key of a tensor's stream of values."""
+    h = int.from_bytes(hashlib.sha256(name.encode()).digest()[:8], "little")
+    return _mix64((int(seed) & _MASK) ^ _mix64(h))
+
+
+_U64, _P, _I, _D = ctypes.c_ulonglong, ctypes.c_void_p, ctypes.c_int, ctypes.c_double
+
+
+def _fill(out: torch.Tensor, key: int, first: int, kind: int, a: float, b: float) -> None:
+    from ..csrc import build
+    code = {torch.float32: 0, torch.bfloat16: 1}[out.dtype]
+    if out.is_cuda:
+        lib = build.library("random_fill")
+        fn = lib.ri_random_fill
+        fn.argtypes, fn.restype = [_P, _U64, _U64, _U64, _I, _D, _D, _I, _P], _I
+        with torch.cuda.device(out.device):
+            rc = fn(out.data_ptr(), key, first, out.numel(), kind, a, b, code, torch.cuda.current_stream().cuda_stream)
+    else:
+        lib = build.library("host_random")
+        fn = lib.ri_random_fill_host
+        fn.argtypes, fn.restype = [_P, _U64, _U64, _U64, _I, _D, _D, _I, _I], _I
+        rc = fn(out.data_ptr(), key, first, out.numel(), kind, a, b, code, 0)
+    if rc:
+        raise RuntimeError(f"random fill: {lib.ri_last_error().decode(errors='replace')}")
+
+
+def random_tensor(seed: int, name: str, shape, role: str, dtype: torch.dtype, device="cpu",
+                  first_row: int = 0) -> torch.Tensor:
+    """The tensor ``name`` of the random model with this seed, made where ``device`` says.
+    ``shape`` with ``first_row`` > 0 gives rows first_row .. first_row + shape[0] - 1 of it."""
+    shape = tuple(int(d) for d in shape)
     if role == "table":
         return torch.zeros(shape, dtype=torch.int32, device=device)
-    raise ValueError(f"unknown parameter role {role!r}")
+    if role not in ("matrix", "gain"):
+        raise ValueError(f"unknown parameter role {role!r}")
+    if dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError(f"random weights are float32 or bfloat16, not {dtype}")
+    out = torch.empty(shape, dtype=dtype, device=device)
+    row = 1
+    for d in shape[1:]:
+        row *= d
+    if role == "matrix":
+        _fill(out, tensor_key(seed, name), first_row * row, 0, MATRIX_STD, 0.0)
+    else:
+        _fill(out, tensor_key(seed, name), first_row * row, 1, 1.0, GAIN_SPREAD)
+    return out
 
 
 def random_tensors(expected: Dict[str, object], seed: int, dtype: torch.dtype, device="cpu") -> Dict[str, torch.Tensor]:

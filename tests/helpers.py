@@ -137,11 +137,13 @@ def replay_subprocess(model_dir, dtype, steps, out_dir, max_tokens=None, env=Non
             proc.kill()
 
 
-def replay_inprocess(model_dir, dtype, steps, out_dir, max_tokens=None, device="cpu"):
+def replay_inprocess(model_dir, dtype, steps, out_dir, max_tokens=None, device="cpu", model=None):
+    """The replay program's function in this process; ``model``: a model built already (no folder is read)."""
     from rust_inference_b200 import trace
     lines = [json.dumps(s) for s in steps]
     buf = io.StringIO()
-    rc = trace.run(model_dir, dtype, out_dir, max_tokens or max_live_tokens(steps), lines=lines, out=buf, device=device)
+    rc = trace.run(model_dir, dtype, out_dir, max_tokens or max_live_tokens(steps), lines=lines, out=buf, device=device,
+                   model=model)
     assert rc == 0
     assert buf.getvalue().split("\n")[:-1] == [f"done {s['step']}" for s in steps]
 

@@ -13,6 +13,7 @@ import numpy as np
 import pytest
 
 import helpers as H
+import plain_qwen3 as plain
 
 pytestmark = pytest.mark.gpu
 
@@ -55,3 +56,68 @@ def test_replay_three_ways_at_large_layer_shapes(tmp_path, large, dtype):
         H.assert_rows_identical(by_cutting, "large layers float32")
         shutil.rmtree(out, ignore_errors=True)
     print(f"large layers {dtype}: worst error / bound = {worst}")
+
+
+# ---- the full width of Qwen3-8B with its real output head, without a file -------------------------------------
+#
+# 2 of the 36 layers, every other size as in Qwen3-8B (vocabulary 151,936 under a separate head of width 4,096).
+# The engine's model is made on the device by the function that bench.py uses (Model.from_random); the plain
+# model gets the same tensors from the host code of the same rule (value = f(seed, name, index)), the embedding
+# only row by row for the ids in use.
+
+FULL_8B = dict(_shapes(2, 4096, 32, 12288, 151936), num_hidden_layers=2)
+FULL_SEED = 5
+
+
+class _EmbeddingRows:
+    """table[ids] and table.shape of the embedding, its rows made one at a time."""
+
+    def __init__(self, name, vocab, width, round_bf16):
+        self.name, self.shape, self.round_bf16 = name, (vocab, width), round_bf16
+
+    def __getitem__(self, ids):
+        import torch
+        from rust_inference_b200.weights.random_init import random_tensor
+        dt = torch.bfloat16 if self.round_bf16 else torch.float32
+        rows = [random_tensor(FULL_SEED, self.name, (1, self.shape[1]), "matrix", dt, first_row=int(i)).float().numpy()[0]
+                for i in np.asarray(ids).reshape(-1)]
+        return np.stack(rows)
+
+
+def _plain_weights_without_a_file(round_bf16):
+    import torch
+    from rust_inference_b200.config import config_from_dict
+    from rust_inference_b200.engine.model import expected_tensors
+    from rust_inference_b200.weights.random_init import random_tensor
+    spec = config_from_dict(FULL_8B).to_spec()
+    W = {}
+    for name, info in expected_tensors(spec).items():
+        if name == spec.embedding_name:
+            W[name] = _EmbeddingRows(name, info.shape[0], info.shape[1], round_bf16)
+            continue
+        dt = torch.bfloat16 if (round_bf16 and info.role == "matrix") else torch.float32
+        W[name] = random_tensor(FULL_SEED, name, info.shape, info.role, dt).float().numpy()
+    return W
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_full_width_with_the_real_output_head(tmp_path, dtype):
+    from rust_inference_b200.engine import Model
+    reqs = H.random_requests(np.random.default_rng(4), FULL_8B["vocab_size"], LENGTHS)
+    W = _plain_weights_without_a_file(round_bf16=(dtype == "bfloat16"))
+    want = {rid: plain.forward_logits(FULL_8B, W, toks) for rid, toks in reqs.items()}
+    del W
+    model = Model.from_random(dict(FULL_8B), FULL_SEED, dtype=dtype, device="cuda:0")
+    worst, by_cutting = {}, {}
+    for label, steps in (("whole", H.trace_whole(reqs)), ("tail", H.trace_tail(reqs, tail=32)),
+                         ("batches", H.trace_batches(reqs, 3, [9, 32, 0]))):
+        out = str(tmp_path / f"out_{label}")
+        H.replay_inprocess(None, dtype, steps, out, device="cuda", model=model)
+        rows = H.collect(steps, out, FULL_8B["vocab_size"])
+        assert len(rows) == sum(LENGTHS)
+        worst[label] = H.assert_rows_close(rows, want, dtype, f"full width {dtype} {label}")
+        by_cutting[label] = rows
+        shutil.rmtree(out, ignore_errors=True)
+    if dtype == "float32":
+        H.assert_rows_identical(by_cutting, "full width float32")
+    print(f"Qwen3-8B width, 2 of 36 layers, vocabulary 151,936, {dtype}: worst error / bound = {worst}")

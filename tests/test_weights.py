@@ -111,3 +111,38 @@ def test_random_mode_is_seeded_and_in_distribution(tmp_path):
         assert float(g.min()) >= 0.9 and float(g.max()) <= 1.1 and float(g.std()) > 0.01
     with open(os.path.join(a, "config.json")) as f:
         assert json.load(f)["hidden_size"] == 96
+
+
+def test_random_weights_are_a_function_of_seed_name_and_index():
+    """The host code gives, bit for bit, what the rule written out in numpy gives; rows of a tensor can be made
+    alone; another name or seed gives other values; the moments are those of N(0, 0.02) and 1 + U(-0.1, 0.1)."""
+    import numpy as np
+    import plain_random as pr
+    from rust_inference_b200.weights.random_init import random_tensor, tensor_key
+    assert tensor_key(7, "model.norm.weight") == pr.tensor_key(7, "model.norm.weight")
+    w = random_tensor(7, "w", (400, 333), "matrix", torch.float32)
+    assert np.array_equal(w.numpy(), pr.normal(pr.tensor_key(7, "w"), np.arange(400 * 333)).reshape(400, 333))
+    assert torch.equal(random_tensor(7, "w", (5, 333), "matrix", torch.float32, first_row=123), w[123:128])
+    assert torch.equal(random_tensor(7, "w", (400, 333), "matrix", torch.bfloat16), w.to(torch.bfloat16))
+    g = random_tensor(7, "g", (50000,), "gain", torch.float32)
+    assert np.array_equal(g.numpy(), pr.uniform(pr.tensor_key(7, "g"), np.arange(50000)))
+    assert not torch.equal(random_tensor(7, "v", (400, 333), "matrix", torch.float32), w)
+    assert not torch.equal(random_tensor(8, "w", (400, 333), "matrix", torch.float32), w)
+    z = (w.double() / 0.02).flatten()
+    assert abs(float(z.mean())) < 0.01 and abs(float(z.std()) - 1) < 0.01 and abs(float((z ** 4).mean()) - 3) < 0.1
+    assert 0.9 <= float(g.min()) < 0.9001 and 1.0999 < float(g.max()) <= 1.1 and abs(float(g.mean()) - 1) < 1e-3
+    assert random_tensor(7, "t", (3, 4), "table", torch.float32).dtype == torch.int32
+
+
+@pytest.mark.gpu
+def test_random_weights_host_and_device_agree():
+    """The device kernel and the host code give the same bits, in float32 and in bfloat16, for whole tensors and
+    for rows in the middle of one: a model made on the device is the model that the host would have written."""
+    from rust_inference_b200.weights.random_init import random_tensor
+    for dtype in (torch.float32, torch.bfloat16):
+        for role, shape in (("matrix", (3000, 777)), ("gain", (4097,)), ("matrix", (1, 5))):
+            host = random_tensor(11, "x", shape, role, dtype)
+            dev = random_tensor(11, "x", shape, role, dtype, device="cuda")
+            assert torch.equal(host, dev.cpu()), (dtype, role, shape)
+        rows = random_tensor(11, "x", (40, 777), "matrix", dtype, device="cuda", first_row=2900)
+        assert torch.equal(rows.cpu(), random_tensor(11, "x", (3000, 777), "matrix", dtype)[2900:2940])
