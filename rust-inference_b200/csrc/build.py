@@ -31,7 +31,7 @@ BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"
 SOURCES: Dict[str, Tuple[str, ...]] = {
     "elementwise": ("elementwise.cu", "common.cuh", "linear_skinny_geometry.cuh"),
     "rope_kv": ("rope_kv.cu", "common.cuh"),
-    "attention_plain": ("attention_plain.cu", "common.cuh"),
+    "attention_rows": ("attention_rows.cu", "common.cuh"),
     "linear_f32": ("linear_f32.cu", "common.cuh"),
     "sampling": ("sampling.cu", "common.cuh"),
     "attention_decode": ("attention_decode.cu", "common.cuh", "mma_helpers.cuh"),

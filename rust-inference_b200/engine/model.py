@@ -13,6 +13,7 @@ import torch
 from .. import ops
 from ..config.registry import load_config
 from ..parts import Block, BuildEnv, ParamInfo, build_part, part_class
+from ..profiler import section
 from ..weights.loader import load_checkpoint
 from ..weights.random_init import random_tensor
 
@@ -145,7 +146,8 @@ class Model:
     # ---- one step ------------------------------------------------------------------------
     def forward(self, ids: torch.Tensor, ctx, cache, want_rows: Optional[torch.Tensor]) -> torch.Tensor:
         """float32 logits [wanted rows, vocab] for the packed tokens ``ids``."""
-        resid = ops.embed(ids, self.embedding)
+        with section("embedding"):
+            resid = ops.embed(ids, self.embedding)
         delta = None
         for e in self.spec.schedule:
             resid, delta = self.blocks[e.layer](resid, delta, ctx, cache.layer(e.cache, e.writes))
@@ -153,4 +155,5 @@ class Model:
             x = self.final_norm(resid, delta, want_rows, self.head)
         else:
             x = self.final_norm(resid, delta, rows=want_rows)
-        return ops.linear(x, self.head, out_dtype=torch.float32)
+        with section("lm head"):
+            return ops.linear(x, self.head, out_dtype=torch.float32)

@@ -27,7 +27,7 @@ _SIGNATURES = {
     ("elementwise", "ri_add_rows"): [_P, _P, _L, _I, _P],
     ("elementwise", "ri_silu_mul"): [_P, _P, _I, _I, _I, _I, _P],
     ("rope_kv", "ri_qk_norm_rope_append"): [_P] * 10 + [_F, _P, _I, _I] + [_I] * 9 + [_P, _P],
-    ("attention_plain", "ri_attention_plain"): [_P] * 8 + [_I] * 7 + [_F, _I, _I, _P, _P],
+    ("attention_rows", "ri_attention_rows"): [_P] * 8 + [_I] * 8 + [_F, _I, _I, _P, _P],
     ("linear_f32", "ri_linear_f32"): [_P, _P, _P, _I, _I, _I, _P],
     ("sampling", "ri_sample"): [_P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _P],
     ("sampling", "ri_sample_work_bytes"): [_I, _I],
@@ -330,9 +330,12 @@ def qk_norm_rope_append(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, he
 
 
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
-              tok_seq: torch.Tensor, tok_pos: torch.Tensor, seq_slot: torch.Tensor, scale: float,
+              seq_slot: torch.Tensor, seq_start: torch.Tensor, seq_len: torch.Tensor, max_new: int, scale: float,
               window: int = 0) -> torch.Tensor:
-    """Causal attention of q [tokens, H, Dh] over the paged cache; [tokens, H, Dh]."""
+    """Causal attention of the step's new tokens (q [tokens, H, Dh], sequences back to back as
+    ``seq_start`` says) over the paged cache, which already holds their keys and values: float32 or
+    bfloat16, any head size up to 512, any page size.  Every (token, head) is computed in one fixed
+    order that depends on its own position only, so the result does not depend on the step's cutting."""
     _need(q, "q")
     tokens, H, Dh = q.shape
     pages, KV, page_size, dh = k_pool.shape
@@ -341,16 +344,20 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
     _need(k_pool, "k_pool", q.dtype)
     _need(v_pool, "v_pool", q.dtype)
     _need(page_table, "page_table", torch.int32)
+    seqs = seq_slot.numel()
+    _need(seq_slot, "seq_slot", torch.int32, (seqs,))
+    _need(seq_start, "seq_start", torch.int32, (seqs + 1,))
+    _need(seq_len, "seq_len", torch.int32, (seqs,))
     out = torch.empty_like(q)
-    _call("attention_plain", "ri_attention_plain", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
-          page_table.data_ptr(), tok_seq.data_ptr(), tok_pos.data_ptr(), seq_slot.data_ptr(), tokens, H, KV, Dh,
-          page_table.shape[1], page_size, pages, float(scale), int(window), _code(q.dtype),
+    _call("attention_rows", "ri_attention_rows", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
+          page_table.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seq_len.data_ptr(), seqs, int(max_new),
+          H, KV, Dh, page_table.shape[1], page_size, pages, float(scale), int(window), _code(q.dtype),
           error_flag(q.device).data_ptr(), _stream())
     return out
 
 
 def fast_attention_supported(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
-    """Whether the tensor-core attention kernels take this case (else the plain kernel does)."""
+    """Whether the tensor-core attention kernels take this case (else the float32-order kernel of ``attention`` does)."""
     return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= MAX_FAST_HEAD_DIM and page_size == 32
 
 

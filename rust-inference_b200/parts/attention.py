@@ -15,6 +15,7 @@ import math
 import torch
 
 from .. import ops
+from ..profiler import section
 from .base import CacheRequest, Mixer, PositionEncoding
 from .registry import ParamInfo, build_part, register_mixer
 
@@ -62,38 +63,42 @@ class Attention(Mixer):
 
     def __call__(self, x, ctx, cache):
         s = self.spec
-        qkv = ops.linear(x, self.qkv)
+        with section("attn q/k/v proj"):
+            qkv = ops.linear(x, self.qkv)
         table = self.position.fused_table()
         eps = s.qk_norm.eps if s.qk_norm is not None else 0.0
         meta = (ctx.tok_seq, ctx.tok_pos, ctx.seq_slot)
-        if table is not None or type(self.position).apply is PositionEncoding.apply:
-            # norm, rotation (by table, or none) and append in one kernel
-            rot = getattr(s.position, "rot", 0) if table is not None else 0
-            q = ops.qk_norm_rope_append(qkv, s.num_heads, s.num_kv_heads, s.head_dim, self.q_gain, self.k_gain, eps,
-                                        table, rot, cache.k_pool, cache.v_pool, cache.page_table, *meta,
-                                        write_kv=cache.writes)
-        else:
-            # a position encoding with a rule of its own: norm q and k, let it work on them, append
-            T, H, KV, Dh = x.shape[0], s.num_heads, s.num_kv_heads, s.head_dim
-            qw, kw = H * Dh, KV * Dh
-            q = ops.qk_norm_rope_append(qkv[:, :qw].contiguous(), H, 0, Dh, self.q_gain, None, eps, None, 0,
-                                        None, None, None, *meta, write_kv=False)
-            k = ops.qk_norm_rope_append(qkv[:, qw:qw + kw].contiguous(), KV, 0, Dh, self.k_gain, None, eps, None, 0,
-                                        None, None, None, *meta, write_kv=False)
-            q, k = self.position.apply(q, k, ctx)
-            if cache.writes:
-                kv = torch.cat([k.reshape(T, kw), qkv[:, qw + kw:]], dim=1).contiguous()
-                ops.qk_norm_rope_append(kv, 0, KV, Dh, None, None, eps, None, 0, cache.k_pool, cache.v_pool,
-                                        cache.page_table, *meta, write_kv=True)
-            q = q.contiguous()
+        with section("attn norm/rope/append"):
+            if table is not None or type(self.position).apply is PositionEncoding.apply:
+                # norm, rotation (by table, or none) and append in one kernel
+                rot = getattr(s.position, "rot", 0) if table is not None else 0
+                q = ops.qk_norm_rope_append(qkv, s.num_heads, s.num_kv_heads, s.head_dim, self.q_gain, self.k_gain, eps,
+                                            table, rot, cache.k_pool, cache.v_pool, cache.page_table, *meta,
+                                            write_kv=cache.writes)
+            else:
+                # a position encoding with a rule of its own: norm q and k, let it work on them, append
+                T, H, KV, Dh = x.shape[0], s.num_heads, s.num_kv_heads, s.head_dim
+                qw, kw = H * Dh, KV * Dh
+                q = ops.qk_norm_rope_append(qkv[:, :qw].contiguous(), H, 0, Dh, self.q_gain, None, eps, None, 0,
+                                            None, None, None, *meta, write_kv=False)
+                k = ops.qk_norm_rope_append(qkv[:, qw:qw + kw].contiguous(), KV, 0, Dh, self.k_gain, None, eps, None, 0,
+                                            None, None, None, *meta, write_kv=False)
+                q, k = self.position.apply(q, k, ctx)
+                if cache.writes:
+                    kv = torch.cat([k.reshape(T, kw), qkv[:, qw + kw:]], dim=1).contiguous()
+                    ops.qk_norm_rope_append(kv, 0, KV, Dh, None, None, eps, None, 0, cache.k_pool, cache.v_pool,
+                                            cache.page_table, *meta, write_kv=True)
+                q = q.contiguous()
         fast = ops.fast_attention_supported(q.dtype, s.head_dim, cache.page_size)
-        if fast and ctx.decode_only:
-            out = ops.attention_decode(q, cache.k_pool, cache.v_pool, cache.page_table, ctx.seq_slot, ctx.seq_len,
-                                       self.scale, s.window, ctx.len_bucket)
-        elif fast:
-            out = ops.attention_prefill(q, cache.k_pool, cache.v_pool, cache.page_table, ctx.seq_slot,
-                                        ctx.seq_start, ctx.seq_len, ctx.max_new, self.scale, s.window)
-        else:
-            out = ops.attention(q, cache.k_pool, cache.v_pool, cache.page_table, ctx.tok_seq, ctx.tok_pos,
-                                ctx.seq_slot, self.scale, s.window)
-        return ops.linear(out.view(x.shape[0], s.num_heads * s.head_dim), self.o)
+        with section("attention"):
+            if fast and ctx.decode_only:
+                out = ops.attention_decode(q, cache.k_pool, cache.v_pool, cache.page_table, ctx.seq_slot, ctx.seq_len,
+                                           self.scale, s.window, ctx.len_bucket)
+            elif fast:
+                out = ops.attention_prefill(q, cache.k_pool, cache.v_pool, cache.page_table, ctx.seq_slot,
+                                            ctx.seq_start, ctx.seq_len, ctx.max_new, self.scale, s.window)
+            else:
+                out = ops.attention(q, cache.k_pool, cache.v_pool, cache.page_table, ctx.seq_slot, ctx.seq_start,
+                                    ctx.seq_len, ctx.max_new, self.scale, s.window)
+        with section("attn o proj"):
+            return ops.linear(out.view(x.shape[0], s.num_heads * s.head_dim), self.o)

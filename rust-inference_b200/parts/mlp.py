@@ -7,6 +7,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
+from ..profiler import section
 from .base import FeedForward
 from .registry import ParamInfo, register_ffn
 
@@ -38,4 +39,7 @@ class SwiGLU(FeedForward):
         return self.gate_up
 
     def __call__(self, x, ctx):
-        return ops.linear(ops.linear_swiglu(x, self.gate_up, self.block), self.down)
+        with section("mlp gate/up"):
+            z = ops.linear_swiglu(x, self.gate_up, self.block)
+        with section("mlp down"):
+            return ops.linear(z, self.down)

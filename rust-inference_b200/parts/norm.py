@@ -5,6 +5,7 @@ one, and writes the normed rows in the compute dtype."""
 from __future__ import annotations
 
 from .. import ops
+from ..profiler import section
 from .base import Norm
 from .registry import ParamInfo, register_norm
 
@@ -25,4 +26,5 @@ class RMSNorm(Norm):
         return self.gain.numel() * 4
 
     def __call__(self, resid, delta=None, rows=None, then=None):
-        return ops.rmsnorm(resid, self.gain, self.spec.eps, self.env.dtype, delta=delta, rows=rows, then=then)
+        with section("rmsnorm"):
+            return ops.rmsnorm(resid, self.gain, self.spec.eps, self.env.dtype, delta=delta, rows=rows, then=then)

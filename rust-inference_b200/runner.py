@@ -39,7 +39,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-pages", type=int, default=256, help="KV cache pages per layer (32 tokens each)")
     ap.add_argument("--pages-per-seq", type=int, default=128, help="maximum KV pages per sequence")
     ap.add_argument("--batch-size", type=int, default=8, help="sequences that run together")
-    ap.add_argument("--profile", action="store_true", help="print a per-kernel launch count and timing at the end")
+    ap.add_argument("--profile", action="store_true",
+                    help="print the time per section (device time of eager steps: no CUDA graphs) and the launch count at the end")
     ap.add_argument("--temperature", type=float, default=0.0, help="sampling temperature; 0 = greedy")
     ap.add_argument("--top-k", type=int, default=0, help="keep only the k most likely tokens (0 = off)")
     ap.add_argument("--top-p", type=float, default=1.0, help="nucleus sampling threshold (1.0 = off)")
@@ -73,7 +74,11 @@ def main(argv=None) -> int:
                 prompts += [_ids(line) for line in f if line.strip()]
         t0 = time.perf_counter()
         llm = ri.LLM(a.model_dir, dtype=a.dtype, max_pages=a.max_pages, pages_per_seq=a.pages_per_seq,
-                     max_seqs=a.batch_size)
+                     max_seqs=a.batch_size, use_graphs=not a.profile)
+        if a.profile:
+            from rust_inference_b200 import profiler
+            profiler.reset()
+            profiler.enable(True)          # as src/bin/runner.rs:207 switches the reference's timers on
         spec = llm.model.spec
         print(f"loaded {spec.architecture} ({len(spec.layers)} layers) in {time.perf_counter() - t0:.2f}s", file=sys.stderr)
         if a.random_prompt:
@@ -106,7 +111,8 @@ def main(argv=None) -> int:
         print(f"decode:  {st.decode_tokens} tokens in {st.decode_s:.3f}s ({st.decode_tokens / max(st.decode_s, 1e-9):.2f} tok/s)",
               file=sys.stderr)
     if a.profile:
-        print(f"\nkernel launches: {ops.launch_count() - n0} (graph replays: {llm.engine.graph_replays}, "
+        print("\n" + profiler.report(), file=sys.stderr, end="")
+        print(f"kernel launches: {ops.launch_count() - n0} (graph replays: {llm.engine.graph_replays}, "
               f"batches: {st.batches}, decode steps: {st.decode_steps})", file=sys.stderr)
     return 0
 

@@ -20,6 +20,7 @@ import numpy as np
 import torch
 
 from .. import ops
+from ..profiler import section
 
 _MASK = (1 << 64) - 1
 
@@ -162,6 +163,10 @@ class Sampler:
     def sample_device(self, logits: torch.Tensor, rows: Sequence[int]) -> torch.Tensor:
         """The same, left on the device (int32 [len(rows)]): the next step can be fed from it
         before the host has seen the ids."""
+        with section("sampling"):
+            return self._sample_device(logits, rows)
+
+    def _sample_device(self, logits: torch.Tensor, rows: Sequence[int]) -> torch.Tensor:
         p = self.params
         n = len(rows)
         if p.greedy and not self.uses_context:

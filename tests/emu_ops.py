@@ -88,24 +88,26 @@ def qk_norm_rope_append(qkv, num_heads, num_kv_heads, head_dim, q_gain, k_gain, 
     return q.to(qkv.dtype).contiguous()
 
 
-def attention(q, k_pool, v_pool, page_table, tok_seq, tok_pos, seq_slot, scale, window=0):
+def attention(q, k_pool, v_pool, page_table, seq_slot, seq_start, seq_len, max_new, scale, window=0):
     T, H, Dh = q.shape
     KV, P = k_pool.shape[1], k_pool.shape[2]
     G = H // KV
     out = torch.zeros_like(q, dtype=torch.float32)
-    for t in range(T):
-        pos = int(tok_pos[t])
-        slot = int(seq_slot[int(tok_seq[t])])
-        first = max(0, pos - window + 1) if window > 0 else 0
-        idx = torch.arange(first, pos + 1)
-        pages = page_table[slot, (idx // P).long()].long()
-        assert (pages >= 0).all(), "read from an unmapped page"
-        kk = k_pool[pages, :, (idx % P).long(), :].float()      # [n, KV, Dh]
-        vv = v_pool[pages, :, (idx % P).long(), :].float()
-        for h in range(H):
-            s = (kk[:, h // G, :] @ q[t, h].float()) * scale
-            p = torch.softmax(s, dim=0)
-            out[t, h] = p @ vv[:, h // G, :]
+    for b in range(seq_slot.numel()):
+        t0, t1, n = int(seq_start[b]), int(seq_start[b + 1]), int(seq_len[b])
+        slot = int(seq_slot[b])
+        for t in range(t0, t1):
+            pos = n - (t1 - t0) + (t - t0)
+            first = max(0, pos - window + 1) if window > 0 else 0
+            idx = torch.arange(first, pos + 1)
+            pages = page_table[slot, (idx // P).long()].long()
+            assert (pages >= 0).all(), "read from an unmapped page"
+            kk = k_pool[pages, :, (idx % P).long(), :].float()      # [n, KV, Dh]
+            vv = v_pool[pages, :, (idx % P).long(), :].float()
+            for h in range(H):
+                s = (kk[:, h // G, :] @ q[t, h].float()) * scale
+                p = torch.softmax(s, dim=0)
+                out[t, h] = p @ vv[:, h // G, :]
     return out.to(q.dtype)
 
 

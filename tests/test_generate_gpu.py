@@ -136,11 +136,21 @@ def test_stop_tokens_and_command_line(dirs):
            "--pages-per-seq", "4", "--profile"]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stderr
-    lines = r.stdout.strip().split("\n")
+    assert r.stdout.endswith("\n")
+    lines = r.stdout[:-1].split("\n")             # one line per prompt; a request that stops at once gives an empty one
     assert len(lines) == 2
     assert [int(t) for t in lines[0].split()] == want
     assert [int(t) for t in lines[1].split()] == plain.generate_plain(pcfg, W, [1, 2, 3], 10, stop_ids=[stop])
     assert "prefill: 7 tokens" in r.stderr and "decode:" in r.stderr and "kernel launches" in r.stderr
+    # --profile: a line per section, largest first, with its share and its calls
+    table = r.stderr[r.stderr.index("section "):].split("\n")
+    rows = {line[:22].strip(): line[22:].split() for line in table[1:] if "%" in line}
+    for name in ("embedding", "rmsnorm", "attn q/k/v proj", "attn norm/rope/append", "attention", "attn o proj",
+                 "mlp gate/up", "mlp down", "lm head", "sampling"):
+        assert name in rows, (name, r.stderr)
+    secs = [float(v[0]) for v in rows.values()]
+    assert secs == sorted(secs, reverse=True) and abs(sum(float(v[1].rstrip("%")) for v in rows.values()) - 100) < 1
+    assert int(rows["attention"][2]) == int(rows["mlp down"][2]) == 3 * int(rows["lm head"][2])      # three layers
     bad = subprocess.run(cmd[:3] + ["--prompt", "99999"], capture_output=True, text=True, timeout=600)
     assert bad.returncode == 1 and "vocabulary" in bad.stderr
 

@@ -128,3 +128,15 @@ def test_generate_matches_plain_on_cpu(tmp_path, emulated_ops, name):
     assert got == want
     llm.engine.cache.check()
     assert llm.engine.cache.slots.live_count == 0
+
+
+def test_section_timers_are_off_by_default_and_cost_nothing():
+    from rust_inference_b200 import profiler
+    assert not profiler.enabled()
+    with profiler.section("anything") as s:
+        assert s is profiler.section("other")           # one shared object that does nothing
+    assert profiler.snapshot() == [] and profiler.report().count("\n") == 1
+    profiler.enable(True)                               # without a GPU there is nothing to time with
+    import torch
+    assert profiler.enabled() == torch.cuda.is_available()
+    profiler.enable(False)

@@ -244,7 +244,9 @@ def test_norm_rope_append_then_attention(dtype, H, KV, Dh, window, full):
     kp, vp = dev(k_pool, tdt), dev(v_pool, tdt)
     args = (dev(table, torch.int32), dev(tok_seq, torch.int32), dev(tok_pos, torch.int32), dev(slots, torch.int32))
     q = ops.qk_norm_rope_append(dev(qkv, tdt), H, KV, Dh, dev(qg), dev(kg), eps, rope.fused_table(), rot, kp, vp, *args)
-    out = ops.attention(q, kp, vp, *args, 1.0 / math.sqrt(Dh), window)
+    starts = np.concatenate([[0], np.cumsum(new)]).astype(np.int32)
+    out = ops.attention(q, kp, vp, args[0], args[3], dev(starts, torch.int32), dev(np.array(lens), torch.int32), max(new),
+                        1.0 / math.sqrt(Dh), window)
     torch.cuda.synchronize()
     assert int(ops.error_flag("cuda").item()) == 0
 
@@ -276,6 +278,56 @@ def test_norm_rope_append_then_attention(dtype, H, KV, Dh, window, full):
         t0 += n
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,KV,Dh,P,window", [(4, 2, 20, 32, 0), (6, 2, 64, 16, 0), (3, 1, 36, 48, 0), (8, 2, 128, 32, 45),
+                                             (40, 1, 512, 32, 0), (2, 2, 8, 5, 7)])
+def test_attention_rows_any_page_size_and_cutting(dtype, H, KV, Dh, P, window):
+    """The attention of the float32 path alone: head sizes that are no multiple of 4 or of 16, page sizes other
+    than 32 (strips shorter than a warp), a group larger than a block holds at head size 512; against the plain
+    attention, and bit for bit the same whether a sequence's queries come in one step, in pieces or one by one
+    beside other sequences."""
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(Dh * 7 + P)
+    tdt = DT[dtype]
+    lens = [70, 33, 101]
+    table, slots, total = _paged(rng, lens, KV, Dh, P, dtype)
+    ks = [rnd(rng, n, KV, Dh, scale=0.5, dtype=dtype) for n in lens]
+    vs = [rnd(rng, n, KV, Dh, dtype=dtype) for n in lens]
+    qs = [rnd(rng, n, H, Dh, dtype=dtype) for n in lens]
+    k_pool = np.full((total, KV, P, Dh), np.nan, dtype=np.float32)        # rows nobody wrote must not matter
+    v_pool = np.full_like(k_pool, np.nan)
+    for b, n in enumerate(lens):
+        for j in range(n):
+            pg = table[slots[b], j // P]
+            k_pool[pg, :, j % P], v_pool[pg, :, j % P] = ks[b][j], vs[b][j]
+    kp, vp, tb = dev(k_pool, tdt), dev(v_pool, tdt), dev(table, torch.int32)
+    scale = 1.0 / math.sqrt(Dh)
+
+    def run(pieces):
+        """pieces: per sequence (first query, one past the last); the cache is taken to hold the keys up to there"""
+        live = [(b, lo, hi) for b, (lo, hi) in enumerate(pieces) if hi > lo]
+        q = np.concatenate([qs[b][lo:hi] for b, lo, hi in live])
+        starts = np.concatenate([[0], np.cumsum([hi - lo for _, lo, hi in live])])
+        out = ops.attention(dev(q, tdt), kp, vp, tb, dev(slots[[b for b, _, _ in live]], torch.int32),
+                            dev(starts, torch.int32), dev(np.array([hi for _, _, hi in live]), torch.int32),
+                            max(hi - lo for _, lo, hi in live), scale, window).float().cpu().numpy()
+        return {(b, lo + i): out[starts[k] + i] for k, (b, lo, hi) in enumerate(live) for i in range(hi - lo)}
+
+    whole = run([(0, n) for n in lens])
+    assert _take_error(ops) == 0
+    for b, n in enumerate(lens):
+        want = plain.causal_attention(qs[b].astype(np.float64), ks[b].astype(np.float64), vs[b].astype(np.float64), window=window)
+        got = np.stack([whole[(b, i)] for i in range(n)])
+        close(got, want, {"float32": 1e-5, "bfloat16": 2e-2}[dtype], f"sequence {b}")
+    cut = {}
+    cut.update(run([(0, 40), (0, 1), (0, 17)]))
+    cut.update(run([(40, 41), (1, 33), (17, 18)]))
+    cut.update(run([(41, 70), (0, 0), (18, 101)]))
+    assert set(cut) == set(whole)
+    for key in whole:
+        assert np.array_equal(cut[key], whole[key]), f"row {key} depends on the cutting"
+
+
 def test_attention_far_key_stands_out():
     """One key far back among hundreds gets nearly all the weight: a kernel that
     skipped or misplaced it would return another value row."""
@@ -297,8 +349,8 @@ def test_attention_far_key_stands_out():
             pg = table[slots[0], j // P]
             k_pool[pg, :, j % P], v_pool[pg, :, j % P] = k[j], v[j]
         out = ops.attention(dev(q, tdt), dev(k_pool, tdt), dev(v_pool, tdt), dev(table, torch.int32),
-                            dev(np.zeros(1), torch.int32), dev(np.array([n - 1]), torch.int32),
-                            dev(slots, torch.int32), 1.0 / math.sqrt(Dh), 0)
+                            dev(slots, torch.int32), dev(np.array([0, 1]), torch.int32), dev(np.array([n]), torch.int32),
+                            1, 1.0 / math.sqrt(Dh), 0)
         qall = np.concatenate([np.zeros((n - 1, H, Dh)), q.astype(np.float64)])
         want = plain.causal_attention(qall, k.astype(np.float64), v.astype(np.float64))[n - 1:]
         assert np.abs(want[0, 2] - v[far, 1]).max() < 1e-2     # the far key really dominates
@@ -644,7 +696,7 @@ def test_kernels_report_indices_they_must_not_follow():
             broken[slots[0], 69 // 32] = bad
             ops.qk_norm_rope_append(qkv, H, KV, Dh, None, None, 0.0, rope.fused_table(), Dh, kp, vp, i32(broken), *meta[1:])
             assert _take_error(ops) == 2
-        # 4: attention that meets such a page: decode (one token each), prefill (several), the plain kernel
+        # 4: attention that meets such a page: decode (one token each), prefill (several), the kernel of the float32 path
         q1 = dev(rnd(rng, 2, H, Dh, dtype="bfloat16"), bt)
         qn = dev(rnd(rng, 10, H, Dh, dtype="bfloat16"), bt)
         for bad in (-1, k_pool.shape[0] + 5):
@@ -654,7 +706,7 @@ def test_kernels_report_indices_they_must_not_follow():
             assert _take_error(ops) == 4 and out.shape == q1.shape
             out = ops.attention_prefill(qn, kp, vp, i32(broken), i32(slots), i32([0, 5, 10]), i32(lens), 5, 0.1, 0)
             assert _take_error(ops) == 4 and out.shape == qn.shape
-            out = ops.attention(q1, kp, vp, i32(broken), i32([0, 1]), i32([69, 32]), i32(slots), 0.1, 0)
+            out = ops.attention(q1, kp, vp, i32(broken), i32(slots), i32([0, 1, 2]), i32([70, 33]), 1, 0.1, 0)
             assert _take_error(ops) == 4 and out.shape == q1.shape
         # 7: a sequence longer than the decode attention's scratch memory covers (`max_len` sizes it): the keys
         # beyond are left out, nothing is read or written past the partial results
