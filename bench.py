@@ -15,7 +15,17 @@ steps end at exactly 4,096 tokens.  One JSON line is printed:
   prefill    a 2,048-token prompt in one step; frac = flops / time / bf16 peak
   roofline   decode step: bytes it has to read (every weight once, the cache of
              the live requests) / time, against the copy bandwidth
-  points     decode tokens a second at batch 1 and 64
+  points     decode tokens a second at batch 1 and 64 (device-timed), and the same through
+             the Python entry point (e2e_b1, e2e_b64)
+
+    python bench.py --workload 14b | 32b
+
+runs the workloads that the reference's figures are quoted on for the larger sizes, whole
+and through the Python entry point (LLM.generate, host token ids in and out): Qwen3-14B
+shapes with 16 unequal prompts of 256 to 2,048 tokens and 256 greedy steps, Qwen3-32B shapes
+with 8 prompts of 1,024 tokens and 512 steps at temperature 0.7.  One JSON line each: decode
+tokens a second (value), ms per step, the prompts' tokens a second with their fraction of the
+bf16 peak, and the decode step's fraction of the copy bandwidth for its own bytes.
 
 Peaks come from MEASURED_PEAKS.json beside this file when it exists, else from
 the fallback figures (6.65 TB/s, 1.59 PFLOP/s).  A decode step reads more than
@@ -116,10 +126,128 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def reference_arm() -> dict:
+    """The reference is a Rust crate whose engine is the `runner` binary (src/bin/runner.rs): look for a Rust
+    toolchain, build the crate with its CUDA backend from the copy under baseline/_ref, and say which step
+    failed.  Where it can be built it still cannot run this metric: its runner takes one text prompt (batch 1,
+    a tokenizer folder) and its checkpoint script has no Qwen3-8B preset (scripts/synthetic_checkpoint.py:18-35)."""
+    import shutil
+    why = None
+    cargo = shutil.which("cargo")
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if cargo is None or shutil.which("rustc") is None:
+        why = ("thanhauco/rust-inference is a Rust crate (Cargo.toml, no Python package); cargo and rustc "
+               "are not installed here and pip finds nothing to install")
+    elif not os.path.exists(os.path.join(ref, "Cargo.toml")):
+        why = "cargo was found, but there is no copy of the reference under baseline/_ref to build"
+    else:
+        try:
+            r = subprocess.run([cargo, "build", "--release", "--offline", "--features", "cuda", "--bin", "runner"],
+                               cwd=ref, capture_output=True, text=True, timeout=3000)
+            if r.returncode != 0:
+                tail = r.stderr.strip().splitlines()[-1] if r.stderr.strip() else "no message"
+                why = f"cargo build --offline --features cuda failed: {tail}"
+            else:
+                why = ("the reference's runner was built, but it generates for one text prompt at batch 1 with a "
+                       "tokenizer folder: it has no batch-8 decode at Qwen3-8B shapes to time")
+        except (OSError, subprocess.TimeoutExpired) as e:
+            why = f"cargo build did not finish: {e}"
+    return {"impl": "reference", "unavailable": why}
+
+
+def prefill_flops(cfg, lens) -> float:
+    """Matrix products of the layers for every token, the head for one row per sequence, causal attention."""
+    L, D, H, KV, Dh, I, V = (cfg[k] for k in ("num_hidden_layers", "hidden_size", "num_attention_heads",
+                                               "num_key_value_heads", "head_dim", "intermediate_size", "vocab_size"))
+    layer_params = D * (H + 2 * KV) * Dh + H * Dh * D + 3 * D * I
+    total = 0.0
+    for T in lens:
+        total += 2.0 * T * layer_params * L + 2.0 * D * V + 4.0 * Dh * H * T * (T + 1) / 2 * L
+    return total
+
+
+WORKLOADS = {
+    # BASELINE.json configs[3] and [4]: what the reference names beside its figures for these sizes
+    "14b": dict(model="14b", batch=16, prompt=(256, 2048), steps=256, temperature=0.0,
+                what="16 unequal prompts uniform in [256, 2048] tokens, then 256 greedy decode steps each"),
+    "32b": dict(model="32b", batch=8, prompt=(1024, 1024), steps=512, temperature=0.7,
+                what="8 prompts of 1,024 tokens, then 512 decode steps each at temperature 0.7, seed fixed"),
+}
+
+
+def run_workload(a) -> int:
+    import numpy as np
+    import torch
+
+    import rust_inference_b200 as ri
+    from rust_inference_b200 import ops
+    from rust_inference_b200.engine import Engine, Model
+
+    w = WORKLOADS[a.workload]
+    cfg = dict(QWEN3_8B, **SHAPES[w["model"]])
+    full_layers = cfg["num_hidden_layers"]
+    if a.layers:
+        cfg["num_hidden_layers"] = a.layers
+    name = f"Qwen3-{w['model'].upper()}"
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    hbm_gbs, bf16_tflops, peak_src = peaks()
+    rng = np.random.default_rng(20)
+    B, steps = w["batch"], (a.steps if a.steps_given else w["steps"])
+    lens = [int(n) for n in rng.integers(w["prompt"][0], w["prompt"][1] + 1, size=B)]
+    prompts = [[int(t) for t in rng.integers(0, cfg["vocab_size"], size=n)] for n in lens]
+    model = Model.from_random(cfg, seed=1, dtype="bfloat16", device=dev)
+    page = 32
+    longest = -(-(max(lens) + steps) // page) * page
+    engine = Engine(model, max_tokens=sum(-(-(n + steps) // page) * page for n in lens), max_seqs=B, max_seq_len=longest)
+    llm = ri.LLM(engine=engine)
+    clocks = ClockSampler()
+    clocks.start()
+    windows, runs = [], []
+    for _ in range(2):           # the first run loads the kernels and records the CUDA graphs; the second is reported
+        n0 = ops.launch_count()
+        t_a = time.time()
+        res = llm.generate(prompts, max_new_tokens=steps, temperature=w["temperature"], seed=20, ignore_eos=True,
+                           return_result=True)
+        windows = [(t_a, time.time())]
+        runs.append((res.stats, ops.launch_count() - n0))
+    clocks.stop()
+    st, launches = runs[-1]
+    ms_step = st.decode_s / st.decode_steps * 1e3
+    kv = engine.cache.bytes_per_token()
+    step_bytes = model.weight_bytes() + kv * sum(n + (st.decode_steps + 1) / 2.0 for n in lens)
+    achieved = step_bytes / (ms_step / 1e3) / 1e9
+    L, D, H, KV, Dh, I, V = (cfg[k] for k in ("num_hidden_layers", "hidden_size", "num_attention_heads",
+                                               "num_key_value_heads", "head_dim", "intermediate_size", "vocab_size"))
+    line = {
+        "metric": f"decode tok/s through LLM.generate, {name} shapes, bf16: {w['what']}",
+        "value": round(st.decode_tokens / st.decode_s, 1), "unit": "tok/s", "n_gpus": 1, "steps": st.decode_steps,
+        "warmup": "one whole run of the workload before the reported one", "ms_per_step": round(ms_step, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random-init weights N(0,0.02), uniform random token ids, seeded prompt lengths",
+        "config": {"model": name + " shapes", "layers": L, "layers_full": full_layers, "hidden": D, "heads": H,
+                   "kv_heads": KV, "head_dim": Dh, "intermediate": I, "vocab": V, "global_batch": B,
+                   "prompt_tokens_min": min(lens), "prompt_tokens_max": max(lens), "prompt_tokens_total": sum(lens),
+                   "decode_steps": st.decode_steps, "temperature": w["temperature"], "parallelism": "1 GPU",
+                   "timing": "host clock of LLM.generate (ids on the host every step)", "peaks": peak_src},
+        "prefill": {"value": round(st.prefill_tokens / st.prefill_s, 1), "tokens": st.prefill_tokens,
+                    "ms": round(st.prefill_s * 1e3, 3),
+                    "frac": round(prefill_flops(cfg, lens) / st.prefill_s / (bf16_tflops * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s",
+                     "frac": round(achieved / hbm_gbs, 4)},
+        "e2e": {"value": round(st.decode_tokens / st.decode_s, 1), "unit": "tok/s",
+                "h2d_bytes_per_step": (7 * B + 1) * 4, "d2h_bytes_per_step": B * 4},
+        "clocks": clocks.summary(windows), "gpu_launches": launches, "graph_replays": engine.graph_replays,
+        "impl": "ours", "workload": a.workload,
+    }
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=32,
                     help="untimed decode steps before the timed ones (right behind the prompt step the clock sits lower under the power cap)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -128,15 +256,20 @@ def main() -> int:
     ap.add_argument("--model", default="8b", choices=sorted(SHAPES), help="layer sizes: Qwen3-8B (the default), 14B or 32B")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS),
+                    help="run a whole workload of the larger sizes through LLM.generate instead of the default line")
     a = ap.parse_args()
+    a.steps_given = a.steps is not None
+    if a.steps is None:
+        a.steps = 64
     if a.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "thanhauco/rust-inference is a Rust crate (Cargo.toml, no Python package); cargo and rustc "
-                          "are not installed here and pip finds nothing to install"}))
+        print(json.dumps(reference_arm()))
         return 0
     if a.gpus != 1:
         print(f"bench.py measures one GPU: this library runs on a single device, --gpus {a.gpus} is not supported")
         return 2
+    if a.workload:
+        return run_workload(a)
     if a.warmup < 3:
         a.warmup = 3
 
@@ -220,8 +353,7 @@ def main() -> int:
     L, D, H, KV, Dh, I = (cfg[k] for k in ("num_hidden_layers", "hidden_size", "num_attention_heads",
                                             "num_key_value_heads", "head_dim", "intermediate_size"))
     T = PREFILL_TOKENS
-    layer_params = D * (H + 2 * KV) * Dh + H * Dh * D + 3 * D * I
-    flops = 2.0 * T * layer_params * L + 2.0 * 1 * D * V + 4.0 * Dh * H * T * (T + 1) / 2 * L
+    flops = prefill_flops(cfg, [T])
     prefill = {"value": round(T / (pre_ms / 1e3), 1), "tokens": T, "ms": round(pre_ms, 3),
                "frac": round(flops / (pre_ms / 1e3) / (bf16_tflops * 1e12), 4)}
 
@@ -247,6 +379,16 @@ def main() -> int:
                "h2d_bytes_per_step": (7 * B + 1) * 4, "d2h_bytes_per_step": B * 4,
                "prefill_tok_s": round(st.prefill_tokens / st.prefill_s, 1), "steps": len(timed),
                "warmup_steps": st.decode_steps - len(timed)}
+        if not a.skip_points:
+            # the same at batch 1 and 64
+            for b in (1, 64):
+                kb = min(K, 32)
+                pb = torch.randint(0, V, (b, CONTEXT - (kb + Wm)), generator=gen).tolist()
+                t_a = time.time()
+                rb = llm.generate(pb, max_new_tokens=kb + Wm, ignore_eos=True, return_result=True)
+                windows.append((t_a, time.time()))
+                tb = rb.stats.decode_step_s[-kb:]
+                points[f"e2e_b{b}"] = round(sum(n for _, n in tb) / sum(t for t, _ in tb), 1)
     clocks.stop()
 
     line = {

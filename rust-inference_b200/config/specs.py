@@ -77,12 +77,32 @@ class SwiGLUSpec:
 
 
 @dataclass(frozen=True)
+class EmbeddingSpec:
+    """h[t] = table[ids[t]], no scaling."""
+    vocab_size: int
+    hidden_size: int
+    kind: str = "embedding"
+
+
+@dataclass(frozen=True)
+class HeadSpec:
+    """logits = x W^T in float32, no bias, no soft-cap; W may be the embedding table (tied)."""
+    vocab_size: int
+    hidden_size: int
+    kind: str = "linear"
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One block: two sub-layers, each a norm followed by a part, each added to
     the residual stream (``arrangement`` "prenorm").
 
     ``names`` maps the block's four parts to the prefixes their tensors carry in
     the checkpoint, e.g. {"mixer": "model.layers.0.self_attn."}.
+
+    A layer with another arrangement is another record class: it needs
+    ``arrangement`` (the kind its block class is registered for) and
+    ``prefix(part)``; which parts it has is for its block class to say.
     """
     mixer: object
     ffn: object
@@ -123,6 +143,17 @@ class ModelSpec:
     stop_ids: Tuple[int, ...] = ()
     # a head tensor that is absent from the checkpoint means tied embeddings
     head_optional: bool = True
+    # records of the embedding and of the output head (None: the plain table and the plain linear head);
+    # the tensor "weight" of each carries ``embedding_name`` / ``head_name``, further tensors the same
+    # name with "weight" replaced by theirs
+    embedding: object = None
+    head: object = None
+
+    def embedding_record(self):
+        return self.embedding or EmbeddingSpec(self.vocab_size, self.hidden_size)
+
+    def head_record(self):
+        return self.head or HeadSpec(self.vocab_size, self.hidden_size)
 
     def cache_entries(self):
         """For every cache entry, the layer whose mixer decides its storage: the

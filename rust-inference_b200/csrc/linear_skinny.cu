@@ -22,7 +22,11 @@
 //
 // A token's result does not depend on M or on the other tokens.  Output is bfloat16
 // or float32 (the float32 accumulator, for the logits).  Waits are bounded: if one
-// runs out the kernel sets the error word (5) and finishes.
+// runs out the warp sets the error word (5), starts no further copies, waits (bounded
+// again) for the copies it has started, and the kernel finishes with a wrong result for
+// that block.  -DSK_TEST_DROP_COPY_K=<k> (tests only; nothing in an ordinary build) makes
+// block 0 leave out one copy of its first stage in launches with K == k, so that this path
+// can be run: the barrier of that stage then never completes.
 #include "common.cuh"
 #include "mma_helpers.cuh"
 #include "linear_skinny_geometry.cuh"
@@ -93,7 +97,12 @@ linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtenso
             const int k0 = (st_lo + i) * SK_STAGE_K;
             sk_expect_tx(&bar[slot], SK_STAGE_TOTAL);
 #pragma unroll
-            for (int j = 0; j < SK_BOXES; j++) sk_tma_2d(&ws[slot][j * SK_BOX_BYTES], &map_w, k0 + j * 64, n0, &bar[slot]);
+            for (int j = 0; j < SK_BOXES; j++) {
+#ifdef SK_TEST_DROP_COPY_K
+                if (K == SK_TEST_DROP_COPY_K && blockIdx.x == 0 && warp == 0 && i == 0 && j == 0) continue;
+#endif
+                sk_tma_2d(&ws[slot][j * SK_BOX_BYTES], &map_w, k0 + j * 64, n0, &bar[slot]);
+            }
         }
     };
     const int prefill = my_stages < SK_STAGES ? my_stages : SK_STAGES;
@@ -113,7 +122,8 @@ linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtenso
         for (int e = 0; e < 4; e++) acc[t][e] = 0.0f;
 
     bool dead = false;
-    for (int i = 0; i < my_stages; i++) {
+    int started = prefill;                              // stages whose copies have been started
+    for (int i = 0; i < started; i++) {
         const int slot = i % SK_STAGES;
         const int k0 = (st_lo + i) * SK_STAGE_K;
         // x for this stage (L1/L2), asked for before the wait
@@ -125,7 +135,9 @@ linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtenso
                 int k = k0 + g * 32 + qc * 8;
                 xv[g][t] = k < K ? ld_ca16(xr[t] + k0 + g * 32) : make_uint4(0, 0, 0, 0);
             }
-        if (!dead && !sk_wait(&bar[slot], (unsigned)((i / SK_STAGES) & 1))) {
+        // after a wait has run out the stages already started are still waited for (their copies must not
+        // outlive the block), each with its own limit, and no further stage is started
+        if (!sk_wait(&bar[slot], (unsigned)((i / SK_STAGES) & 1))) {
             if (lane == 0) atomicExch(err, 5);
             dead = true;
         }
@@ -142,7 +154,10 @@ linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtenso
             }
         }
         __syncwarp();                                   // every lane has read the slot
-        if (i + SK_STAGES < my_stages) issue(i + SK_STAGES);
+        if (!dead && i + SK_STAGES < my_stages) {
+            issue(i + SK_STAGES);
+            started = i + SK_STAGES + 1;
+        }
     }
     pdl_trigger_late();
     // acc[t][0,1]: (W row rho, tokens t*8 + 2qc, +1); acc[t][2,3]: (W row rho + 8, same tokens)

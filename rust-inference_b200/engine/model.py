@@ -1,6 +1,7 @@
 """The model: an embedding, scheduled blocks, a final norm and an output head,
 assembled from a :class:`~..config.specs.ModelSpec`.  Nothing here is specific
-to an architecture; the order of work is thanhauco/rust-inference's
+to an architecture: every one of those five is a registered part named by the
+spec, and the order of work is thanhauco/rust-inference's
 src/models/qwen3.rs:255-287 (embedding, layers, row selection, final norm,
 output projection), with the row selection generalised to any wanted rows.
 """
@@ -12,7 +13,7 @@ import torch
 
 from .. import ops
 from ..config.registry import load_config
-from ..parts import Block, BuildEnv, ParamInfo, build_part, part_class
+from ..parts import BuildEnv, ParamInfo, build_block, build_part, part_class
 from ..profiler import section
 from ..weights.loader import load_checkpoint
 from ..weights.random_init import random_tensor
@@ -28,37 +29,57 @@ def compute_dtype(name) -> torch.dtype:
         raise ValueError(f"dtype must be bfloat16 or float32, got {name!r}") from None
 
 
+def _end_name(full_weight_name: str, local: str) -> str:
+    """The tensor name of an embedding's or a head's tensor: "weight" carries the given name itself,
+    any other tensor the same name with "weight" replaced by its own."""
+    if local == "weight":
+        return full_weight_name
+    stem = full_weight_name[:-len("weight")] if full_weight_name.endswith("weight") else full_weight_name + "."
+    return stem + local
+
+
 def _part_tensors(spec):
     """Yield (full tensor name, ParamInfo, owner key, local name) for every tensor of the model."""
-    V, D = spec.vocab_size, spec.hidden_size
-    yield spec.embedding_name, ParamInfo((V, D), "matrix"), ("embedding",), "weight"
+    emb = spec.embedding_record()
+    for local, info in part_class("embedding", emb).param_infos(emb).items():
+        yield _end_name(spec.embedding_name, local), info, ("embedding",), local
     for local, info in part_class("norm", spec.final_norm).param_infos(spec.final_norm).items():
         yield spec.final_norm_prefix + local, info, ("final_norm",), local
     for i, layer in enumerate(spec.layers):
-        for part, family, record in (("mixer_norm", "norm", layer.mixer_norm), ("mixer", "mixer", layer.mixer),
-                                     ("ffn_norm", "norm", layer.ffn_norm), ("ffn", "ffn", layer.ffn)):
+        for part, family, record in part_class("block", layer).slots(layer):
             for local, info in part_class(family, record).param_infos(record).items():
                 yield layer.prefix(part) + local, info, ("layer", i, part), local
+    head = spec.head_record()
+    for local, info in part_class("head", head).param_infos(head).items():
+        if local == "weight" and spec.tie_embeddings:
+            continue                                   # the embedding's table
+        yield _end_name(spec.head_name, local), info, ("head",), local
 
 
 def expected_tensors(spec, for_writing: bool = False) -> Dict[str, ParamInfo]:
     """name -> ParamInfo of every tensor the checkpoint has to hold."""
-    out = {name: info for name, info, _, _ in _part_tensors(spec)}
-    if not spec.tie_embeddings:
-        out[spec.head_name] = ParamInfo((spec.vocab_size, spec.hidden_size), "matrix")
-    return out
+    return {name: info for name, info, _, _ in _part_tensors(spec)}
 
 
 class Model:
     def __init__(self, spec, dtype, device="cuda:0"):
         self.spec = spec
         self.env = BuildEnv(compute_dtype(dtype), torch.device(device))
-        self.blocks = [Block(ls, self.env) for ls in spec.layers]
+        self.blocks = [build_block(ls, self.env) for ls in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, self.env)
-        self.embedding: Optional[torch.Tensor] = None
-        self.head: Optional[torch.Tensor] = None
+        self.embed_part = build_part("embedding", spec.embedding_record(), self.env)
+        self.head_part = build_part("head", spec.head_record(), self.env)
         self.config = None
         self.cache_entry_layers = spec.cache_entries()
+
+    # the two big tables, as the tests and the bench look at them
+    @property
+    def embedding(self) -> Optional[torch.Tensor]:
+        return getattr(self.embed_part, "table", None)
+
+    @property
+    def head(self) -> Optional[torch.Tensor]:
+        return getattr(self.head_part, "weight", None)
 
     # ---- weights -------------------------------------------------------------------------
     def _to_role(self, t: torch.Tensor, role: str) -> torch.Tensor:
@@ -77,20 +98,28 @@ class Model:
                 groups[owner] = {}
                 order.append(owner)
             groups[owner][local] = (name, info)
+        if ("head",) not in groups:
+            groups[("head",)] = {}
+            order.append(("head",))
         for owner in order:
-            tensors = {local: self._to_role(get(name, info), info.role) for local, (name, info) in groups[owner].items()}
+            tensors = {}
+            for local, (name, info) in groups[owner].items():
+                t = get(name, info)
+                # a head tensor that is absent means tied embeddings (src/models/qwen3.rs:166-171)
+                if t is None and owner == ("head",) and local == "weight" and spec.head_optional:
+                    continue
+                tensors[local] = self._to_role(t, info.role)
             if owner == ("embedding",):
-                self.embedding = tensors["weight"]
+                self.embed_part.load(tensors)
             elif owner == ("final_norm",):
                 self.final_norm.load(tensors)
+            elif owner == ("head",):
+                if "weight" not in tensors:
+                    tensors["weight"] = self.embed_part.table          # tied: the same storage
+                self.head_part.load(tensors)
             else:
                 _, i, part = owner
                 getattr(self.blocks[i], part).load(tensors)
-        head = None
-        if not spec.tie_embeddings:
-            head = get(spec.head_name, ParamInfo((spec.vocab_size, spec.hidden_size), "matrix"))
-        # a head that is absent means tied embeddings (src/models/qwen3.rs:166-171)
-        self.head = self.embedding if head is None else self._to_role(head, "matrix")
 
     @classmethod
     def from_dir(cls, model_dir: str, dtype="bfloat16", device="cuda:0") -> "Model":
@@ -126,7 +155,7 @@ class Model:
     @property
     def graph_safe(self) -> bool:
         """Whether one-token steps of this model may be replayed from a CUDA graph."""
-        parts = [p for b in self.blocks for _, p, _, _ in b.parts()] + [self.final_norm]
+        parts = [p for b in self.blocks for _, p, _, _ in b.parts()] + [self.final_norm, self.embed_part, self.head_part]
         parts += [b.mixer.position for b in self.blocks if hasattr(b.mixer, "position")]
         return all(getattr(p, "graph_safe", False) for p in parts)
 
@@ -138,22 +167,22 @@ class Model:
         """Bytes of the matrices a step reads once each (the head included; the
         embedding only counts when asked, a step reads a few rows of it)."""
         n = sum(p.weight_bytes() for b in self.blocks for _, p, _, _ in b.parts())
-        n += self.final_norm.weight_bytes() + self.head.numel() * self.head.element_size()
+        n += self.final_norm.weight_bytes() + self.head_part.weight_bytes()
         if with_embedding and self.head is not self.embedding:
-            n += self.embedding.numel() * self.embedding.element_size()
+            n += self.embed_part.weight_bytes()
         return n
 
     # ---- one step ------------------------------------------------------------------------
     def forward(self, ids: torch.Tensor, ctx, cache, want_rows: Optional[torch.Tensor]) -> torch.Tensor:
         """float32 logits [wanted rows, vocab] for the packed tokens ``ids``."""
         with section("embedding"):
-            resid = ops.embed(ids, self.embedding)
+            resid = self.embed_part(ids)
         delta = None
         for e in self.spec.schedule:
             resid, delta = self.blocks[e.layer](resid, delta, ctx, cache.layer(e.cache, e.writes))
         if self.final_norm.takes_hint:
-            x = self.final_norm(resid, delta, want_rows, self.head)
+            x = self.final_norm(resid, delta, want_rows, self.head_part.reads_first())
         else:
             x = self.final_norm(resid, delta, rows=want_rows)
         with section("lm head"):
-            return ops.linear(x, self.head, out_dtype=torch.float32)
+            return self.head_part(x)

@@ -27,6 +27,9 @@ class Attention(Mixer):
         super().__init__(spec, env)
         if spec.num_heads % spec.num_kv_heads:
             raise ValueError(f"{spec.num_heads} heads are not a multiple of {spec.num_kv_heads} kv heads")
+        if spec.qk_norm is not None and getattr(spec.qk_norm, "kind", None) != "rmsnorm":
+            raise ValueError(f"the attention part norms its heads with RMSNorm inside its kernel; a per-head norm of kind "
+                             f"{getattr(spec.qk_norm, 'kind', None)!r} is not built")
         self.position = build_part("position", spec.position, env)
         self.scale = spec.scale or 1.0 / math.sqrt(spec.head_dim)
         self.q_gain = self.k_gain = None

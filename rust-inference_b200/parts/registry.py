@@ -5,15 +5,18 @@ A part class is registered for the ``kind`` of its spec record::
     @register_mixer("attention")
     class Attention(Mixer): ...
 
-and is built by ``build_mixer(spec, ctx)`` wherever a layer's record names that
-kind.  Tests register toy parts the same way; nothing else has to change.
+and is built by ``build_part("mixer", spec, env)`` wherever a layer's record names that
+kind.  The arrangement of a layer's parts (``block``, named by ``LayerSpec.arrangement``), the
+embedding and the output head are registered in the same way.  Tests register toy parts like
+this; nothing else has to change.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
 from typing import Callable, Dict, Tuple
 
-_REGISTRIES: Dict[str, Dict[str, type]] = {"mixer": {}, "ffn": {}, "norm": {}, "position": {}}
+_REGISTRIES: Dict[str, Dict[str, type]] = {"mixer": {}, "ffn": {}, "norm": {}, "position": {}, "block": {},
+                                           "embedding": {}, "head": {}}
 
 
 @dataclass(frozen=True)
@@ -52,8 +55,23 @@ def register_position(kind: str):
     return _register("position", kind)
 
 
+def register_block(kind: str):
+    """The arrangement of a layer's parts (``LayerSpec.arrangement`` names it)."""
+    return _register("block", kind)
+
+
+def register_embedding(kind: str):
+    """What turns token ids into the residual stream."""
+    return _register("embedding", kind)
+
+
+def register_head(kind: str):
+    """What turns the final norm's rows into float32 logits."""
+    return _register("head", kind)
+
+
 def part_class(family: str, spec) -> type:
-    kind = getattr(spec, "kind", None)
+    kind = getattr(spec, "arrangement", None) if family == "block" else getattr(spec, "kind", None)
     try:
         return _REGISTRIES[family][kind]
     except KeyError:

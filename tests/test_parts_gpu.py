@@ -469,3 +469,161 @@ def test_toy_architecture_with_two_cache_groups_a_shared_cache_and_routing(tmp_p
         rows = H.collect(steps, out, cfg.vocab_size)
         assert len(rows) == sum(len(t) for t in reqs.values())
         H.assert_rows_close({k: r for k, r in rows.items() if k not in close_call}, want, dtype, f"mixed {dtype} {label}")
+
+
+# ---- a toy architecture with an arrangement, an embedding and an output head of its own, all defined here ------
+#
+# One norm per layer whose output feeds the mixer and the feed-forward side by side (their outputs are added
+# to the stream together); an embedding scaled by sqrt(width); a head with a bias and a soft-cap.
+
+from rust_inference_b200.parts import (BlockBase, Part, norm_before, register_block, register_embedding,  # noqa: E402
+                                       register_head)
+
+
+@dataclass(frozen=True)
+class ParallelLayerSpec:
+    norm: object
+    mixer: object
+    ffn: object
+    names: tuple = ()
+    arrangement: str = "toy_parallel"
+
+    def prefix(self, part):
+        return dict(self.names)[part]
+
+
+@register_block("toy_parallel")
+class ParallelBlock(BlockBase):
+    @classmethod
+    def slots(cls, spec):
+        return (("norm", "norm", spec.norm), ("mixer", "mixer", spec.mixer), ("ffn", "ffn", spec.ffn))
+
+    def __call__(self, resid, delta, ctx, cache):
+        x = norm_before(self.norm, resid, delta, self.mixer)
+        a, f = self.mixer(x, ctx, cache), self.ffn(x, ctx)
+        return resid, (a.float() + f.float()).to(a.dtype)
+
+
+@dataclass(frozen=True)
+class ScaledEmbeddingSpec:
+    vocab_size: int
+    hidden_size: int
+    scale: float
+    kind: str = "toy_scaled"
+
+
+@register_embedding("toy_scaled")
+class ScaledEmbedding(Part):
+    @classmethod
+    def param_infos(cls, spec):
+        return {"weight": ParamInfo((spec.vocab_size, spec.hidden_size))}
+
+    def load(self, tensors):
+        self.table = tensors["weight"]
+
+    def __call__(self, ids):
+        from rust_inference_b200 import ops
+        return ops.embed(ids, self.table) * self.spec.scale
+
+
+@dataclass(frozen=True)
+class CappedHeadSpec:
+    vocab_size: int
+    hidden_size: int
+    cap: float
+    kind: str = "toy_capped"
+
+
+@register_head("toy_capped")
+class CappedHead(Part):
+    @classmethod
+    def param_infos(cls, spec):
+        return {"weight": ParamInfo((spec.vocab_size, spec.hidden_size)), "bias": ParamInfo((spec.vocab_size,), "gain")}
+
+    def load(self, tensors):
+        self.weight, self.bias = tensors["weight"], tensors["bias"]
+
+    def __call__(self, x):
+        from rust_inference_b200 import ops
+        z = ops.linear(x, self.weight, out_dtype=torch.float32) + self.bias
+        return self.spec.cap * torch.tanh(z / self.spec.cap)
+
+
+@register_architecture("ToyParallelLM")
+@dataclass(frozen=True)
+class ParallelConfig:
+    vocab_size: int = 83
+    hidden_size: int = 40
+    cap: float = 2.5
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(**{k: d[k] for k in ("vocab_size", "hidden_size", "cap") if k in d})
+
+    def validate(self):
+        pass
+
+    def to_dict(self):
+        return {"architectures": ["ToyParallelLM"], "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
+                "cap": self.cap}
+
+    def to_spec(self):
+        D = self.hidden_size
+        norm = RMSNormSpec(size=D, eps=1e-5)
+        attn = AttentionSpec(hidden_size=D, num_heads=2, num_kv_heads=2, head_dim=24,
+                             position=RopeSpec(head_dim=24, theta=1e4), qk_norm=None)
+        layers = tuple(ParallelLayerSpec(norm=norm, mixer=attn, ffn=SwiGLUSpec(hidden_size=D, intermediate_size=56), names=(
+            ("norm", f"blocks.{i}.norm."), ("mixer", f"blocks.{i}.attn."), ("ffn", f"blocks.{i}.ffn."))) for i in range(2))
+        return ModelSpec(architecture="ToyParallelLM", vocab_size=self.vocab_size, hidden_size=D, layers=layers,
+                         schedule=(ScheduleEntry(0, 0), ScheduleEntry(1, 1)), final_norm=norm, tie_embeddings=False,
+                         max_positions=256, embedding_name="tok.weight", head_name="out.weight", final_norm_prefix="norm.",
+                         head_optional=False,
+                         embedding=ScaledEmbeddingSpec(self.vocab_size, D, math.sqrt(D)),
+                         head=CappedHeadSpec(self.vocab_size, D, self.cap))
+
+
+def parallel_plain(cfg, W, ids):
+    n, D = len(ids), cfg.hidden_size
+    h = W["tok.weight"][np.asarray(ids)] * math.sqrt(D)
+    for i in range(2):
+        p = f"blocks.{i}."
+        x = plain.rms_norm(h, W[p + "norm.weight"], 1e-5)
+        q = plain.linear(x, W[p + "attn.q_proj.weight"]).reshape(n, 2, 24)
+        k = plain.linear(x, W[p + "attn.k_proj.weight"]).reshape(n, 2, 24)
+        v = plain.linear(x, W[p + "attn.v_proj.weight"]).reshape(n, 2, 24)
+        cos, sin = plain.rope_cos_sin(np.arange(n), 24, 1e4)
+        a = plain.causal_attention(plain.apply_rope(q, cos, sin), plain.apply_rope(k, cos, sin), v)
+        h = h + plain.linear(a.reshape(n, 48), W[p + "attn.o_proj.weight"]) + plain.swiglu_mlp(x, W, p + "ffn.")
+    z = plain.rms_norm(h, W["norm.weight"], 1e-5) @ W["out.weight"].T + W["out.bias"]
+    return cfg.cap * np.tanh(z / cfg.cap)
+
+
+def test_toy_architecture_with_its_own_arrangement_embedding_and_head(tmp_path):
+    from rust_inference_b200.engine import expected_tensors
+    cfg = ParallelConfig()
+    names = set(expected_tensors(cfg.to_spec()))
+    assert {"tok.weight", "out.weight", "out.bias", "blocks.1.norm.weight", "blocks.0.attn.q_proj.weight",
+            "blocks.1.ffn.down_proj.weight"} <= names and not any("norm1" in n or "mixer_norm" in n for n in names)
+    d = H.make_model_dir(tmp_path, cfg.to_dict(), seed=12, stored="float32", name="parallel")
+    W = {k: v.astype(np.float64) for k, v in plain.read_safetensors(d + "/model.safetensors").items()}
+    reqs = H.random_requests(np.random.default_rng(1), cfg.vocab_size, [9, 50, 33, 70])
+    want = {rid: parallel_plain(cfg, W, toks) for rid, toks in reqs.items()}
+    by_cutting = {}
+    for label, steps in (("whole", H.trace_whole(reqs)), ("tail", H.trace_tail(reqs, tail=32)),
+                         ("batches", H.trace_batches(reqs, 3, [7, 0, 20]))):
+        out = str(tmp_path / f"parallel_{label}")
+        H.replay_inprocess(d, "float32", steps, out, device="cuda")
+        by_cutting[label] = H.collect(steps, out, cfg.vocab_size)
+        H.assert_rows_close(by_cutting[label], want, "float32", f"toy parallel {label}")
+    H.assert_rows_identical(by_cutting, "toy parallel")
+
+
+def test_attention_refuses_a_per_head_norm_it_does_not_have():
+    @dataclass(frozen=True)
+    class OtherNormSpec:
+        size: int
+        eps: float
+        kind: str = "layernorm"
+    spec = AttentionSpec(hidden_size=32, num_heads=2, num_kv_heads=1, head_dim=16, qk_norm=OtherNormSpec(16, 1e-5))
+    with pytest.raises(ValueError, match="per-head norm"):
+        build_part("mixer", spec, env("float32"))
