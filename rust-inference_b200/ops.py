@@ -29,7 +29,7 @@ _SIGNATURES = {
     ("rope_kv", "ri_qk_norm_rope_append"): [_P] * 10 + [_F, _P, _I, _I] + [_I] * 9 + [_P, _P],
     ("attention_rows", "ri_attention_rows"): [_P] * 8 + [_I] * 8 + [_F, _I, _I, _P, _P],
     ("linear_f32", "ri_linear_f32"): [_P, _P, _P, _I, _I, _I, _P],
-    ("sampling", "ri_sample"): [_P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _P],
+    ("sampling", "ri_sample"): [_P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _P, _I, _P],
     ("sampling", "ri_sample_work_bytes"): [_I, _I],
     ("sampling", "ri_argmax"): [_P, _L, _I, _I, _P, _P, _P, _P],
     ("sampling", "ri_mark_seen"): [_P, _L, _P, _P, _I, _I, _P],
@@ -59,6 +59,8 @@ _STREAM_TC = os.environ.get("RUST_INFERENCE_B200_STREAM_TC") == "1"
 # the selection of a token other than the greedy one: from this many logits a row on, several blocks per row
 SAMPLE_WIDE_VOCAB = 16384
 _SAMPLE_WIDE = os.environ.get("RUST_INFERENCE_B200_SAMPLE_WIDE", "1") != "0"
+# ... and those passes as one kernel whose blocks meet at barriers per row (0: a kernel per pass, for comparisons)
+SAMPLE_ONE_KERNEL = os.environ.get("RUST_INFERENCE_B200_SAMPLE_ONE_KERNEL", "1") != "0"
 _fn_cache = {}
 
 
@@ -478,8 +480,9 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
     k_on, p_on = bool(uses_top_k and top_k is not None), bool(uses_top_p and top_p is not None)
     _call("sampling", "ri_sample", logits.data_ptr(), logits.stride(0), rows, vocab, _ptr(seen), _ptr(seen_rows),
           seen_stride, temperature.data_ptr(), _ptr(top_k), _ptr(top_p), _ptr(penalty), uniform.data_ptr(),
-          out.data_ptr(), _ptr(work), work_bytes, int(k_on), int(p_on), _stream())
-    if work is not None:
+          out.data_ptr(), _ptr(work), work_bytes, int(k_on), int(p_on), error_flag(logits.device).data_ptr(),
+          int(SAMPLE_ONE_KERNEL), _stream())
+    if work is not None and not SAMPLE_ONE_KERNEL:
         add_launches(2 + 12 * (1 + k_on + p_on) + p_on)          # one was counted by the call
     return out
 

@@ -415,8 +415,9 @@ def test_sample_matches_plain(vocab):
 
 @pytest.mark.parametrize("vocab", [16384, 40001, 151936])
 def test_sample_with_several_blocks_per_row_picks_the_same_token(vocab, monkeypatch):
-    """Large vocabularies are sampled by several blocks per row; the token is the one the one-block kernel
-    picks, for every mix of options within a batch (rows with and without top-k, top-p, a penalty, greedy rows)."""
+    """Large vocabularies are sampled by several blocks per row, as one kernel whose blocks meet at a barrier per
+    row after every pass, or (batches too large for that) as a kernel per pass; the token is the one the one-block
+    kernel picks, for every mix of options within a batch (rows with and without top-k, top-p, a penalty, greedy rows)."""
     from rust_inference_b200 import ops
     rng = np.random.default_rng(vocab)
     rows = 37
@@ -436,18 +437,30 @@ def test_sample_with_several_blocks_per_row_picks_the_same_token(vocab, monkeypa
         if trial == 0:
             u[:4] = [0.0, 0.99999994, 0.5, 1e-7]
         monkeypatch.setattr(ops, "_SAMPLE_WIDE", True)
+        monkeypatch.setattr(ops, "SAMPLE_ONE_KERNEL", True)
+        fused = ops.sample(dev(logits), dev(temperature), dev(u), **args).cpu().numpy()
+        monkeypatch.setattr(ops, "SAMPLE_ONE_KERNEL", False)
         wide = ops.sample(dev(logits), dev(temperature), dev(u), **args).cpu().numpy()
         monkeypatch.setattr(ops, "_SAMPLE_WIDE", False)
         one = ops.sample(dev(logits), dev(temperature), dev(u), **args).cpu().numpy()
         assert wide.tolist() == one.tolist(), trial
+        assert fused.tolist() == one.tolist(), trial
     # without the searches that a caller rules out: plain temperature rows
     monkeypatch.setattr(ops, "_SAMPLE_WIDE", True)
     u = rng.random(rows).astype(np.float32)
     t = dev(np.full(rows, 0.7, dtype=np.float32))
     wide = ops.sample(dev(logits), t, dev(u), uses_top_k=False, uses_top_p=False).cpu().numpy()
+    monkeypatch.setattr(ops, "SAMPLE_ONE_KERNEL", True)
+    fused = ops.sample(dev(logits), t, dev(u), uses_top_k=False, uses_top_p=False).cpu().numpy()
+    # a batch of 300 rows: more blocks than the device holds at once with many slices, so fewer slices per row
+    big = np.tile(logits, (9, 1))[:300]
+    ub = rng.random(300).astype(np.float32)
+    tb = dev(np.full(300, 0.7, dtype=np.float32))
+    fused_big = ops.sample(dev(big), tb, dev(ub), uses_top_k=False, uses_top_p=False).cpu().numpy()
     monkeypatch.setattr(ops, "_SAMPLE_WIDE", False)
     one = ops.sample(dev(logits), t, dev(u)).cpu().numpy()
-    assert wide.tolist() == one.tolist()
+    assert wide.tolist() == one.tolist() and fused.tolist() == one.tolist()
+    assert fused_big.tolist() == ops.sample(dev(big), tb, dev(ub)).cpu().numpy().tolist()
     assert int(ops.error_flag("cuda").item()) == 0
 
 
