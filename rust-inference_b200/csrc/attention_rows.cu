@@ -15,8 +15,9 @@
 // Work is shared between rows, not split inside one: a block takes up to `tile_q` consecutive new tokens
 // of one sequence and up to `group_chunk` query heads of one kv head, stages each strip of keys and
 // values once in shared memory (as float32) for all of them, and every warp then takes the rows
-// w, w + 8, ...: a row belongs to one warp from start to end, its running maximum, sum and output
-// live in shared memory between strips.  Keys and values are thus read from memory once per
+// w, w + 8, ... two at a time (two query heads of one token: what is read of a key or a value from shared memory
+// serves both): a row belongs to one warp from start to end, its running maximum, sum and output live in shared
+// memory between strips.  Keys and values are thus read from memory once per
 // (tile, kv head) where one block per (token, head) would read them tile_q x group size times.
 //
 //   q, out  [tokens, H, Dh];  k_pool, v_pool [pages, KV, page_size, Dh]
@@ -50,6 +51,93 @@ template <> struct ArVec<__nv_bfloat16> {
 };
 
 __host__ __device__ inline int ar_key_pitch(int Dh, bool vec4) { return vec4 ? Dh + 4 : Dh + 1; }    // floats per staged key
+
+// One strip of keys for R (1 or 2) rows that follow each other in shared memory and see the same keys j_lo .. j_hi of
+// the strip: scores (lane j = key j), the online-softmax update of each row's maximum and sum, and the rows' outputs
+// (a lane owns head elements lane, lane + 32, ...; the keys are added in rising order).
+template <bool VEC4, int R>
+__device__ __forceinline__ void ar_strip(const float* __restrict__ qs, float* __restrict__ accs, float* __restrict__ ms,
+                                         float* __restrict__ ls, const float* __restrict__ ks, const float* __restrict__ vs,
+                                         int row, int Dh, int kpitch, int j_lo, int j_hi, float scale, int lane) {
+    const bool mine = lane >= j_lo && lane <= j_hi;
+    float s[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) s[r] = -INFINITY;
+    if (mine) {
+        const float* qr = qs + (size_t)row * Dh;
+        const float* kr = ks + lane * kpitch;
+        float dot[R];
+#pragma unroll
+        for (int r = 0; r < R; r++) dot[r] = 0.0f;
+        if (VEC4) {
+            for (int c = 0; c < Dh; c += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(kr + c);
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    const float4 a = *reinterpret_cast<const float4*>(qr + (size_t)r * Dh + c);
+                    dot[r] = fmaf(a.x, k4.x, dot[r]);
+                    dot[r] = fmaf(a.y, k4.y, dot[r]);
+                    dot[r] = fmaf(a.z, k4.z, dot[r]);
+                    dot[r] = fmaf(a.w, k4.w, dot[r]);
+                }
+            }
+        } else {
+            for (int d = 0; d < Dh; d++) {
+                const float kd = kr[d];
+#pragma unroll
+                for (int r = 0; r < R; r++) dot[r] = fmaf(qr[(size_t)r * Dh + d], kd, dot[r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; r++) s[r] = dot[r] * scale;
+    }
+    float corr[R], p[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+        const float m_old = ms[row + r];
+        const float m_new = fmaxf(m_old, warp_max(s[r]));
+        corr[r] = expf(m_old - m_new);                            // 0 at the row's first strip (m_old is -inf)
+        p[r] = mine ? expf(s[r] - m_new) : 0.0f;
+        const float p_sum = warp_sum(p[r]);
+        __syncwarp();
+        if (lane == 0) {
+            ms[row + r] = m_new;
+            ls[row + r] = ls[row + r] * corr[r] + p_sum;
+        }
+    }
+    // the outputs: four head elements per lane and row at a time, the strip's keys in rising order
+    float* ar = accs + (size_t)row * Dh;
+    for (int d0 = 0; d0 < Dh; d0 += 128) {
+        float a[R][4];
+#pragma unroll
+        for (int r = 0; r < R; r++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const int d = d0 + c * 32 + lane;
+                a[r][c] = d < Dh ? ar[(size_t)r * Dh + d] * corr[r] : 0.0f;
+            }
+        for (int j = j_lo; j <= j_hi; j++) {
+            float pj[R];
+#pragma unroll
+            for (int r = 0; r < R; r++) pj[r] = __shfl_sync(0xffffffffu, p[r], j);
+            const float* vr = vs + j * Dh + d0 + lane;
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+                if (d0 + c * 32 + lane < Dh) {
+                    const float v = vr[c * 32];
+#pragma unroll
+                    for (int r = 0; r < R; r++) a[r][c] = fmaf(pj[r], v, a[r][c]);
+                }
+        }
+#pragma unroll
+        for (int r = 0; r < R; r++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const int d = d0 + c * 32 + lane;
+                if (d < Dh) ar[(size_t)r * Dh + d] = a[r][c];
+            }
+    }
+}
 
 // VEC4: the head size is a multiple of 4 (vector loads, and a staged key's row starts on 16 bytes)
 template <typename T, bool VEC4>
@@ -123,63 +211,20 @@ attention_rows_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, con
             }
         }
         __syncthreads();
-        for (int row = warp; row < rows; row += AR_WARPS) {
-            const int pos = pos0 + row / ng;
+        // a warp takes two query heads of one token at a time (they see the same keys): a key or a value read from
+        // shared memory then serves both rows; each row's own arithmetic and its order are what they would be alone
+        const int pairs = (ng + 1) >> 1;
+        for (int unit = warp; unit < nq * pairs; unit += AR_WARPS) {
+            const int i = unit / pairs, g_first = 2 * (unit - i * pairs);
+            const int pos = pos0 + i;
             const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-            const int j_lo = max(first - key0, 0), j_hi = min(pos - key0, width - 1);       // the row's keys in this strip
-            if (j_lo > j_hi) continue;                                // none: the row's state stays as it is
-            const bool mine = lane >= j_lo && lane <= j_hi;
-            float s = -INFINITY;
-            if (mine) {
-                const float* qr = qs + (size_t)row * Dh;
-                const float* kr = ks + lane * kpitch;
-                float dot = 0.0f;
-                if (VEC4) {
-                    for (int c = 0; c < Dh; c += 4) {
-                        const float4 a = *reinterpret_cast<const float4*>(qr + c);
-                        const float4 k4 = *reinterpret_cast<const float4*>(kr + c);
-                        dot = fmaf(a.x, k4.x, dot);
-                        dot = fmaf(a.y, k4.y, dot);
-                        dot = fmaf(a.z, k4.z, dot);
-                        dot = fmaf(a.w, k4.w, dot);
-                    }
-                } else {
-                    for (int d = 0; d < Dh; d++) dot = fmaf(qr[d], kr[d], dot);
-                }
-                s = dot * scale;
-            }
-            const float m_old = ms[row];
-            const float m_new = fmaxf(m_old, warp_max(s));
-            const float corr = expf(m_old - m_new);                   // 0 at the row's first strip (m_old is -inf)
-            const float p = mine ? expf(s - m_new) : 0.0f;
-            const float p_sum = warp_sum(p);
-            __syncwarp();
-            if (lane == 0) {
-                ms[row] = m_new;
-                ls[row] = ls[row] * corr + p_sum;
-            }
-            // the output: four head elements per lane at a time, the strip's keys in rising order
-            float* ar = accs + (size_t)row * Dh;
-            for (int d0 = 0; d0 < Dh; d0 += 128) {
-                float a[4];
-#pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    const int d = d0 + c * 32 + lane;
-                    a[c] = d < Dh ? ar[d] * corr : 0.0f;
-                }
-                for (int j = j_lo; j <= j_hi; j++) {
-                    const float pj = __shfl_sync(0xffffffffu, p, j);
-                    const float* vr = vs + j * Dh + d0 + lane;
-#pragma unroll
-                    for (int c = 0; c < 4; c++)
-                        if (d0 + c * 32 + lane < Dh) a[c] = fmaf(pj, vr[c * 32], a[c]);
-                }
-#pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    const int d = d0 + c * 32 + lane;
-                    if (d < Dh) ar[d] = a[c];
-                }
-            }
+            const int j_lo = max(first - key0, 0), j_hi = min(pos - key0, width - 1);       // the token's keys in this strip
+            if (j_lo > j_hi) continue;                                // none: the rows' state stays as it is
+            const int row_a = i * ng + g_first;
+            if (g_first + 1 < ng)
+                ar_strip<VEC4, 2>(qs, accs, ms, ls, ks, vs, row_a, Dh, kpitch, j_lo, j_hi, scale, lane);
+            else
+                ar_strip<VEC4, 1>(qs, accs, ms, ls, ks, vs, row_a, Dh, kpitch, j_lo, j_hi, scale, lane);
         }
         key0 += width;
     }

@@ -14,14 +14,16 @@ import plain_qwen3 as plain
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
-# Tolerances, fixed before the first GPU run.
-#  float32: the reference's own bound for its f32 engine against the float64 model,
-#           max|a-b| <= 2e-4 * max|want| + 1e-5 (tests/model_parity.rs:23-28 there).
-#  bfloat16: activations are rounded to 8 significant bits between parts; with the
-#           residual stream in float32 the logits of these small models stay within
-#           4 % of the largest logit.  The reference accepts far more for its bf16 path
-#           (cosine > 0.995, tests/cuda_parity.rs:154-166).
-TOL = {"float32": (2e-4, 1e-5), "bfloat16": (4e-2, 1e-3)}
+# Tolerances: max|got - want| <= rel * max|want| + abs per row of logits.
+#  float32: the reference's own bound for its f32 engine against the float64 model is 2e-4 * max|want| + 1e-5
+#           (tests/model_parity.rs:23-28 there).  The worst row of any replay test here (tiny models, the large
+#           models' layer shapes, Qwen3-8B's width with the head of 151,936 rows) comes to 0.044 of that bound, so
+#           the tests hold the engine to an eighth of it: 2.5e-5, a little under three times the worst seen.
+#  bfloat16: activations are rounded to 8 significant bits between parts; with the residual stream in float32
+#           the worst row seen is 1.84 % of the largest logit (8B layer shapes, 64 sequences decoding together),
+#           and the bound is twice that.  The reference accepts far more for its bf16 path (cosine > 0.995,
+#           tests/cuda_parity.rs:154-166).
+TOL = {"float32": (2.5e-5, 1e-5), "bfloat16": (3.7e-2, 1e-3)}
 
 
 def make_model_dir(tmp_path, config, seed, stored="float32", name="model"):
