@@ -769,3 +769,60 @@ print("gave up after %.1f ms" % ms)
     assert r.returncode == 0, r.stdout + r.stderr
     ms = float(r.stdout.split("after")[1].split()[0])
     assert 3.0 <= ms <= 2000.0, r.stdout          # the first launch also loads the library: no tight upper bound
+
+
+@pytest.mark.parametrize("Dh,window,n", [(128, 100, 450), (64, 33, 300), (32, 64, 257), (48, 1, 90)])
+def test_window_edges_stand_out(Dh, window, n):
+    """The two keys at a window's edge get a score far above all others in two heads: in head 0 the last key
+    outside the window (position pos - window), in head 1 the first one inside (pos - window + 1).  A kernel that
+    is off by one at the edge returns the outside key's value row in head 0, or misses the inside key's in head 1.
+    Checked for the newest token through the decode kernels, the float32-order kernel in both dtypes, and for
+    several query positions at once through the prefill kernels (head sizes 64 and 128: tcgen05; others: mma.sync)."""
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(Dh + window)
+    H, KV = 2, 1
+    bt = torch.bfloat16
+    scale = 1.0 / math.sqrt(Dh)
+    new = 70                                         # the last `new` positions are this step's queries
+    table, slots, k, v, k_pool, v_pool = _fill_pools(rng, [n], KV, Dh, "bfloat16", scale=0.1)
+    q = rnd(rng, new, H, Dh, scale=0.1, dtype="bfloat16")
+    # per checked query one direction that only it and the two keys at its window's edge carry
+    kk = k[0].copy()
+    q = q.astype(np.float32)
+    dims = rng.permutation(Dh)
+    checks = []
+    for c, t in enumerate((0, new // 2, new - 1)):
+        pos = n - new + t
+        outside, inside = pos - window, pos - window + 1
+        if outside < 0:
+            continue
+        q[t, :, dims[c]] += 40.0
+        kk[outside, 0, dims[c]] += 60.0
+        kk[inside, 0, dims[c]] += 30.0
+        checks.append((t, pos, outside, inside))
+    q = plain.bf16_round(q)
+    assert checks
+    kk = plain.bf16_round(kk)
+    kp = k_pool.copy()
+    for j in range(n):
+        kp[table[slots[0], j // 32], :, j % 32] = kk[j]
+    want = plain.causal_attention(np.concatenate([np.zeros((n - new, H, Dh)), q.astype(np.float64)]),
+                                  kk.astype(np.float64), v[0].astype(np.float64), window=window)[n - new:]
+    i32 = lambda a: dev(np.asarray(a), torch.int32)
+    args = (i32(table), i32(slots), i32([0, new]), i32([n]), new, scale, window)
+    outs = {"prefill": ops.attention_prefill(dev(q, bt), dev(kp, bt), dev(v_pool, bt), *args),
+            "rows bfloat16": ops.attention(dev(q, bt), dev(kp, bt), dev(v_pool, bt), *args),
+            "rows float32": ops.attention(dev(q), dev(kp), dev(v_pool), *args)}
+    last = dev(q[new - 1:new], bt)
+    outs_last = {"decode": ops.attention_decode(last, dev(kp, bt), dev(v_pool, bt), i32(table), i32(slots), i32([n]),
+                                                scale, window, n)}
+    assert _take_error(ops) == 0
+    for t, pos, outside, inside in checks:
+        # (the plain attention agrees that the edge decides: the inside key takes nearly all the weight)
+        assert np.abs(want[t, 0] - v[0][inside, 0]).max() < 0.05 * np.abs(v[0]).max()
+        for name, out in outs.items():
+            got = out[t].float().cpu().numpy()
+            assert np.abs(got - want[t]).max() <= 2e-2 * np.abs(want).max(), (name, t, pos, "window edge")
+            assert np.abs(got[0] - v[0][outside, 0]).max() > 0.2, (name, t, "took the key outside the window")
+    got = outs_last["decode"][0].float().cpu().numpy()
+    assert np.abs(got - want[new - 1]).max() <= 2e-2 * np.abs(want).max(), "decode, window edge"

@@ -627,3 +627,80 @@ def test_attention_refuses_a_per_head_norm_it_does_not_have():
     spec = AttentionSpec(hidden_size=32, num_heads=2, num_kv_heads=1, head_dim=16, qk_norm=OtherNormSpec(16, 1e-5))
     with pytest.raises(ValueError, match="per-head norm"):
         build_part("mixer", spec, env("float32"))
+
+
+# ---- the remaining parts alone: embedding, output head, the arrangement of a layer -----------------------------
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding_and_head_parts(dtype):
+    from rust_inference_b200.config import EmbeddingSpec, HeadSpec
+    rng = np.random.default_rng(5)
+    V, D = 333, 56
+    table = rng.standard_normal((V, D)).astype(np.float32)
+    table = plain.bf16_round(table) if dtype == "bfloat16" else table
+    emb = build_part("embedding", EmbeddingSpec(V, D), env(dtype))
+    emb.load({"weight": dev(table, DT[dtype])})
+    ids = np.array([0, 332, 7, 7, 100], dtype=np.int32)
+    rows = emb(dev(ids, torch.int32))
+    assert rows.dtype == torch.float32 and np.array_equal(rows.cpu().numpy(), plain.embedding(ids, table).astype(np.float32))
+    head = build_part("head", HeadSpec(V, D), env(dtype))
+    head.load({"weight": emb.table})                  # tied: the embedding's own storage
+    assert head.weight.data_ptr() == emb.table.data_ptr()
+    x = rng.standard_normal((4, D)).astype(np.float32)
+    x = plain.bf16_round(x) if dtype == "bfloat16" else x
+    logits = head(dev(x, DT[dtype]))
+    want = plain.linear(x, table)
+    assert logits.dtype == torch.float32 and logits.shape == (4, V)
+    assert np.abs(logits.cpu().numpy() - want).max() <= (1e-5 if dtype == "float32" else 2e-2) * np.abs(want).max()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prenorm_block_alone(dtype):
+    """One layer's arrangement by itself: the pending output of the part before is added by the first norm, the
+    block's own outputs by the norms after them; against the plain decoder layer on a whole sequence."""
+    from rust_inference_b200.cache import Cache
+    from rust_inference_b200.parts import build_block
+    from rust_inference_b200.parts.base import StepContext
+    rng = np.random.default_rng(8)
+    D, Hh, KV, Dh, I, n = 48, 3, 1, 16, 72, 37
+    norm = RMSNormSpec(size=D, eps=1e-5)
+    attn = AttentionSpec(hidden_size=D, num_heads=Hh, num_kv_heads=KV, head_dim=Dh, position=RopeSpec(head_dim=Dh, theta=1e4),
+                         qk_norm=RMSNormSpec(size=Dh, eps=1e-5))
+    spec = LayerSpec(mixer=attn, ffn=SwiGLUSpec(hidden_size=D, intermediate_size=I), mixer_norm=norm, ffn_norm=norm)
+    block = build_block(spec, env(dtype))
+    assert [name for name, _, _, _ in block.parts()] == ["mixer_norm", "mixer", "ffn_norm", "ffn"]
+    p = "model.layers.0."
+    W = {p + "self_attn.q_proj.weight": (Hh * Dh, D), p + "self_attn.k_proj.weight": (KV * Dh, D),
+         p + "self_attn.v_proj.weight": (KV * Dh, D), p + "self_attn.o_proj.weight": (D, Hh * Dh),
+         p + "mlp.gate_proj.weight": (I, D), p + "mlp.up_proj.weight": (I, D), p + "mlp.down_proj.weight": (D, I)}
+    W = {k: (rng.standard_normal(s) * 0.2).astype(np.float32) for k, s in W.items()}
+    if dtype == "bfloat16":
+        W = {k: plain.bf16_round(w) for k, w in W.items()}
+    for k in ("input_layernorm.weight", "post_attention_layernorm.weight"):
+        W[p + k] = (1 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    for k in ("self_attn.q_norm.weight", "self_attn.k_norm.weight"):
+        W[p + k] = (1 + 0.1 * rng.standard_normal(Dh)).astype(np.float32)
+    role = lambda k: torch.float32 if "norm" in k else DT[dtype]
+    take = lambda prefix: {k[len(prefix):]: dev(w, role(k)) for k, w in W.items() if k.startswith(prefix)}
+    block.mixer_norm.load(take(p + "input_layernorm."))
+    block.ffn_norm.load(take(p + "post_attention_layernorm."))
+    block.mixer.load(take(p + "self_attn."))
+    block.ffn.load(take(p + "mlp."))
+    block.mixer.prepare(64)
+    cache = Cache([block.mixer.cache_request()], num_slots=1, num_pages=2, max_pages_per_seq=2, dtype=DT[dtype], device="cuda")
+    slot = cache.alloc_slot()
+    cache.extend([(slot, n)])
+    cache.upload()
+    i32 = lambda a: dev(np.asarray(a), torch.int32)
+    ctx = StepContext(tok_seq=i32(np.zeros(n)), tok_pos=i32(np.arange(n)), seq_slot=i32([slot]), seq_start=i32([0, n]),
+                      seq_len=i32([n]), num_tokens=n, num_seqs=1, max_new=n, max_len=n)
+    h0 = rng.standard_normal((n, D)).astype(np.float32)
+    pending = rng.standard_normal((n, D)).astype(np.float32) * 0.1
+    pending = plain.bf16_round(pending) if dtype == "bfloat16" else pending
+    resid = dev(h0)
+    resid_out, delta = block(resid, dev(pending, DT[dtype]), ctx, cache.layer(0))
+    got = resid_out.float().cpu().numpy() + delta.float().cpu().numpy()
+    cfg = {"num_attention_heads": Hh, "num_key_value_heads": KV, "head_dim": Dh, "hidden_size": D, "rms_norm_eps": 1e-5,
+           "rope_theta": 1e4}
+    want = plain.decoder_layer(h0.astype(np.float64) + pending, {k: w.astype(np.float64) for k, w in W.items()}, 0, cfg, np.arange(n))
+    assert np.abs(got - want).max() <= (2e-5 if dtype == "float32" else 3e-2) * np.abs(want).max()
