@@ -40,3 +40,25 @@ def test_replay_three_ways(tmp_path, model_dirs, name, dtype):
     if dtype == "float32":
         H.assert_rows_identical(by_cutting, f"{name} float32")
     print(f"{name} {dtype}: worst error / bound = {worst}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["E", "F", "G", "H"])
+def test_odd_sizes(tmp_path, name, dtype):
+    """Sizes at the edges of what the kernels take, or beyond them where another kernel stands in (see
+    tiny_configs.ODD): whole requests, the last 32 tokens one by one, and a batch that shrinks, against the plain
+    model; in float32 the rows of the cuttings are the same bits."""
+    from tiny_configs import ODD
+    cfg, stored = ODD[name]
+    d = H.make_model_dir(tmp_path, cfg, seed=40 + ord(name), stored=stored, name=name)
+    reqs = H.random_requests(np.random.default_rng(ord(name)), cfg["vocab_size"], [70, 33, 1, 140, 65])
+    want = H.plain_logits(d, reqs, dtype)
+    by_cutting = {}
+    for label, steps in (("whole", H.trace_whole(reqs)), ("tail", H.trace_tail(reqs, tail=32)),
+                         ("batches", H.trace_batches(reqs, 5, [20, 3, 0, 40, 33]))):
+        out = str(tmp_path / f"out_{label}")
+        H.replay_inprocess(d, dtype, steps, out, device="cuda")
+        by_cutting[label] = H.collect(steps, out, cfg["vocab_size"])
+        H.assert_rows_close(by_cutting[label], want, dtype, f"odd sizes {name} {dtype} {label}")
+    if dtype == "float32":
+        H.assert_rows_identical(by_cutting, f"odd sizes {name}")
