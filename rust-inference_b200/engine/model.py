@@ -56,7 +56,7 @@ def _part_tensors(spec):
         yield _end_name(spec.head_name, local), info, ("head",), local
 
 
-def expected_tensors(spec, for_writing: bool = False) -> Dict[str, ParamInfo]:
+def expected_tensors(spec) -> Dict[str, ParamInfo]:
     """name -> ParamInfo of every tensor the checkpoint has to hold."""
     return {name: info for name, info, _, _ in _part_tensors(spec)}
 

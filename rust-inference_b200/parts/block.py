@@ -63,9 +63,5 @@ def norm_before(norm, resid, delta, reader):
 
 
 def build_block(spec, env):
+    """The block of a layer record: the class registered for its ``arrangement``."""
     return part_class("block", spec)(spec, env)
-
-
-def Block(spec, env):
-    """The block of a layer record (kept as a callable name: ``Block(layer_spec, env)``)."""
-    return build_block(spec, env)

@@ -99,7 +99,7 @@ def write_random_model(config: dict, seed: int, out_dir: str, dtype: str = "bflo
     tdt = {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype]
     cfg = config_from_dict(config)
     spec = cfg.to_spec()
-    expected = expected_tensors(spec, for_writing=True)
+    expected = expected_tensors(spec)
     os.makedirs(out_dir, exist_ok=True)
     save_safetensors(os.path.join(out_dir, "model.safetensors"), random_tensors(expected, seed, tdt))
     d = dict(config)
