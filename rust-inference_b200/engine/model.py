@@ -176,7 +176,7 @@ class Model:
     def forward(self, ids: torch.Tensor, ctx, cache, want_rows: Optional[torch.Tensor]) -> torch.Tensor:
         """float32 logits [wanted rows, vocab] for the packed tokens ``ids``."""
         with section("embedding"):
-            resid = self.embed_part(ids)
+            resid = self.embed_part(ids, ctx)
         delta = None
         for e in self.spec.schedule:
             resid, delta = self.blocks[e.layer](resid, delta, ctx, cache.layer(e.cache, e.writes))

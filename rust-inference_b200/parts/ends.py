@@ -11,9 +11,10 @@ given the embedding's table instead of a tensor of its own.
 Another architecture registers other kinds (a scaled embedding, a head with a soft-cap or a bias)
 with ``@register_embedding`` / ``@register_head`` and names them in its ``ModelSpec``.
 
-Interfaces: embedding ``__call__(ids) -> float32 [tokens, hidden]`` and ``table`` (what a tied head
-shares); head ``__call__(x) -> float32 [rows, vocab]``, ``load(tensors)`` where ``tensors["weight"]``
-is its own tensor or the embedding's table.
+Interfaces: embedding ``__call__(ids, ctx) -> float32 [tokens, hidden]`` (``ctx`` is the step's
+:class:`~.base.StepContext`: an embedding that adds learned positions reads ``ctx.tok_pos``) and
+``table`` (what a tied head shares); head ``__call__(x) -> float32 [rows, vocab]``, ``load(tensors)``
+where ``tensors["weight"]`` is its own tensor or the embedding's table.
 """
 from __future__ import annotations
 
@@ -38,7 +39,7 @@ class TokenEmbedding(Part):
     def weight_bytes(self):
         return self.table.numel() * self.table.element_size()
 
-    def __call__(self, ids):
+    def __call__(self, ids, ctx=None):
         return ops.embed(ids, self.table)
 
 

@@ -474,7 +474,7 @@ def test_toy_architecture_with_two_cache_groups_a_shared_cache_and_routing(tmp_p
 # ---- a toy architecture with an arrangement, an embedding and an output head of its own, all defined here ------
 #
 # One norm per layer whose output feeds the mixer and the feed-forward side by side (their outputs are added
-# to the stream together); an embedding scaled by sqrt(width); a head with a bias and a soft-cap.
+# to the stream together); an embedding scaled by sqrt(width) plus learned positions; a head with a bias and a soft-cap.
 
 from rust_inference_b200.parts import (BlockBase, Part, norm_before, register_block, register_embedding,  # noqa: E402
                                        register_head)
@@ -509,21 +509,24 @@ class ScaledEmbeddingSpec:
     vocab_size: int
     hidden_size: int
     scale: float
+    positions: int
     kind: str = "toy_scaled"
 
 
 @register_embedding("toy_scaled")
 class ScaledEmbedding(Part):
+    """table[id] * scale + learned[position]: the positions come from the step's context."""
     @classmethod
     def param_infos(cls, spec):
-        return {"weight": ParamInfo((spec.vocab_size, spec.hidden_size))}
+        return {"weight": ParamInfo((spec.vocab_size, spec.hidden_size)),
+                "positions": ParamInfo((spec.positions, spec.hidden_size))}
 
     def load(self, tensors):
-        self.table = tensors["weight"]
+        self.table, self.learned = tensors["weight"], tensors["positions"].float()
 
-    def __call__(self, ids):
+    def __call__(self, ids, ctx):
         from rust_inference_b200 import ops
-        return ops.embed(ids, self.table) * self.spec.scale
+        return ops.embed(ids, self.table) * self.spec.scale + self.learned[ctx.tok_pos.long()]
 
 
 @dataclass(frozen=True)
@@ -578,13 +581,13 @@ class ParallelConfig:
                          schedule=(ScheduleEntry(0, 0), ScheduleEntry(1, 1)), final_norm=norm, tie_embeddings=False,
                          max_positions=256, embedding_name="tok.weight", head_name="out.weight", final_norm_prefix="norm.",
                          head_optional=False,
-                         embedding=ScaledEmbeddingSpec(self.vocab_size, D, math.sqrt(D)),
+                         embedding=ScaledEmbeddingSpec(self.vocab_size, D, math.sqrt(D), 256),
                          head=CappedHeadSpec(self.vocab_size, D, self.cap))
 
 
 def parallel_plain(cfg, W, ids):
     n, D = len(ids), cfg.hidden_size
-    h = W["tok.weight"][np.asarray(ids)] * math.sqrt(D)
+    h = W["tok.weight"][np.asarray(ids)] * math.sqrt(D) + W["tok.positions"][:n]
     for i in range(2):
         p = f"blocks.{i}."
         x = plain.rms_norm(h, W[p + "norm.weight"], 1e-5)
@@ -602,7 +605,7 @@ def test_toy_architecture_with_its_own_arrangement_embedding_and_head(tmp_path):
     from rust_inference_b200.engine import expected_tensors
     cfg = ParallelConfig()
     names = set(expected_tensors(cfg.to_spec()))
-    assert {"tok.weight", "out.weight", "out.bias", "blocks.1.norm.weight", "blocks.0.attn.q_proj.weight",
+    assert {"tok.weight", "tok.positions", "out.weight", "out.bias", "blocks.1.norm.weight", "blocks.0.attn.q_proj.weight",
             "blocks.1.ffn.down_proj.weight"} <= names and not any("norm1" in n or "mixer_norm" in n for n in names)
     d = H.make_model_dir(tmp_path, cfg.to_dict(), seed=12, stored="float32", name="parallel")
     W = {k: v.astype(np.float64) for k, v in plain.read_safetensors(d + "/model.safetensors").items()}
