@@ -121,3 +121,40 @@ def test_full_width_with_the_real_output_head(tmp_path, dtype):
     if dtype == "float32":
         H.assert_rows_identical(by_cutting, "full width float32")
     print(f"Qwen3-8B width, 2 of 36 layers, vocabulary 151,936, {dtype}: worst error / bound = {worst}")
+
+
+# ---- all 36 layers of Qwen3-8B: the cuttings against each other -------------------------------------------------
+#
+# The plain model would need minutes on the CPU for this depth, so here the engine is compared with itself: in
+# float32 the three cuttings must give the same bits (with 36 layers between a token and its logits, and the real
+# head), and the bfloat16 engine must stay close to the float32 one (the reference accepts a cosine above 0.995
+# between its bfloat16 GPU path and its float32 path: tests/cuda_parity.rs:154-166).
+
+def test_all_36_layers_cuttings_agree(tmp_path):
+    import torch
+    from rust_inference_b200.engine import Model
+    cfg = dict(FULL_8B, num_hidden_layers=36)
+    reqs = H.random_requests(np.random.default_rng(6), cfg["vocab_size"], [70, 33, 97])
+    cuttings = (("whole", H.trace_whole(reqs)), ("tail", H.trace_tail(reqs, tail=32)),
+                ("batches", H.trace_batches(reqs, 3, [9, 32, 0])))
+    rows = {}
+    for dtype in ("float32", "bfloat16"):
+        model = Model.from_random(dict(cfg), FULL_SEED, dtype=dtype, device="cuda:0")
+        for label, steps in cuttings if dtype == "float32" else cuttings[:1]:
+            out = str(tmp_path / f"out_{dtype}_{label}")
+            H.replay_inprocess(None, dtype, steps, out, device="cuda", model=model)
+            rows[(dtype, label)] = H.collect(steps, out, cfg["vocab_size"])
+            shutil.rmtree(out, ignore_errors=True)
+        del model
+        torch.cuda.empty_cache()
+    H.assert_rows_identical({label: rows[("float32", label)] for label, _ in cuttings}, "36 layers float32")
+    f32, b16 = rows[("float32", "whole")], rows[("bfloat16", "whole")]
+    worst_cos, worst_rel = 1.0, 0.0
+    for key, a in f32.items():
+        b = b16[key].astype(np.float64)
+        a = a.astype(np.float64)
+        worst_cos = min(worst_cos, float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b))))
+        worst_rel = max(worst_rel, float(np.abs(a - b).max() / np.abs(a).max()))
+        assert int(np.argmax(a)) == int(np.argmax(b)) or np.sort(a)[-1] - np.sort(a)[-2] < 0.05 * np.abs(a).max()
+    print(f"36 layers: bfloat16 against float32 engine: worst cosine {worst_cos:.5f}, worst |diff| / max|logit| {worst_rel:.4f}")
+    assert worst_cos > 0.995
