@@ -715,18 +715,30 @@ attention_decode_merge_kernel(const float* __restrict__ o_part, const float* __r
         // this warp's quarter of the tile
         const int lo = n * warp / MW, hi = n * (warp + 1) / MW;
         for (int i = lo + lane; i < hi; i += 32) L += ml[(t0 + i) * 2 + 1] * s_w[i];
-#pragma unroll 4
-        for (int i = lo; i < hi; i++) {
-            const float w = s_w[i];
+        // eight chunks' partial outputs are asked for before the first is added (the additions stay in rising order
+        // of the chunks): the loop is a chain of loads from L2 otherwise, and the kernel nothing but that chain
+        for (int i0 = lo; i0 < hi; i0 += 8) {
+            float4 v[8][PER];
 #pragma unroll
-            for (int j = 0; j < PER; j++) {
-                const int d = (j * 32 + lane) * 4;
-                if (d < AD_DH) {
-                    const float4 v = *(const float4*)(op + (size_t)(t0 + i) * AD_DH + d);
-                    acc[j].x = fmaf(v.x, w, acc[j].x);
-                    acc[j].y = fmaf(v.y, w, acc[j].y);
-                    acc[j].z = fmaf(v.z, w, acc[j].z);
-                    acc[j].w = fmaf(v.w, w, acc[j].w);
+            for (int u = 0; u < 8; u++)
+#pragma unroll
+                for (int j = 0; j < PER; j++) {
+                    const int d = (j * 32 + lane) * 4;
+                    if (i0 + u < hi && d < AD_DH) v[u][j] = *(const float4*)(op + (size_t)(t0 + i0 + u) * AD_DH + d);
+                }
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                if (i0 + u >= hi) break;
+                const float w = s_w[i0 + u];
+#pragma unroll
+                for (int j = 0; j < PER; j++) {
+                    const int d = (j * 32 + lane) * 4;
+                    if (d < AD_DH) {
+                        acc[j].x = fmaf(v[u][j].x, w, acc[j].x);
+                        acc[j].y = fmaf(v[u][j].y, w, acc[j].y);
+                        acc[j].z = fmaf(v[u][j].z, w, acc[j].z);
+                        acc[j].w = fmaf(v[u][j].w, w, acc[j].w);
+                    }
                 }
             }
         }
