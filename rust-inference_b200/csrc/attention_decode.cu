@@ -676,17 +676,18 @@ attention_decode_merge_kernel(const float* __restrict__ o_part, const float* __r
     const int h = blockIdx.x, b = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     pdl_trigger();
-    pdl_wait();
-    const int len = seq_len[b];
+    const int len = seq_len[b];                          // a table of the step, not the work of the kernel before
     const int first_key = (window > 0 && len - window > 0) ? len - window : 0;
     int c_lo = first_key / AD_CHUNK, c_hi = (len + AD_CHUNK - 1) / AD_CHUNK;           // [c_lo, c_hi)
-    if (c_hi > max_chunks) {
+    const bool too_long = c_hi > max_chunks;
+    if (too_long) {
         // the caller's scratch memory has no partial results for the keys past max_chunks * 128: they are left
         // out (nothing is read past the sequence's rows) and the mistake is reported
-        if (threadIdx.x == 0) atomicExch(err, 7);
         c_hi = max_chunks;
         c_lo = c_lo < c_hi ? c_lo : c_hi;
     }
+    pdl_wait();
+    if (too_long && threadIdx.x == 0) atomicExch(err, 7);
     const float* ml = ml_part + ((size_t)b * H + h) * max_chunks * 2;
     const float* op = o_part + ((size_t)b * H + h) * max_chunks * AD_DH;
     __shared__ float s_w[AD_MERGE_TILE], s_red[MW], s_l[MW];

@@ -103,6 +103,19 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restric
                                    int write_back, int n_rows, WeightHint next) {
     __shared__ float red[33];
     pdl_trigger();
+    const int nvec = dim >> 2;
+    // the gains (and which row this block norms: a table of the step) are not the work of the kernel before this
+    // one: they are read before the wait for it, which takes a load from memory out of the chain behind the wait
+    float4 g[NV];
+    size_t r = blockIdx.x;
+    if ((int)blockIdx.x < n_rows) {
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            int i = threadIdx.x + j * blockDim.x;
+            if (i < nvec) g[j] = ld4(gain + 4 * i);
+        }
+        if (rows) r = (size_t)rows[blockIdx.x];
+    }
     pdl_wait();
     if ((int)blockIdx.x >= n_rows) {
         // the blocks beyond the rows ask for the weights that the linear after this norm reads
@@ -110,10 +123,8 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restric
                              ((int)gridDim.x - n_rows) * (int)blockDim.x);
         return;
     }
-    size_t r = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
     float* rp = resid + r * dim;
     const T* dp = delta ? delta + r * dim : nullptr;
-    const int nvec = dim >> 2;
     float4 v[NV];
     float ss = 0.0f;
 #pragma unroll
@@ -139,10 +150,8 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restric
 #pragma unroll
     for (int j = 0; j < NV; j++) {
         int i = threadIdx.x + j * blockDim.x;
-        if (i < nvec) {
-            float4 g = ld4(gain + 4 * i);
-            st4(op + 4 * i, make_float4(v[j].x * inv * g.x, v[j].y * inv * g.y, v[j].z * inv * g.z, v[j].w * inv * g.w));
-        }
+        if (i < nvec)
+            st4(op + 4 * i, make_float4(v[j].x * inv * g[j].x, v[j].y * inv * g[j].y, v[j].z * inv * g[j].z, v[j].w * inv * g[j].w));
     }
 }
 

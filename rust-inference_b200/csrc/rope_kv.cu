@@ -112,28 +112,27 @@ __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, T* __r
                                                int page_size, int num_pages, int write_kv, int* __restrict__ err) {
     constexpr int Dh = 32 * VEC;
     pdl_trigger();
-    pdl_wait();
+    // What the kernel before this one does not write is read before the wait for it: the step's tables (copied to
+    // the device before the step's first kernel), the page table, the angles of this position and the gains.  With
+    // a handful of tokens this kernel is a chain of dependent loads, and these are three links of it.
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int pos = tok_pos[t];
     const int slot = seq_slot[tok_seq[t]];
-    int page = -1;
+    int page = -1, bad = 0;
     if (write_kv) {
         page = page_table[(size_t)slot * mpps + pos / page_size];
         if (page < 0 || page >= num_pages) {
-            if (threadIdx.x == 0) atomicExch(err, 2);
+            bad = 2;                                             // unmapped page: skip the write, report
             page = -1;
         }
     }
-    if (rope && (pos < 0 || pos >= rope_rows)) {
-        if (threadIdx.x == 0) atomicExch(err, 3);
-        return;
-    }
+    const bool rope_ok = !rope || (pos >= 0 && pos < rope_rows);
     const int heads_total = H + 2 * KV;
     const T* row = qkv + (size_t)t * heads_total * Dh;
     const int d0 = lane * VEC;                                   // this lane's first element
-    float cs_c[VEC], cs_s[VEC];
-    if (rope) {
+    float cs_c[VEC], cs_s[VEC], gq[VEC], gk[VEC];
+    if (rope && rope_ok) {
         const float2* cs = rope + (size_t)pos * (Dh / 2) + (lane & 15) * VEC;
 #pragma unroll
         for (int j = 0; j < VEC; j++) {
@@ -141,6 +140,17 @@ __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, T* __r
             cs_c[j] = c.x;
             cs_s[j] = (lane < 16) ? -c.y : c.y;                  // low half: a*c - b*s; high half: b*c + a*s
         }
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; j++) {
+        gq[j] = q_gain ? q_gain[d0 + j] : 1.0f;
+        gk[j] = k_gain ? k_gain[d0 + j] : 1.0f;
+    }
+    pdl_wait();
+    if (bad && threadIdx.x == 0) atomicExch(err, bad);
+    if (!rope_ok) {
+        if (threadIdx.x == 0) atomicExch(err, 3);
+        return;
     }
     // heads in batches of RK_UNROLL: all their loads are started before the first is worked on
     const int stride = RK_WARPS * gridDim.y;
@@ -176,12 +186,11 @@ __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, T* __r
                 x[j] = ld_f(&in[u].v[j]);
                 ss += x[j] * x[j];
             }
-            const float* gain = which == 0 ? q_gain : k_gain;
-            if (gain) {
+            if (which == 0 ? q_gain != nullptr : k_gain != nullptr) {
                 ss = warp_sum(ss);
                 const float inv = 1.0f / sqrtf(ss / (float)Dh + eps);
 #pragma unroll
-                for (int j = 0; j < VEC; j++) x[j] = x[j] * inv * gain[d0 + j];
+                for (int j = 0; j < VEC; j++) x[j] = x[j] * inv * (which == 0 ? gq[j] : gk[j]);
             }
             VecOf<T, VEC> o;
 #pragma unroll
