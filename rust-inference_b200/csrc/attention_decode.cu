@@ -692,6 +692,18 @@ attention_decode_merge_kernel(const float* __restrict__ o_part, const float* __r
     const float* op = o_part + ((size_t)b * H + h) * max_chunks * AD_DH;
     __shared__ float s_w[AD_MERGE_TILE], s_red[MW], s_l[MW];
     __shared__ __align__(16) float s_acc[MW][AD_DH];
+    // The partial outputs of this warp's first eight chunks are asked for at once, before the maxima (on which
+    // their weights depend) are known: the kernel is a chain of trips to L2, and this takes one out of it.
+    float4 first[8][PER];
+    const int n0 = min(AD_MERGE_TILE, c_hi - c_lo);
+    const int lo0 = n0 * warp / MW, hi0 = n0 * (warp + 1) / MW;
+#pragma unroll
+    for (int u = 0; u < 8; u++)
+#pragma unroll
+        for (int j = 0; j < PER; j++) {
+            const int d = (j * 32 + lane) * 4;
+            if (lo0 + u < hi0 && d < AD_DH) first[u][j] = *(const float4*)(op + (size_t)(c_lo + lo0 + u) * AD_DH + d);
+        }
     // the maximum over the visible chunks
     float M = -FLT_MAX;
     for (int c = c_lo + (int)threadIdx.x; c < c_hi; c += AD_MERGE_THREADS) M = fmaxf(M, ml[c * 2]);
@@ -717,15 +729,17 @@ attention_decode_merge_kernel(const float* __restrict__ o_part, const float* __r
         const int lo = n * warp / MW, hi = n * (warp + 1) / MW;
         for (int i = lo + lane; i < hi; i += 32) L += ml[(t0 + i) * 2 + 1] * s_w[i];
         // eight chunks' partial outputs are asked for before the first is added (the additions stay in rising order
-        // of the chunks): the loop is a chain of loads from L2 otherwise, and the kernel nothing but that chain
+        // of the chunks)
         for (int i0 = lo; i0 < hi; i0 += 8) {
             float4 v[8][PER];
+            const bool have = t0 == c_lo && i0 == lo;             // the ones asked for at the top
 #pragma unroll
             for (int u = 0; u < 8; u++)
 #pragma unroll
                 for (int j = 0; j < PER; j++) {
                     const int d = (j * 32 + lane) * 4;
-                    if (i0 + u < hi && d < AD_DH) v[u][j] = *(const float4*)(op + (size_t)(t0 + i0 + u) * AD_DH + d);
+                    if (have) v[u][j] = first[u][j];
+                    else if (i0 + u < hi && d < AD_DH) v[u][j] = *(const float4*)(op + (size_t)(t0 + i0 + u) * AD_DH + d);
                 }
 #pragma unroll
             for (int u = 0; u < 8; u++) {

@@ -12,6 +12,21 @@
 // ---------------------------------------------------------------------------
 // out[t, :] = float(table[ids[t], :])
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ void embed_load8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void embed_load8(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float2 f = __bfloat1622float2(h[j]);
+        v[2 * j] = f.x;
+        v[2 * j + 1] = f.y;
+    }
+}
+
 template <typename T>
 __global__ void embed_rows_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
                                   int dim, int vocab, int* __restrict__ bad) {
@@ -24,6 +39,16 @@ __global__ void embed_rows_kernel(const int* __restrict__ ids, const T* __restri
     }
     const T* src = table + (size_t)id * dim;
     float* dst = out + (size_t)blockIdx.x * dim;
+    if (dim % 8 == 0 && ((((uintptr_t)table | (uintptr_t)out)) & 15) == 0) {
+        // 16 bytes per load: a row of 4,096 elements is one or two loads per thread instead of sixteen in a row
+        for (int i = threadIdx.x * 8; i < dim; i += blockDim.x * 8) {
+            float v[8];
+            embed_load8(src + i, v);
+            *reinterpret_cast<float4*>(dst + i) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(dst + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = ld_f(src + i);
 }
 
