@@ -68,13 +68,20 @@ struct __align__(1024) SkinnySmem {
 template <int NT, typename OutT, bool SWIGLU>
 __global__ void __launch_bounds__(32 * SK_WARPS, SK_MIN_BLOCKS)
 linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ y, int M, int N,
-                     int K, int* __restrict__ err) {
+                     int K, int early_from, int* __restrict__ err) {
     extern __shared__ __align__(16) unsigned char sk_raw[];
     SkinnySmem& sm = *reinterpret_cast<SkinnySmem*>(sk_raw + ((1024u - (smem_u32(sk_raw) & 1023u)) & 1023u));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int quad = lane >> 2, qc = lane & 3;
     const int rho = (quad >> 1) | ((quad & 1) << 2);          // the W row (of 8) behind MMA row `quad`
     const int n0 = blockIdx.x * SK_ROWS;
+    // The kernel after this one may start when every block of this grid has said so (or has ended).  The blocks of
+    // the grid's last wave (`early_from` on: by then no block of this grid waits for a place on an SM) say so at
+    // once, the earlier ones when their loops are done: so the successor's blocks come in as the last wave drains,
+    // read what they can before their own wait (their first weight stages, their tables) and then sit in it, and a
+    // grid of several waves still keeps the SMs to itself while it has blocks waiting.
+    const bool trigger_early = (int)blockIdx.x >= early_from;
+    if (trigger_early) pdl_trigger();
     // this warp's share of K, in stages of 128 k
     const int stages_total = (K + SK_STAGE_K - 1) / SK_STAGE_K;
     const int st_lo = (int)((long long)stages_total * warp / SK_WARPS), st_hi = (int)((long long)stages_total * (warp + 1) / SK_WARPS);
@@ -159,7 +166,7 @@ linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtenso
             started = i + SK_STAGES + 1;
         }
     }
-    pdl_trigger_late();
+    if (!trigger_early) pdl_trigger_late();
     // acc[t][0,1]: (W row rho, tokens t*8 + 2qc, +1); acc[t][2,3]: (W row rho + 8, same tokens)
 #pragma unroll
     for (int t = 0; t < NT; t++)
@@ -246,8 +253,17 @@ static int launch_skinny(const void* x, const void* w, void* y, int M, int N, in
     int rc = weight_tensor_map(&map, w, N, K);
     if (rc) return rc;
     dim3 grid((N + SK_ROWS - 1) / SK_ROWS);
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    const long long resident = (long long)sms * SK_MIN_BLOCKS;                // blocks on the device at once
+    const int early_from = (long long)grid.x > resident ? (int)((long long)grid.x - resident) : 0;
     ri_launch_pdl(linear_skinny_kernel<NT, OutT, SWIGLU>, grid, dim3(32 * SK_WARPS), SK_SMEM_BYTES, stream, (const bf16*)x,
-                  *map, (OutT*)y, M, N, K, err);
+                  *map, (OutT*)y, M, N, K, early_from, err);
     return 0;
 }
 
