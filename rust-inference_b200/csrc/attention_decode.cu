@@ -474,6 +474,9 @@ attention_decode_stream_kernel(const bf16* __restrict__ q, const __grid_constant
     // sequence); the pages before that one were written by earlier steps and may be copied at once.
 #pragma unroll 1
     while (more && in_flight < SLOTS && (ci.p + 1) * AD_PAGE < ci.len) issue();
+    // every block of this grid is on an SM from the start (one per SM), so the kernel after it (the merge: small
+    // blocks that read the lengths and then wait) may come in at once
+    pdl_trigger();
     pdl_wait();
 #pragma unroll 1
     while (more && in_flight < SLOTS) issue();
@@ -633,7 +636,6 @@ attention_decode_stream_kernel(const bf16* __restrict__ q, const __grid_constant
         live = stream_next<false>(cc, a, lane);
         if (dead) break;
     }
-    pdl_trigger();
 }
 
 // ---- tensor maps of the pools, made on the host -------------------------------------------------------
