@@ -125,6 +125,9 @@ linear_stream_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const unsigned tmem = tail.tmem_base;
+    // the launcher sizes the grid so that all its blocks are on the SMs at once: the kernel after this one (small
+    // blocks that read their tables and wait) may come in right away
+    pdl_trigger();
 
     if (warp == 0 && lane == 0) {
         // ---- the copying lane ---------------------------------------------------------------------------------
@@ -171,7 +174,6 @@ linear_stream_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         tail.dead = 1;
     }
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    pdl_trigger_late();
     // ---- the accumulator: thread = output row (tensor-memory lane), columns = tokens ----------------------------
     const int row = tid;                           // warp w reads lanes 32 w .. 32 w + 31
     const unsigned taddr = tmem + ((unsigned)(warp * 32) << 16);

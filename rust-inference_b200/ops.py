@@ -48,14 +48,16 @@ _NO_TCGEN05 = os.environ.get("RUST_INFERENCE_B200_NO_TCGEN05") == "1"   # for co
 _FUSED_SWIGLU = os.environ.get("RUST_INFERENCE_B200_FUSED_SWIGLU", "1") != "0"
 _WEIGHT_HINTS = os.environ.get("RUST_INFERENCE_B200_WEIGHT_HINTS", "1") != "0"
 SKINNY_MAX_TOKENS = 16      # up to here the bfloat16 linear is this package's weight-streaming kernel
-# For 17 to 128 tokens there is a tcgen05 weight-streaming kernel of this package as well (linear_stream_tc).  Measured
-# at 64 tokens and Qwen3-8B shapes, replayed from a graph: 14.6 / 12.0 / 37.1 / 22.6 us for the four linears of a layer
-# against cuBLAS's 11.5 / 9.6 / 37.9 / 22.3 us, the output head 192 against 213 us, and the whole batch-64 step
-# 3 % slower: so it is taken for wide matrices only (the output head: 65,536 outputs and more), or for all of them
-# when RUST_INFERENCE_B200_STREAM_TC=1 asks for it.
+# For 17 to 128 tokens there is a tcgen05 weight-streaming kernel of this package (linear_stream_tc).  Measured inside
+# the decode step at Qwen3-8B shapes against the library product (cuBLAS): the step is 2.8 % faster with it at 24
+# tokens and 1.9 % at 32, the same at 40, and 1.5 to 2 % slower from 48 on (at 64 tokens a layer's products are
+# half tensor-core-bound, and the library's tiles do better there); the output head (65,536 outputs and more) is
+# faster on it at every token count.  So it is taken up to STREAM_TC_SMALL tokens and for wide matrices;
+# RUST_INFERENCE_B200_STREAM_TC=1 takes it for all linears of 17 to 128 tokens, =0 for none but the wide ones.
 STREAM_TC_MAX_TOKENS = 128
+STREAM_TC_SMALL = 32
 STREAM_TC_WIDE = int(os.environ.get("RUST_INFERENCE_B200_STREAM_TC_WIDE", "65536"))   # from this many outputs on it is taken anyway
-_STREAM_TC = os.environ.get("RUST_INFERENCE_B200_STREAM_TC") == "1"
+_STREAM_TC = os.environ.get("RUST_INFERENCE_B200_STREAM_TC", "")
 # the selection of a token other than the greedy one: from this many logits a row on, several blocks per row
 SAMPLE_WIDE_VOCAB = 16384
 _SAMPLE_WIDE = os.environ.get("RUST_INFERENCE_B200_SAMPLE_WIDE", "1") != "0"
@@ -243,6 +245,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
 
     float32: this package's own FMA kernel (no tensor cores, no TF32).
     bfloat16, up to 16 tokens: this package's weight-streaming tensor-core kernel (mma.sync).
+    bfloat16, 17 to 32 tokens (and up to 128 for wide matrices such as the output head): this package's
+    tcgen05 weight-streaming kernel.
     bfloat16, more tokens: the library GEMM (cuBLAS through torch), as the
     reference engine uses cuBLAS for its linears (src/cuda/mod.rs:186-232 there).
     ``out_dtype`` float32 keeps the float32 accumulator (used for the logits)."""
@@ -264,7 +268,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         _call("linear_skinny", "ri_linear_skinny", x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K,
               1 if out_dtype == torch.float32 else 0, 0, error_flag(x.device).data_ptr(), _stream())
         return y
-    if M <= STREAM_TC_MAX_TOKENS and K % 8 == 0 and (_STREAM_TC or N >= STREAM_TC_WIDE):
+    if M <= STREAM_TC_MAX_TOKENS and K % 8 == 0 and (
+            _STREAM_TC == "1" or N >= STREAM_TC_WIDE or (M <= STREAM_TC_SMALL and _STREAM_TC != "0")):
         return linear_stream_tc(x, w, out_dtype)
     if out_dtype == torch.float32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)

@@ -185,6 +185,11 @@ def test_linear_takes_the_streaming_kernel_for_wide_outputs(monkeypatch):
     close(own, want, 2e-5, "linear (streaming kernel)")
     close(library, want, 2e-5, "linear (library)")
     assert torch.equal(own, ops.linear_stream_tc(xd, wd, out_dtype=torch.float32))
+    # up to 32 tokens the streaming kernel is taken whatever the width (it is the faster one inside a decode step)
+    n0 = ops.launch_count()
+    few = ops.linear(xd[:24], wd, out_dtype=torch.float32)
+    assert ops.launch_count() == n0 + 1
+    close(few, want[:24], 2e-5, "linear (streaming kernel, 24 tokens)")
 
 
 def _paged(rng, lens, KV, Dh, P, dtype, extra_pages=3):
