@@ -180,6 +180,81 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restric
     }
 }
 
+// Many rows (a prompt step): a block of 256 threads takes a row, each thread doing the work of the four threads
+// t, t+256, t+512, t+768 of the 1,024-thread kernel above: the same partial sums, the same warp trees (a warp here
+// computes those of warps w, w+8, w+16 and w+24 there) and the same last tree, so every bit is as above.  Several
+// such blocks fit on an SM, so that one block's loads are on their way while another reduces or stores, and each
+// thread has four times the bytes in flight.
+constexpr int RMS_VT = 4;
+template <typename T, int NV>
+__global__ void __launch_bounds__(256) rmsnorm_many_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                                           const float* __restrict__ gain, T* __restrict__ out, int dim,
+                                                           float eps, int write_back) {
+    __shared__ float red[33];
+    pdl_trigger();
+    pdl_wait();
+    const int nvec = dim >> 2;
+    const int r = blockIdx.x;
+    float* rp = resid + (size_t)r * dim;
+    const T* dp = delta ? delta + (size_t)r * dim : nullptr;
+    float4 v[RMS_VT][NV];
+    float ss[RMS_VT];
+#pragma unroll
+    for (int q = 0; q < RMS_VT; q++)
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            const int i = threadIdx.x + 256 * q + j * 1024;
+            if (i < nvec) {
+                v[q][j] = ld4(rp + 4 * i);
+                if (dp) {
+                    float4 d = ld4(dp + 4 * i);
+                    v[q][j].x += d.x; v[q][j].y += d.y; v[q][j].z += d.z; v[q][j].w += d.w;
+                }
+            }
+        }
+#pragma unroll
+    for (int q = 0; q < RMS_VT; q++) {
+        ss[q] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            const int i = threadIdx.x + 256 * q + j * 1024;
+            if (i < nvec) {
+                const float4 a = v[q][j];
+                if (dp && write_back) st4(rp + 4 * i, a);
+                ss[q] += a.x * a.x;
+                ss[q] += a.y * a.y;
+                ss[q] += a.z * a.z;
+                ss[q] += a.w * a.w;
+            }
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int q = 0; q < RMS_VT; q++) {
+        ss[q] = warp_sum(ss[q]);
+        if (lane == 0) red[warp + 8 * q] = ss[q];
+    }
+    __syncthreads();
+    if (warp == 0) {
+        float t = warp_sum(red[lane]);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    const float inv = 1.0f / sqrtf(red[32] / (float)dim + eps);
+    T* op = out + (size_t)r * dim;
+#pragma unroll
+    for (int q = 0; q < RMS_VT; q++)
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            const int i = threadIdx.x + 256 * q + j * 1024;
+            if (i < nvec) {
+                const float4 g = ld4(gain + 4 * i);
+                st4(op + 4 * i, make_float4(v[q][j].x * inv * g.x, v[q][j].y * inv * g.y, v[q][j].z * inv * g.z,
+                                            v[q][j].w * inv * g.w));
+            }
+        }
+}
+
 template <typename T>
 static bool launch_rmsnorm_vec(float* resid, const void* delta, const int* rows, const float* gain, void* out,
                                int n_rows, int dim, float eps, int write_back, const WeightHint& next, cudaStream_t stream) {
@@ -192,6 +267,11 @@ static bool launch_rmsnorm_vec(float* resid, const void* delta, const int* rows,
     const T* d = (const T*)delta;
     T* o = (T*)out;
     if (nv > 4) return false;
+    if (!rows && !next.base && n_rows >= 512 && threads == 1024 && nv <= 2) {
+        if (nv == 1) ri_launch_pdl(rmsnorm_many_kernel<T, 1>, dim3(n_rows), dim3(256), 0, stream, resid, d, gain, o, dim, eps, write_back);
+        else ri_launch_pdl(rmsnorm_many_kernel<T, 2>, dim3(n_rows), dim3(256), 0, stream, resid, d, gain, o, dim, eps, write_back);
+        return true;
+    }
     // with a hint: as many more blocks as give each thread a few requests
     int extra = 0;
     if (next.base) {

@@ -66,6 +66,28 @@ def test_rmsnorm(dtype, dim):
     close(r2, resid.astype(np.float64), 0, "gathered norm leaves the stream alone")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dim,n_rows", [(72, 513), (4096, 1026), (5120, 700), (12288, 600)])
+def test_rmsnorm_of_many_rows_equals_rows_taken_a_few_at_a_time(dtype, dim, n_rows):
+    """A prompt step's norm runs several rows per block; each row's bits are those of the same
+    row normed in a small call, at a row count that is no multiple of the rows per block."""
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(dim + n_rows)
+    resid = rnd(rng, n_rows, dim)
+    delta = rnd(rng, n_rows, dim, dtype=dtype)
+    gain = dev((1 + 0.1 * rng.standard_normal(dim)).astype(np.float32))
+    r = dev(resid)
+    got = ops.rmsnorm(r, gain, 1e-6, DT[dtype], delta=dev(delta, DT[dtype]))
+    total = resid.astype(np.float64) + delta
+    close(got, plain.rms_norm(total, gain.cpu().numpy(), 1e-6), ETOL[dtype], "many-row add+rmsnorm")
+    for lo in (0, n_rows - 5):
+        r_few = dev(resid[lo:lo + 5])
+        few = ops.rmsnorm(r_few, gain, 1e-6, DT[dtype], delta=dev(delta[lo:lo + 5], DT[dtype]))
+        assert torch.equal(few, got[lo:lo + 5]) and torch.equal(r_few, r[lo:lo + 5])
+    no_delta = ops.rmsnorm(r, gain, 1e-6, DT[dtype])
+    assert torch.equal(no_delta, got)
+
+
 @pytest.mark.parametrize("n,k", [(40, 1024), (7200, 2048), (24, 256), (9, 24)])
 def test_rmsnorm_with_a_weight_hint(n, k):
     """Naming the matrix that the next linear reads changes no result (the kernel only asks for a
