@@ -47,13 +47,17 @@ _NO_TCGEN05 = os.environ.get("RUST_INFERENCE_B200_NO_TCGEN05") == "1"   # for co
 # Qwen3-8B shapes, 0.3 % at batch 8); RUST_INFERENCE_B200_FUSED_SWIGLU=0 takes the separate kernel, for comparisons
 _FUSED_SWIGLU = os.environ.get("RUST_INFERENCE_B200_FUSED_SWIGLU", "1") != "0"
 _WEIGHT_HINTS = os.environ.get("RUST_INFERENCE_B200_WEIGHT_HINTS", "1") != "0"
-SKINNY_MAX_TOKENS = 16      # up to here the bfloat16 linear is this package's weight-streaming kernel
-# For 17 to 128 tokens there is a tcgen05 weight-streaming kernel of this package (linear_stream_tc).  Measured inside
+# Up to here the bfloat16 linear is this package's mma.sync weight-streaming kernel (it takes up to 16 tokens).  From 13
+# tokens on the tcgen05 kernel below is faster inside the decode step (Qwen3-8B shapes, ms a step with 12 / 16 as the
+# limit: 13 tokens 4.65 / 4.73, 14 tokens 4.80 / 4.99, 15 tokens 4.90 / 5.27, 16 tokens 5.02 / 5.48; at 9 and 12 tokens
+# the mma.sync kernel wins by 0.5 to 1 %).  RUST_INFERENCE_B200_SKINNY_MAX=8..16 moves the limit, for comparisons.
+SKINNY_MAX_TOKENS = min(16, max(1, int(os.environ.get("RUST_INFERENCE_B200_SKINNY_MAX", "12"))))
+# For 13 to 128 tokens there is a tcgen05 weight-streaming kernel of this package (linear_stream_tc).  Measured inside
 # the decode step at Qwen3-8B shapes against the library product (cuBLAS): the step is 2.8 % faster with it at 24
 # tokens and 1.9 % at 32, the same at 40, and 1.5 to 2 % slower from 48 on (at 64 tokens a layer's products are
 # half tensor-core-bound, and the library's tiles do better there); the output head (65,536 outputs and more) is
 # faster on it at every token count.  So it is taken up to STREAM_TC_SMALL tokens and for wide matrices;
-# RUST_INFERENCE_B200_STREAM_TC=1 takes it for all linears of 17 to 128 tokens, =0 for none but the wide ones.
+# RUST_INFERENCE_B200_STREAM_TC=1 takes it for all linears of 13 to 128 tokens, =0 for none but the wide ones.
 STREAM_TC_MAX_TOKENS = 128
 STREAM_TC_SMALL = 32
 STREAM_TC_WIDE = int(os.environ.get("RUST_INFERENCE_B200_STREAM_TC_WIDE", "65536"))   # from this many outputs on it is taken anyway
@@ -244,8 +248,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     """y = x w^T for x [M, K], w [N, K].
 
     float32: this package's own FMA kernel (no tensor cores, no TF32).
-    bfloat16, up to 16 tokens: this package's weight-streaming tensor-core kernel (mma.sync).
-    bfloat16, 17 to 32 tokens (and up to 128 for wide matrices such as the output head): this package's
+    bfloat16, up to 12 tokens: this package's weight-streaming tensor-core kernel (mma.sync).
+    bfloat16, 13 to 32 tokens (and up to 128 for wide matrices such as the output head): this package's
     tcgen05 weight-streaming kernel.
     bfloat16, more tokens: the library GEMM (cuBLAS through torch), as the
     reference engine uses cuBLAS for its linears (src/cuda/mod.rs:186-232 there).

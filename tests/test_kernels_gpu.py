@@ -136,9 +136,11 @@ def test_linear_f32(shape):
 
 @pytest.mark.parametrize("shape", [(1, 64, 64), (5, 48, 80), (300, 264, 1000), (8, 100, 4096), (3, 257, 1544),
                                    (9, 40, 72), (16, 4096, 264), (2, 151936, 96), (17, 64, 64)])
-def test_linear_bf16(shape):
+def test_linear_bf16(shape, monkeypatch):
     from rust_inference_b200 import ops
     M, N, K = shape
+    if M <= 16:
+        monkeypatch.setattr(ops, "SKINNY_MAX_TOKENS", 16)      # the mma.sync kernel over its whole range of tokens
     rng = np.random.default_rng(M)
     x, w = rnd(rng, M, K, dtype="bfloat16"), rnd(rng, N, K, dtype="bfloat16")
     want = plain.linear(x, w)
@@ -151,10 +153,11 @@ def test_linear_bf16(shape):
 
 
 @pytest.mark.parametrize("shape", [(1, 32, 64), (5, 208, 520), (16, 4096, 1024), (9, 48, 72)])
-def test_linear_swiglu_fused(shape):
+def test_linear_swiglu_fused(shape, monkeypatch):
     """The weight-streaming linear with the SiLU gate in its epilogue: gate and up rows interleaved
     in blocks of 8, widths and depths that end inside a tile or a stage."""
     from rust_inference_b200 import ops
+    monkeypatch.setattr(ops, "SKINNY_MAX_TOKENS", 16)          # the kernel's whole range of tokens
     M, N, K = shape                      # N rows of gate and up together
     rng = np.random.default_rng(N)
     x = rnd(rng, M, K, dtype="bfloat16")
@@ -169,7 +172,7 @@ def test_linear_swiglu_fused(shape):
 
 
 @pytest.mark.parametrize("shape", [(17, 100, 72), (40, 257, 1544), (64, 4096, 4096), (128, 1000, 12288), (65, 24576, 512),
-                                   (33, 130, 8)])
+                                   (33, 130, 8), (13, 4096, 1544), (16, 264, 4096)])
 def test_linear_stream_tc(shape):
     """The tcgen05 weight-streaming linear (up to 128 tokens): widths and depths that end inside a tile or a
     stage, splits of K over a cluster with the partial tiles added in a fixed order, twice in a row."""
@@ -186,9 +189,9 @@ def test_linear_stream_tc(shape):
     assert torch.equal(again, full)
     assert int(ops.error_flag("cuda").item()) == 0
     # a token's result does not depend on the tokens around it (as long as the kernel is the same)
-    if M > 17:
-        fewer = ops.linear_stream_tc(dev(x[:17], torch.bfloat16), wd, out_dtype=torch.float32)
-        assert torch.equal(fewer, full[:17])
+    if M > 13:
+        fewer = ops.linear_stream_tc(dev(x[:13], torch.bfloat16), wd, out_dtype=torch.float32)
+        assert torch.equal(fewer, full[:13])
 
 
 def test_linear_takes_the_streaming_kernel_for_wide_outputs(monkeypatch):

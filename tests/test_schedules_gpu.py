@@ -45,7 +45,7 @@ def tiny_d(tmp_path_factory):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("seqs,stream_tc", [(24, False), (64, False), (64, True)])
+@pytest.mark.parametrize("seqs,stream_tc", [(14, False), (24, False), (64, False), (64, True)])
 def test_many_sequences_decode_together_tiny(tmp_path, tiny_d, dtype, seqs, stream_tc):
     if stream_tc and dtype == "float32":
         pytest.skip("the tcgen05 weight-streaming linear is a bfloat16 kernel")
@@ -86,7 +86,7 @@ def large_8b(tmp_path_factory):
     shutil.rmtree(d, ignore_errors=True)
 
 
-@pytest.mark.parametrize("dtype,seqs,wide", [("float32", 24, None), ("bfloat16", 24, None), ("bfloat16", 64, None),
+@pytest.mark.parametrize("dtype,seqs,wide", [("float32", 24, None), ("bfloat16", 24, None), ("bfloat16", 15, None), ("bfloat16", 64, None),
                                              ("bfloat16", 64, 2000), ("float32", 64, None)])
 def test_many_sequences_decode_together_at_8b_layer_shapes(tmp_path, monkeypatch, large_8b, dtype, seqs, wide):
     """Two layers of Qwen3-8B's shapes (width 4096, 32 heads over 8 kv heads of 128, feed-forward 12288) and a
