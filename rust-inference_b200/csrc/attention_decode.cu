@@ -842,15 +842,20 @@ extern "C" int ri_attention_decode(const void* q, const void* k_pool, const void
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
             if (sms <= 0) sms = 148;
         }
-        // Pages per item: the fewest (whole chunks of 128 keys) with which the items fill the grid's warps
-        // at most once; a batch too large for that takes items of 16 pages.
+        // Pages per item (whole chunks of 128 keys): the number with which the warp that gets the most items has the
+        // fewest pages to walk, if every sequence were as long as the scratch memory allows; among equals the
+        // largest (fewer items to open).  64 sequences of 4,096 keys and 8 kv heads on 1,184 warps: items of 8
+        // pages (6.9 items a warp, at most 7: 56 pages where 55.4 is the mean), not of 16 (3.5 items, at most 4: 64).
         const int max_pages = max_chunks * (AD_CHUNK / AD_PAGE);
         const long long workers = (long long)sms * ADS_WARPS;
-        int chunk_pages = 16;
+        int chunk_pages = AD_CHUNK / AD_PAGE;
+        long long fewest = -1;
         for (int c = AD_CHUNK / AD_PAGE; c <= 32; c += AD_CHUNK / AD_PAGE) {
-            if ((long long)seqs * KV * ((max_pages + c - 1) / c) <= workers) {
+            const long long items = (long long)seqs * KV * ((max_pages + c - 1) / c);
+            const long long walk = ((items + workers - 1) / workers) * c;
+            if (fewest < 0 || walk <= fewest) {
+                fewest = walk;
                 chunk_pages = c;
-                break;
             }
         }
         RI_REQUIRE((long long)num_pages * KV * AD_PAGE < (1ll << 31), "attention_decode: a pool of %d pages", num_pages);
