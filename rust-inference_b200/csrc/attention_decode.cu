@@ -21,10 +21,12 @@
 // Each K/V byte is read from memory once for all heads of the group.
 //
 // Which keys a chunk holds depends on the sequence's own length only (chunk c is
-// keys 128c .. 128c+127), so a sequence's result does not depend on the batch.
+// keys 128c .. 128c+127), so with this kernel a sequence's result does not depend on
+// the batch (with the streaming kernel it does, in its last bits: see there).
 //
-// Scratch memory: o_part [seqs, H, max_chunks, Dh] and ml_part [seqs, H,
-// max_chunks, 2], float32, given by the caller.
+// Scratch memory: o_part [seqs, H, parts, Dh] and ml_part [seqs, H, parts, 2], float32,
+// given by the caller, parts = ri_attention_decode_parts(max_chunks); this kernel uses
+// the start of them, as [seqs, H, max_chunks, ...].
 //
 // Every wait on an mbarrier is bounded; if it runs out the kernel reports error 5
 // through the error word and goes on (its output is then wrong, the context is not).
@@ -285,26 +287,33 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
 // ---------------------------------------------------------------------------------------------
 // The streaming kernel, for groups of at most 16 query heads and head sizes of 64 and 128.
 //
-// One block per SM, ADS_WARPS warps, and every warp works alone: it walks the items (run of
-// pages, sequence, kv head) w, w + W, w + 2W, ... (W warps in the grid) and, inside an item,
-// the pages in rising order with the running maximum, sum and output of a flash decoder in
-// its registers, so nothing is combined across warps and the block never synchronises.
+// One block per SM, ADS_WARPS warps, and every warp works alone.  The pages that the step's
+// queries see, of all sequences and kv heads, form one list (sequence by sequence, kv head by
+// kv head, pages in rising order); it is cut into as many runs as the grid has warps, of
+// lengths that differ by one page at most (and of at least ADS_MIN_PAGES pages), and a warp
+// walks its run with the running maximum, sum and output of a flash decoder in its
+// registers, so nothing is combined across warps, and with up to 32 sequences (their
+// lengths in the warp's lanes) the block never synchronises; with more it does so once, at
+// its start, for the table of the sequences' page counts in shared memory.  Every warp of
+// the grid so has the same number of pages to read, whatever the batch and the lengths are.
 // The keys and the values of a page are two tiles of a stream that runs through the warp's
 // own ring of ADS_SLOTS shared-memory slots: one lane starts a TMA tensor copy
 // (cp.async.bulk.tensor.2d, 128-byte swizzle, completion on the slot's mbarrier) per 64
 // head elements of the tile, the warp waits for the oldest tile, reads it with ldmatrix
 // (keys) or ldmatrix.trans (values) for mma.sync m16n8k16, and refills the slot with the
-// tile ADS_SLOTS ahead - which may belong to the warp's next item, so the copies never stop
-// between items.  A tile is one or two instructions to start, where a copy per row costs
-// the warp a loop over its lanes; the swizzle makes the ldmatrix reads free of bank
+// tile ADS_SLOTS ahead - which may belong to the next (sequence, kv head) of the run, so
+// the copies never stop.  A tile is one or two instructions to start, where a copy per row
+// costs the warp a loop over its lanes; the swizzle makes the ldmatrix reads free of bank
 // conflicts without padding.  With three slots of 8 KB for each of eight warps an SM has
 // 192 KB on its way at all times.
 //
-// An item is a run of `chunk_pages` pages (a multiple of four), chosen by the launcher from
-// the batch's size so that the items fill the grid's warps once (see ri_attention_decode).
-// Whatever that number is, the warp writes one partial result for every 128 keys (four
-// pages, starting afresh after each), in the layout of the kernel above, and the same merge
-// kernel adds them: the bits of a sequence's result do not depend on the batch it is in.
+// Where a run ends inside a (sequence, kv head), or passes from one to the next, the warp
+// writes a partial result (maximum, sum, unnormalised output): piece i of a (sequence, kv
+// head) comes from the i-th warp whose run touches it, at place i of that head's scratch
+// rows (at most 2 max_chunks + 1 pieces, since a run has at least two pages), and the merge
+// kernel, which computes the same cut from the same lengths, adds the pieces in that order.
+// The cut depends on the whole batch: a sequence's result is the same from run to run, but
+// its last bits may differ between batches (the pieces are other pieces).
 //
 // The running maximum is only raised when a page's maximum exceeds it by more than 2^8
 // (the weights stay below 2^8, exact in float32 and as good as any in bfloat16), which
@@ -321,18 +330,23 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
 #define ADS_SLOTS_RAW ((208 * 1024) / (ADS_WARPS * ADS_SLOT_BYTES))
 #define ADS_SLOTS (ADS_SLOTS_RAW > 6 ? 6 : ADS_SLOTS_RAW)
 #endif
-// a small batch has fewer items than the grid has warps: then fewer warps per block (four, or two), each with
-// a deeper ring, so that more of an item's tiles are on their way at once
+// a small batch has fewer runs of two pages than the grid has warps: then fewer warps per block (four, or two),
+// each with a deeper ring, so that more of a run's tiles are on their way at once
 #define ADS_SLOTS_FOR(warps) ((208 * 1024) / ((warps) * ADS_SLOT_BYTES) > 12 ? 12 : (208 * 1024) / ((warps) * ADS_SLOT_BYTES))
-#define ADS_SMEM_BYTES(warps, slots) ((size_t)(warps) * (slots) * ADS_SLOT_BYTES + (size_t)(warps) * (slots) * 8 + 1024)
+#define ADS_MAX_SEQS 1024                              // sequences of a step (their page counts stand in shared memory)
+#define ADS_MIN_PAGES 2                                // a warp's run has at least this many pages
+#define ADS_PARTS(max_chunks) (2 * (max_chunks) + 1)   // pieces of a (sequence, kv head) at most
+#define ADS_SMEM_BYTES(warps, slots) ((size_t)(warps) * (slots) * ADS_SLOT_BYTES + (size_t)(warps) * (slots) * 8 + (ADS_MAX_SEQS + 1) * 4 + 1024)
 #define ADS_LAZY 8.0f                                  // log2 of how far a page's maximum may exceed the running one
 
-// where a warp stands in its list of pages
+// where a warp stands in its run of pages
 struct StreamCursor {
-    int item;          // index of the item, or >= n_items when the list is at its end
-    int b, kvh, chunk;
+    int rem;           // pages of the run after the piece at hand
+    int b, kvh;        // the piece at hand: of which sequence and kv head
+    int seg, at;       // where the list has this (sequence, kv head), and where this piece of it
+    int part;          // which of the (sequence, kv head)'s pieces it is (the cursor that computes keeps this)
     int len, first_key;
-    int p, p_end;      // the page (index within the sequence) and the end of the item's pages
+    int p, p_end;      // the page (index within the sequence) and the end of the piece
     int ids_base;      // lane l holds the pool index of page ids_base + l of the sequence
     int id_lane;
     int slot_row;      // the sequence's row of the page table
@@ -342,8 +356,73 @@ struct StreamArgs {
     const int* page_table;
     const int* seq_slot;
     const int* seq_len;
-    int seqs, KV, mpps, num_pages, n_items, chunk_pages, window, stride, max_pages;
+    int seqs, KV, mpps, num_pages, window, max_pages, parts;
     int* err;
+};
+
+__device__ __forceinline__ int warp_sum_int(int v) { return __reduce_add_sync(0xffffffffu, v); }
+
+// the pages that the query of a sequence of `len` keys sees: [p_first, p_first + n)
+__device__ __forceinline__ int stream_visible(int len, int window, int max_pages, int& first_key, int& p_first) {
+    first_key = (window > 0 && len - window > 0) ? len - window : 0;
+    p_first = first_key / AD_PAGE;
+    int p_last = (len + AD_PAGE - 1) / AD_PAGE;
+    p_last = p_last < max_pages ? p_last : max_pages;     // no partial result has a place beyond (the merge reports it)
+    return p_last > p_first ? p_last - p_first : 0;
+}
+// How a list of `total` pages is cut into runs for `workers` warps: the first `more` runs have len + 1 pages, the
+// others len, which together is the whole list; a list too short for runs of ADS_MIN_PAGES pages everywhere
+// is cut into runs of that length, as many as it takes.
+struct StreamCut {
+    int len, more;
+    __device__ __forceinline__ StreamCut(int total, int workers) {
+        len = total / workers;
+        more = total - len * workers;
+        if (len < ADS_MIN_PAGES) {
+            len = ADS_MIN_PAGES;
+            more = 0;
+        }
+    }
+    __device__ __forceinline__ int start(int w) const { return w * len + (w < more ? w : more); }     // of run w
+    __device__ __forceinline__ int pages(int w) const { return len + (w < more ? 1 : 0); }
+    __device__ __forceinline__ int owner(int u) const {                                                // the run that holds place u
+        const int longs = more * (len + 1);
+        return u < longs ? u / (len + 1) : more + (u - longs) / len;
+    }
+};
+
+// The step's sequences as a warp's cursors see them: lengths, rows of the page table and the running count of
+// visible pages.  SMALL (at most 32 sequences): lane b of the warp holds sequence b's, read once at the kernel's
+// start and passed around by shuffles (every call is made by the whole warp); else the counts stand in shared
+// memory and the rest is read from the step's tables.
+template <bool SMALL>
+struct SeqTable {
+    const int* pre;                        // !SMALL: pre[b] = visible pages of the sequences before b, pre[seqs] = all
+    const int* seq_len;
+    const int* seq_slot;
+    int seqs;
+    int lane_through, lane_len, lane_slot; // SMALL
+    __device__ __forceinline__ int through(int b) const {          // visible pages of sequences 0..b
+        return SMALL ? __shfl_sync(0xffffffffu, lane_through, b) : pre[b + 1];
+    }
+    __device__ __forceinline__ int before(int b) const {
+        if (!SMALL) return pre[b];
+        const int v = __shfl_sync(0xffffffffu, lane_through, (b + 31) & 31);
+        return b == 0 ? 0 : v;
+    }
+    __device__ __forceinline__ int all() const { return through(seqs - 1); }
+    __device__ __forceinline__ int len(int b) const { return SMALL ? __shfl_sync(0xffffffffu, lane_len, b) : seq_len[b]; }
+    __device__ __forceinline__ int slot(int b) const { return SMALL ? __shfl_sync(0xffffffffu, lane_slot, b) : seq_slot[b]; }
+    // the sequence b with KV before(b) <= u < KV through(b), for a place u of the list
+    __device__ __forceinline__ int find(int u, int KV) const {
+        if (SMALL) return __popc(__ballot_sync(0xffffffffu, KV * lane_through <= u));     // lanes past the last sequence hold all()
+        int lo = 0, hi = seqs;
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (KV * pre[mid] <= u) lo = mid; else hi = mid;
+        }
+        return lo;
+    }
 };
 
 __device__ __forceinline__ void stream_load_ids(StreamCursor& c, const StreamArgs& a, int lane) {
@@ -357,42 +436,51 @@ __device__ __forceinline__ void stream_load_ids(StreamCursor& c, const StreamArg
     c.id_lane = id;
 }
 
-// moves to the first item at or after c.item that has a visible page; false at the end of the list.
+// the piece of (c.b, c.kvh) that starts `off` pages into its visible pages and has at most `rem` pages;
 // IDS: the cursor is the one that copies, so it needs the pages' places in the pool.
-template <bool IDS>
-__device__ __forceinline__ bool stream_open(StreamCursor& c, const StreamArgs& a, int lane) {
-    for (; c.item < a.n_items; c.item += a.stride) {
-        c.kvh = c.item % a.KV;
-        int r = c.item / a.KV;
-        c.b = r % a.seqs;
-        c.chunk = r / a.seqs;
-        c.len = a.seq_len[c.b];
-        c.first_key = (a.window > 0 && c.len - a.window > 0) ? c.len - a.window : 0;
-        int p_lo = c.chunk * a.chunk_pages, p_hi = p_lo + a.chunk_pages;
-        int p_first = c.first_key / AD_PAGE, p_last = (c.len + AD_PAGE - 1) / AD_PAGE;
-        p_last = p_last < a.max_pages ? p_last : a.max_pages;     // no partial result has a place beyond (the merge reports it)
-        c.p = p_lo > p_first ? p_lo : p_first;
-        c.p_end = p_hi < p_last ? p_hi : p_last;
-        if (c.p < c.p_end) {
-            if (IDS) {
-                c.slot_row = a.seq_slot[c.b];
-                stream_load_ids(c, a, lane);
-            }
-            return true;
-        }
+template <bool IDS, bool SMALL>
+__device__ __forceinline__ void stream_piece(StreamCursor& c, const StreamArgs& a, const SeqTable<SMALL>& t, int off, int rem, const StreamCut& cut, int lane) {
+    int p_first;
+    c.len = t.len(c.b);
+    const int n = stream_visible(c.len, a.window, a.max_pages, c.first_key, p_first);
+    c.p = p_first + off;
+    c.p_end = min(p_first + n, c.p + rem);
+    c.rem = rem - (c.p_end - c.p);
+    c.seg = a.KV * t.before(c.b) + c.kvh * n;
+    c.at = c.seg + off;
+    if (IDS) {
+        c.slot_row = t.slot(c.b);
+        stream_load_ids(c, a, lane);
+    } else {
+        c.part = cut.owner(c.at) - cut.owner(c.seg);         // (divisions: kept off the path to the first copies)
     }
-    return false;
 }
 
-// the next page of the list; false at its end
-template <bool IDS>
-__device__ __forceinline__ bool stream_next(StreamCursor& c, const StreamArgs& a, int lane) {
+// the first piece of the run [u, u + rem) of the list; false if the run is empty
+template <bool IDS, bool SMALL>
+__device__ __forceinline__ bool stream_seek(StreamCursor& c, const StreamArgs& a, const SeqTable<SMALL>& t, int u, int rem, const StreamCut& cut, int lane) {
+    if (rem <= 0) return false;
+    c.b = t.find(u, a.KV);
+    const int r = u - a.KV * t.before(c.b), n = t.through(c.b) - t.before(c.b);
+    c.kvh = r / n;
+    stream_piece<IDS>(c, a, t, r - c.kvh * n, rem, cut, lane);
+    return true;
+}
+
+// the next page of the run; false at its end
+template <bool IDS, bool SMALL>
+__device__ __forceinline__ bool stream_next(StreamCursor& c, const StreamArgs& a, const SeqTable<SMALL>& t, const StreamCut& cut, int lane) {
     if (++c.p < c.p_end) {
         if (IDS && c.p - c.ids_base == 32) stream_load_ids(c, a, lane);
         return true;
     }
-    c.item += a.stride;
-    return stream_open<IDS>(c, a, lane);
+    if (c.rem <= 0) return false;
+    if (++c.kvh == a.KV) {                                    // pages are left, so a sequence with pages follows
+        c.kvh = 0;
+        do c.b++; while (c.b + 1 < a.seqs && t.through(c.b) == t.before(c.b));
+    }
+    stream_piece<IDS>(c, a, t, 0, c.rem, cut, lane);
+    return true;
 }
 
 // one box of a tensor map into shared memory: x in elements (a multiple of 64 here, so of 16 bytes), y the row
@@ -407,11 +495,11 @@ __device__ __forceinline__ float ex2_fast(float x) {
 }
 
 #if ADS_OK
-template <int WARPS, int SLOTS>
+template <int WARPS, int SLOTS, bool SMALL>
 __global__ void __launch_bounds__(32 * WARPS, 1)
 attention_decode_stream_kernel(const bf16* __restrict__ q, const __grid_constant__ CUtensorMap map_k,
                                const __grid_constant__ CUtensorMap map_v, float* __restrict__ o_part,
-                               float* __restrict__ ml_part, StreamArgs a, int H, int max_chunks, float scale_log2) {
+                               float* __restrict__ ml_part, StreamArgs a, int H, float scale_log2) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int quad = lane >> 2, qc = lane & 3;
@@ -420,7 +508,20 @@ attention_decode_stream_kernel(const bf16* __restrict__ q, const __grid_constant
     unsigned char* ring = base + (size_t)warp * SLOTS * ADS_SLOT_BYTES;
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(base + (size_t)WARPS * SLOTS * ADS_SLOT_BYTES)
                                + warp * SLOTS;
+    int* pre = reinterpret_cast<int*>(base + (size_t)WARPS * SLOTS * ADS_SLOT_BYTES + (size_t)WARPS * SLOTS * 8);
     const int G = H / a.KV;
+    // the sequences' lengths and rows of the page table are tables of the step, not the work of the kernel before;
+    // they are asked for first of all, so that they are on their way while the barriers are set up
+    SeqTable<SMALL> tab;
+    tab.pre = pre;
+    tab.seq_len = a.seq_len;
+    tab.seq_slot = a.seq_slot;
+    tab.seqs = a.seqs;
+    tab.lane_through = tab.lane_len = tab.lane_slot = 0;
+    if (SMALL && lane < a.seqs) {
+        tab.lane_len = a.seq_len[lane];
+        tab.lane_slot = a.seq_slot[lane];
+    }
     if (lane == 0) {
         asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_v) : "memory");
@@ -429,11 +530,45 @@ attention_decode_stream_kernel(const bf16* __restrict__ q, const __grid_constant
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncwarp();
+    if (SMALL) {
+        int fk, pf;
+        int v = lane < a.seqs ? stream_visible(tab.lane_len, a.window, a.max_pages, fk, pf) : 0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, v, o);
+            if (lane >= o) v += up;
+        }
+        tab.lane_through = v;
+    } else {
+        for (int b = threadIdx.x; b < a.seqs; b += 32 * WARPS) {
+            int fk, pf;
+            pre[b + 1] = stream_visible(a.seq_len[b], a.window, a.max_pages, fk, pf);
+        }
+        __syncthreads();
+        if (warp == 0) {
+            int carry = 0;
+            for (int b0 = 0; b0 < a.seqs; b0 += 32) {
+                int v = b0 + lane < a.seqs ? pre[b0 + lane + 1] : 0;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int up = __shfl_up_sync(0xffffffffu, v, o);
+                    if (lane >= o) v += up;
+                }
+                if (b0 + lane < a.seqs) pre[b0 + lane + 1] = carry + v;
+                carry += __shfl_sync(0xffffffffu, v, 31);
+            }
+            if (lane == 0) pre[0] = 0;
+        }
+        __syncthreads();
+    }
+    const int total = a.KV * tab.all(), workers = (int)gridDim.x * WARPS;
+    const StreamCut cut(total, workers);
+    const int my_run = blockIdx.x + gridDim.x * warp;        // neighbouring runs go to different SMs
+    const int u0 = cut.start(my_run);
 
     StreamCursor ci, cc;                  // the page whose tiles are copied next, the page that is worked on
-    ci.item = blockIdx.x + gridDim.x * warp;
-    bool more = stream_open<true>(ci, a, lane);
-    cc = ci;
+    bool more = u0 < total && stream_seek<true>(ci, a, tab, u0, min(cut.pages(my_run), total - u0), cut, lane);
+    cc = ci;                              // (its part is computed below, once the first copies are on their way)
     bool live = more;
     int issue_v = 0;                      // 0: the keys of ci's page come next, 1: its values
     int in_flight = 0, slot_i = 0, slot_c = 0;
@@ -453,7 +588,7 @@ attention_decode_stream_kernel(const bf16* __restrict__ q, const __grid_constant
         }
         slot_i = slot_i + 1 == SLOTS ? 0 : slot_i + 1;
         in_flight++;
-        if (issue_v) more = stream_next<true>(ci, a, lane);
+        if (issue_v) more = stream_next<true>(ci, a, tab, cut, lane);
         issue_v ^= 1;
     };
     auto wait_tile = [&]() {
@@ -476,6 +611,7 @@ attention_decode_stream_kernel(const bf16* __restrict__ q, const __grid_constant
     while (more && in_flight < SLOTS && (ci.p + 1) * AD_PAGE < ci.len) issue();
     // every block of this grid is on an SM from the start (one per SM), so the kernel after it (the merge: small
     // blocks that read the lengths and then wait) may come in at once
+    if (live) cc.part = cut.owner(cc.at) - cut.owner(cc.seg);
     pdl_trigger();
     pdl_wait();
 #pragma unroll 1
@@ -484,14 +620,14 @@ attention_decode_stream_kernel(const bf16* __restrict__ q, const __grid_constant
     float m_run[2] = {-FLT_MAX, -FLT_MAX}, l_run[2] = {0.0f, 0.0f};
     float o[AD_DH / 8][4];
     unsigned qf[AD_DH / 16][4];
-    bool fresh = true, new_item = true;   // the next page is the first of a chunk of 128 keys, of an item
+    bool fresh = true, new_item = true;   // the next page is the first of a piece (of another sequence or kv head)
     // this lane's corner of the 8x8 matrices that ldmatrix reads (rows of 128 bytes, 16-byte pieces swizzled by the row)
     const int k_row = (lane & 7) + ((lane >> 4) & 1) * 8, k_piece = (lane >> 3) & 1;
     const int v_row = (lane & 7) + ((lane >> 3) & 1) * 8, v_piece = lane >> 4;
 #pragma unroll 1
     while (live) {
         if (new_item) {
-            // ---- the item's query fragments: rows quad and quad + 8 of the group ---------------------------
+            // ---- the piece's query fragments: rows quad and quad + 8 of the group --------------------------
             const bf16* pa = q + ((size_t)cc.b * H + cc.kvh * G + (quad < G ? quad : 0)) * AD_DH + qc * 2;
             const bf16* pb = q + ((size_t)cc.b * H + cc.kvh * G + (quad + 8 < G ? quad + 8 : 0)) * AD_DH + qc * 2;
 #pragma unroll
@@ -613,17 +749,15 @@ attention_decode_stream_kernel(const bf16* __restrict__ q, const __grid_constant
             if (rows < AD_PAGE) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the zeros, before the next copy into the slot
         }
         release_tile();
-        // ---- the last page of a chunk of 128 keys: write the chunk's partial result ----------------------
-        const bool item_ends = cc.p + 1 == cc.p_end;
-        if (item_ends || (cc.p + 1) % (AD_CHUNK / AD_PAGE) == 0) {
-            const int chunk = cc.p / (AD_CHUNK / AD_PAGE);
+        // ---- the last page of a piece: write its partial result ------------------------------------------
+        if (cc.p + 1 == cc.p_end) {
 #pragma unroll
             for (int r = 0; r < 2; r++) {
                 l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
                 l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
                 const int row = quad + r * 8;
                 if (row < G) {
-                    const size_t at = ((size_t)cc.b * H + cc.kvh * G + row) * max_chunks + chunk;
+                    const size_t at = ((size_t)cc.b * H + cc.kvh * G + row) * a.parts + cc.part;
                     float* dst = o_part + at * AD_DH + qc * 2;
 #pragma unroll
                     for (int t = 0; t < AD_DH / 8; t++) *(float2*)(dst + t * 8) = make_float2(o[t][r * 2], o[t][r * 2 + 1]);
@@ -631,9 +765,9 @@ attention_decode_stream_kernel(const bf16* __restrict__ q, const __grid_constant
                 }
             }
             fresh = true;
-            new_item = item_ends;
+            new_item = true;              // the next piece is of another sequence or kv head
         }
-        live = stream_next<false>(cc, a, lane);
+        live = stream_next<false>(cc, a, tab, cut, lane);
         if (dead) break;
     }
 }
@@ -666,33 +800,81 @@ static int pool_tensor_map(CUtensorMap* map, const void* pool, long long rows) {
 }
 #endif  // ADS_OK
 
-// out[b, h, :] = the partial results of the visible chunks added up.  The block's four warps each take a
-// quarter of the chunks (in rising order, four head elements per lane), then the four sums are added in
-// warp order: the order of the additions depends on the sequence's length only.
+// how the streaming kernel cut its list of pages (0 workers: the partial results are those of chunks of 128 keys)
+struct MergeCut {
+    int workers, seqs, KV, parts;
+};
+
+// out[b, h, :] = the partial results of the head's chunks (or pieces) added up.  The block's four warps each take
+// a quarter of them (in rising order, four head elements per lane), then the four sums are added in
+// warp order: the order of the additions depends on the partial results' number only.
 __global__ void __launch_bounds__(AD_MERGE_THREADS)
 attention_decode_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
                               bf16* __restrict__ out, const int* __restrict__ seq_len, int H, int max_chunks,
-                              int window, int* __restrict__ err) {
+                              int window, MergeCut cut, int* __restrict__ err) {
     constexpr int MW = AD_MERGE_THREADS / 32;            // warps
     constexpr int PER = (AD_DH + 127) / 128;             // float4 per lane
     const int h = blockIdx.x, b = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __shared__ float s_w[AD_MERGE_TILE], s_red[MW], s_l[MW];
+    __shared__ int s_cnt[2][MW];
     pdl_trigger();
     const int len = seq_len[b];                          // a table of the step, not the work of the kernel before
     const int first_key = (window > 0 && len - window > 0) ? len - window : 0;
     int c_lo = first_key / AD_CHUNK, c_hi = (len + AD_CHUNK - 1) / AD_CHUNK;           // [c_lo, c_hi)
     const bool too_long = c_hi > max_chunks;
+    int stride = max_chunks;                             // partial results a head has room for
     if (too_long) {
         // the caller's scratch memory has no partial results for the keys past max_chunks * 128: they are left
         // out (nothing is read past the sequence's rows) and the mistake is reported
         c_hi = max_chunks;
         c_lo = c_lo < c_hi ? c_lo : c_hi;
     }
+#if ADS_OK
+    if (cut.workers > 0) {
+        // the streaming kernel's cut, from the same lengths: the pages before this sequence's and all pages
+        const int max_pages = max_chunks * (AD_CHUNK / AD_PAGE);
+        int below = 0, all = 0;
+        if (cut.seqs <= 32) {
+            // every warp for itself: a lane per sequence, two additions across the warp
+            int f2, p2;
+            const int n = lane < cut.seqs ? stream_visible(seq_len[lane], window, max_pages, f2, p2) : 0;
+            all = warp_sum_int(n);
+            below = warp_sum_int(lane < b ? n : 0);
+        } else {
+            for (int s = threadIdx.x; s < cut.seqs; s += AD_MERGE_THREADS) {
+                int f2, p2;
+                const int n = stream_visible(seq_len[s], window, max_pages, f2, p2);
+                all += n;
+                below += s < b ? n : 0;
+            }
+            below = warp_sum_int(below);
+            all = warp_sum_int(all);
+            if (lane == 0) {
+                s_cnt[0][warp] = below;
+                s_cnt[1][warp] = all;
+            }
+            __syncthreads();
+            below = all = 0;
+#pragma unroll
+            for (int w = 0; w < MW; w++) {
+                below += s_cnt[0][w];
+                all += s_cnt[1][w];
+            }
+        }
+        int f2, p2;
+        const int n = stream_visible(len, window, max_pages, f2, p2);
+        const StreamCut runs(cut.KV * all, cut.workers);
+        const int seg = cut.KV * below + (h / (H / cut.KV)) * n;
+        c_lo = 0;
+        c_hi = n > 0 ? runs.owner(seg + n - 1) - runs.owner(seg) + 1 : 0;
+        stride = cut.parts;
+    }
+#endif
     pdl_wait();
     if (too_long && threadIdx.x == 0) atomicExch(err, 7);
-    const float* ml = ml_part + ((size_t)b * H + h) * max_chunks * 2;
-    const float* op = o_part + ((size_t)b * H + h) * max_chunks * AD_DH;
-    __shared__ float s_w[AD_MERGE_TILE], s_red[MW], s_l[MW];
+    const float* ml = ml_part + ((size_t)b * H + h) * stride * 2;
+    const float* op = o_part + ((size_t)b * H + h) * stride * AD_DH;
     __shared__ __align__(16) float s_acc[MW][AD_DH];
     // The partial outputs of this warp's first eight chunks are asked for at once, before the maxima (on which
     // their weights depend) are known: the kernel is a chain of trips to L2, and this takes one out of it.
@@ -802,26 +984,40 @@ static int decode_configure(int G, size_t* smem_out) {
 }
 
 #if ADS_OK
-template <int WARPS, int SLOTS>
-static int launch_stream(int blocks, cudaStream_t stream, const bf16* q, const CUtensorMap& map_k, const CUtensorMap& map_v,
-                         float* o_part, float* ml_part, StreamArgs a, int H, int max_chunks, float scale_log2) {
+template <int WARPS, int SLOTS, bool SMALL>
+static int launch_stream_for(int blocks, cudaStream_t stream, const bf16* q, const CUtensorMap& map_k, const CUtensorMap& map_v,
+                         float* o_part, float* ml_part, StreamArgs a, int H, float scale_log2) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_stream_kernel<WARPS, SLOTS>,
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_stream_kernel<WARPS, SLOTS, SMALL>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ADS_SMEM_BYTES(WARPS, SLOTS));
         if (e != cudaSuccess) RI_FAIL((int)e, "attention_decode: shared memory limit: %s", cudaGetErrorString(e));
         configured = true;
     }
-    a.stride = blocks * WARPS;
-    ri_launch_pdl(attention_decode_stream_kernel<WARPS, SLOTS>, dim3(blocks), dim3(32 * WARPS), ADS_SMEM_BYTES(WARPS, SLOTS),
-                  stream, q, map_k, map_v, o_part, ml_part, a, H, max_chunks, scale_log2);
+    ri_launch_pdl(attention_decode_stream_kernel<WARPS, SLOTS, SMALL>, dim3(blocks), dim3(32 * WARPS), ADS_SMEM_BYTES(WARPS, SLOTS),
+                  stream, q, map_k, map_v, o_part, ml_part, a, H, scale_log2);
     RI_CHECK_LAUNCH("attention_decode_stream");
     return 0;
 }
+template <int WARPS, int SLOTS>
+static int launch_stream(int blocks, cudaStream_t stream, const bf16* q, const CUtensorMap& map_k, const CUtensorMap& map_v,
+                         float* o_part, float* ml_part, StreamArgs a, int H, float scale_log2) {
+    return a.seqs <= 32 ? launch_stream_for<WARPS, SLOTS, true>(blocks, stream, q, map_k, map_v, o_part, ml_part, a, H, scale_log2)
+                        : launch_stream_for<WARPS, SLOTS, false>(blocks, stream, q, map_k, map_v, o_part, ml_part, a, H, scale_log2);
+}
 #endif
 
-// q, out [seqs, H, Dh] bf16; o_part [seqs, H, max_chunks, Dh] f32; ml_part [seqs, H, max_chunks, 2] f32.
-// max_chunks * 128 must cover the longest sequence of the step.
+// how many partial results per (sequence, head) the scratch memory of ri_attention_decode must have room for
+extern "C" int ri_attention_decode_parts(int max_chunks) {
+#if ADS_OK && !defined(AD_NO_STREAM)
+    return ADS_PARTS(max_chunks);
+#else
+    return max_chunks;
+#endif
+}
+
+// q, out [seqs, H, Dh] bf16; o_part [seqs, H, parts, Dh] f32; ml_part [seqs, H, parts, 2] f32 with
+// parts = ri_attention_decode_parts(max_chunks).  max_chunks * 128 must cover the longest sequence of the step.
 extern "C" int ri_attention_decode(const void* q, const void* k_pool, const void* v_pool, void* out, float* o_part,
                                    float* ml_part, const int* page_table, const int* seq_slot, const int* seq_len,
                                    int seqs, int H, int KV, int Dh, int mpps, int page_size, int num_pages,
@@ -834,7 +1030,7 @@ extern "C" int ri_attention_decode(const void* q, const void* k_pool, const void
     RI_REQUIRE(window >= 0, "attention_decode: negative window");
     RI_REQUIRE((((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0, "attention_decode: q and the pools must be 16-byte aligned");
 #if ADS_OK && !defined(AD_NO_STREAM)
-    if (H / KV <= AD_ROWS && scale > 0.0f) {
+    if (H / KV <= AD_ROWS && scale > 0.0f && seqs <= ADS_MAX_SEQS) {
         static int sms = 0;
         if (!sms) {
             int dev = 0;
@@ -842,22 +1038,8 @@ extern "C" int ri_attention_decode(const void* q, const void* k_pool, const void
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
             if (sms <= 0) sms = 148;
         }
-        // Pages per item (whole chunks of 128 keys): the number with which the warp that gets the most items has the
-        // fewest pages to walk, if every sequence were as long as the scratch memory allows; among equals the
-        // largest (fewer items to open).  64 sequences of 4,096 keys and 8 kv heads on 1,184 warps: items of 8
-        // pages (6.9 items a warp, at most 7: 56 pages where 55.4 is the mean), not of 16 (3.5 items, at most 4: 64).
         const int max_pages = max_chunks * (AD_CHUNK / AD_PAGE);
-        const long long workers = (long long)sms * ADS_WARPS;
-        int chunk_pages = AD_CHUNK / AD_PAGE;
-        long long fewest = -1;
-        for (int c = AD_CHUNK / AD_PAGE; c <= 32; c += AD_CHUNK / AD_PAGE) {
-            const long long items = (long long)seqs * KV * ((max_pages + c - 1) / c);
-            const long long walk = ((items + workers - 1) / workers) * c;
-            if (fewest < 0 || walk <= fewest) {
-                fewest = walk;
-                chunk_pages = c;
-            }
-        }
+        RI_REQUIRE((long long)seqs * KV * max_pages < (1ll << 30), "attention_decode: %d sequences of up to %d pages", seqs, max_pages);
         RI_REQUIRE((long long)num_pages * KV * AD_PAGE < (1ll << 31), "attention_decode: a pool of %d pages", num_pages);
         CUtensorMap map_k, map_v;
         int rc_map = pool_tensor_map(&map_k, k_pool, (long long)num_pages * KV * AD_PAGE);
@@ -872,26 +1054,31 @@ extern "C" int ri_attention_decode(const void* q, const void* k_pool, const void
         a.KV = KV;
         a.mpps = mpps;
         a.num_pages = num_pages;
-        long long n_items = (long long)seqs * KV * ((max_pages + chunk_pages - 1) / chunk_pages);
-        RI_REQUIRE(n_items < (1ll << 30), "attention_decode: %lld items", n_items);
-        a.n_items = (int)n_items;
-        a.chunk_pages = chunk_pages;
         a.max_pages = max_pages;
+        a.parts = ADS_PARTS(max_chunks);
         a.window = window;
         a.err = err_flag;
-        const long long smallest = (long long)seqs * KV * ((max_pages + 3) / 4);       // items of four pages
-        const int blocks = n_items < sms ? (int)n_items : sms;      // warp w of block x starts at item x + blocks * w
+        // the most runs of ADS_MIN_PAGES pages that the step can have: fewer blocks than SMs, or fewer warps per
+        // block (each with a deeper ring), when they do not fill the grid
+        const long long runs = ((long long)seqs * KV * max_pages + ADS_MIN_PAGES - 1) / ADS_MIN_PAGES;
+        const int warps = runs <= (long long)sms * 2 ? 2 : (runs <= (long long)sms * 4 ? 4 : ADS_WARPS);
+        const int blocks = (int)((runs + warps - 1) / warps < sms ? (runs + warps - 1) / warps : sms);
         const float scale_log2 = scale * 1.4426950408889634f;
         int rc;
-        if (smallest <= (long long)sms * 2)
-            rc = launch_stream<2, ADS_SLOTS_FOR(2)>(blocks, stream, (const bf16*)q, map_k, map_v, o_part, ml_part, a, H, max_chunks, scale_log2);
-        else if (smallest <= (long long)sms * 4)
-            rc = launch_stream<4, ADS_SLOTS_FOR(4)>(blocks, stream, (const bf16*)q, map_k, map_v, o_part, ml_part, a, H, max_chunks, scale_log2);
+        if (warps == 2)
+            rc = launch_stream<2, ADS_SLOTS_FOR(2)>(blocks, stream, (const bf16*)q, map_k, map_v, o_part, ml_part, a, H, scale_log2);
+        else if (warps == 4)
+            rc = launch_stream<4, ADS_SLOTS_FOR(4)>(blocks, stream, (const bf16*)q, map_k, map_v, o_part, ml_part, a, H, scale_log2);
         else
-            rc = launch_stream<ADS_WARPS, ADS_SLOTS>(blocks, stream, (const bf16*)q, map_k, map_v, o_part, ml_part, a, H, max_chunks, scale_log2);
+            rc = launch_stream<ADS_WARPS, ADS_SLOTS>(blocks, stream, (const bf16*)q, map_k, map_v, o_part, ml_part, a, H, scale_log2);
         if (rc) return rc;
+        MergeCut cut;
+        cut.workers = blocks * warps;
+        cut.seqs = seqs;
+        cut.KV = KV;
+        cut.parts = a.parts;
         ri_launch_pdl(attention_decode_merge_kernel, dim3(H, seqs), dim3(AD_MERGE_THREADS), 0, stream,
-                      (const float*)o_part, (const float*)ml_part, (bf16*)out, seq_len, H, max_chunks, window, err_flag);
+                      (const float*)o_part, (const float*)ml_part, (bf16*)out, seq_len, H, max_chunks, window, cut, err_flag);
         RI_CHECK_LAUNCH("attention_decode_merge");
         return 0;
     }
@@ -904,8 +1091,13 @@ extern "C" int ri_attention_decode(const void* q, const void* k_pool, const void
                   (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, o_part, ml_part, page_table, seq_slot, seq_len,
                   H, KV, mpps, num_pages, max_chunks, scale * 1.4426950408889634f, window, err_flag);
     RI_CHECK_LAUNCH("attention_decode");
+    MergeCut chunks_of_128;
+    chunks_of_128.workers = 0;
+    chunks_of_128.seqs = seqs;
+    chunks_of_128.KV = KV;
+    chunks_of_128.parts = max_chunks;
     ri_launch_pdl(attention_decode_merge_kernel, dim3(H, seqs), dim3(AD_MERGE_THREADS), 0, stream,
-                  (const float*)o_part, (const float*)ml_part, (bf16*)out, seq_len, H, max_chunks, window, err_flag);
+                  (const float*)o_part, (const float*)ml_part, (bf16*)out, seq_len, H, max_chunks, window, chunks_of_128, err_flag);
     RI_CHECK_LAUNCH("attention_decode_merge");
     return 0;
 }

@@ -71,8 +71,13 @@ extern "C" int ri_attention_decode_noalloc(const void* q, const void* k_pool, co
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, o_part, ml_part, page_table, seq_slot, seq_len, H, KV,
         mpps, num_pages, max_chunks, scale * 1.4426950408889634f, window, err_flag);
     RI_CHECK_LAUNCH("attention_decode_noalloc");
+    MergeCut chunks_of_128;                    // the partial results are those of chunks of 128 keys
+    chunks_of_128.workers = 0;
+    chunks_of_128.seqs = seqs;
+    chunks_of_128.KV = KV;
+    chunks_of_128.parts = max_chunks;
     attention_decode_merge_kernel<<<dim3(H, seqs), AD_MERGE_THREADS, 0, stream>>>(
-        o_part, ml_part, (bf16*)out, seq_len, H, max_chunks, window, err_flag);
+        o_part, ml_part, (bf16*)out, seq_len, H, max_chunks, window, chunks_of_128, err_flag);
     RI_CHECK_LAUNCH("attention_decode_noalloc (merge)");
     return 0;
 }

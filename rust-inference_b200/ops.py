@@ -372,6 +372,12 @@ def fast_attention_supported(dtype: torch.dtype, head_dim: int, page_size: int) 
     return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= MAX_FAST_HEAD_DIM and page_size == 32
 
 
+def _decode_parts(head_dim: int, chunks: int) -> int:
+    """Partial results per (sequence, head) that the decode attention's scratch memory must have room for."""
+    _, lib = _fn("attention_decode", "ri_attention_decode", {"RI_HEAD_DIM": head_dim})
+    return int(lib.ri_attention_decode_parts(int(chunks)))
+
+
 def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                      seq_slot: torch.Tensor, seq_len: torch.Tensor, scale: float, window: int,
                      max_len: int) -> torch.Tensor:
@@ -391,8 +397,9 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     _need(seq_slot, "seq_slot", torch.int32, (seqs,))
     _need(seq_len, "seq_len", torch.int32, (seqs,))
     chunks = max(1, -(-int(max_len) // DECODE_CHUNK))
-    o_part = torch.empty((seqs, H, chunks, Dh), dtype=torch.float32, device=q.device)
-    ml_part = torch.empty((seqs, H, chunks, 2), dtype=torch.float32, device=q.device)
+    parts = _decode_parts(Dh, chunks)
+    o_part = torch.empty((seqs, H, parts, Dh), dtype=torch.float32, device=q.device)
+    ml_part = torch.empty((seqs, H, parts, 2), dtype=torch.float32, device=q.device)
     out = torch.empty_like(q)
     _call("attention_decode", "ri_attention_decode", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
           out.data_ptr(), o_part.data_ptr(), ml_part.data_ptr(), page_table.data_ptr(), seq_slot.data_ptr(),
