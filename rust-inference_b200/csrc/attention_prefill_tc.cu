@@ -277,6 +277,8 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
     const int key_lo = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
     const int kb_lo = key_lo / TC_BN, kb_hi = pos_last / TC_BN;
     const int n_blocks = kb_hi - kb_lo + 1;
+    // the first tile's last query is 128 positions before the block's: the blocks of keys past it hold nothing it sees
+    const int n_blocks_0 = n_tiles > 1 ? min(n_blocks, (pos_first + TC_BM - 1) / TC_BN - kb_lo + 1) : n_blocks;
     const int kvh = h / (H / KV);
     const int* table = page_table + (size_t)seq_slot[b] * mpps;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -388,13 +390,14 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
                 umma_commit(&tail.s_full[t][jb & 1]);
                 umma_commit(&tail.k_empty[st]);                          // this tile is done with the keys of block jb
             };
+            const int my_blocks = t == 0 ? n_blocks_0 : n_blocks;
             issue_qk(0);
-            if (n_blocks > 1) issue_qk(1);
-            for (int j = 0; j < n_blocks && !dead; j++) {
+            if (my_blocks > 1) issue_qk(1);
+            for (int j = 0; j < my_blocks && !dead; j++) {
                 const int st = j % TC_STAGES;
                 // as soon as the tile's threads hold S_t of block j in their registers, its buffer takes S_t of block
                 // j + 2: the tensor core's answer has two blocks' time to come back
-                if (j + 2 < n_blocks) {
+                if (j + 2 < my_blocks) {
                     wait(&tail.s_read[t][j & 1], (unsigned)((j >> 1) & 1));
                     issue_qk(j + 2);
                 }
@@ -411,6 +414,16 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
                 umma_commit(&tail.pv_done[t][j & 1]);
                 umma_commit(&tail.v_empty[st]);                           // this tile is done with the values of block j
             }
+            // The blocks of keys that this tile leaves out: both tiles hand a stage back, so it does that once the
+            // block has landed.  (Not earlier: before that the stage's barrier may still be in the phase of the block
+            // that was there before, which the other tile may not have read yet.)
+            for (int j = my_blocks; j < n_blocks && !dead; j++) {
+                const int st = j % TC_STAGES;
+                wait(&tail.k_full[st], (unsigned)((j / TC_STAGES) & 1));
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&tail.k_empty[st])) : "memory");
+                wait(&tail.v_full[st], (unsigned)((j / TC_STAGES) & 1));
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&tail.v_empty[st])) : "memory");
+            }
         }
     } else if (warp < 4 * n_tiles) {
         // ---- a query row ------------------------------------------------------------------------------------
@@ -420,7 +433,9 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
         unsigned char* p_rows = smem + TC_OFF_P + t * 2 * TC_P_BYTES + row * 128;
         float m = -FLT_MAX, l = 0.0f;
         bool dead = false;
-        for (int j = 0; j < n_blocks; j++) {
+        const int my_blocks = t == 0 ? n_blocks_0 : n_blocks;
+        const int tile_first = pos_first + t * TC_BM, tile_last = min(tile_first + TC_BM - 1, pos_last);
+        for (int j = 0; j < my_blocks; j++) {
             const int kb = kb_lo + j;
             if (!dead && !tc_mbar_wait(&tail.s_full[t][j & 1], (unsigned)((j >> 1) & 1))) { atomicExch(err, 5); tail.dead = 1; }
             dead = dead || tail.dead != 0;
@@ -441,7 +456,8 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
             tc_fence_before();
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&tail.s_read[t][j & 1])) : "memory");
-            const bool edge = (kb * TC_BN + TC_BN - 1 > pos_first) || (window > 0 && kb * TC_BN < pos_last - window + 1);
+            // a block of keys needs the mask if some query of this tile does not see all of it
+            const bool edge = (kb * TC_BN + TC_BN - 1 > tile_first) || (window > 0 && kb * TC_BN < tile_last - window + 1);
             if (edge) {
 #pragma unroll
                 for (int i = 0; i < TC_BN; i++) {
@@ -489,23 +505,9 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
                 if (!dead && !tc_mbar_wait(&tail.pv_done[t][j & 1], (unsigned)(((j - 2) >> 1) & 1))) { atomicExch(err, 5); tail.dead = 1; dead = true; }
             }
             const float neg_m = (m == -FLT_MAX) ? 0.0f : -m;
-            if (edge) {
-                float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-                for (int c = 0; c < TC_BN / 8; c++) {
-                    float p[8];
-#pragma unroll
-                    for (int e = 0; e < 8; e++) {
-                        float x = s[c * 8 + e];
-                        p[e] = x == -FLT_MAX ? 0.0f : ex2_approx(fmaf(x, scale_log2, neg_m));
-                        l4[e & 3] += p[e];
-                    }
-                    *(uint4*)(p_row + ((c ^ (row & 7)) << 4)) =
-                        make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
-                }
-                l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-            } else {
-                // no key of the block is masked: pairs of float32 for the scaling and the sum
+            {
+                // pairs of float32 for the scaling and the sum.  A masked score is -FLT_MAX: times the (positive)
+                // scale and less any maximum it stays below every exponent that gives more than zero
                 const unsigned long long sc2 = pack2(scale_log2, scale_log2), nm2 = pack2(neg_m, neg_m);
                 unsigned long long l2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
 #pragma unroll
@@ -527,9 +529,10 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
                 l += (a0 + a1) + (b0 + b1);
             }
             if (kb * TC_BN + TC_BN > len) {
-                // value rows past the sequence's end may hold anything: the first tile's threads zero them (the tile has
-                // landed: the control lane waits for it before the product, but these writes must come before that too)
-                if (t == 0) {
+                // value rows past the sequence's end may hold anything: each tile's threads zero them before they say
+                // that P is written, so before their own tile's product (the tile has landed: the control lane waits
+                // for it before the product, but these writes must come before that too)
+                {
                     if (!dead && !tc_mbar_wait(&tail.v_full[j % TC_STAGES], (unsigned)((j / TC_STAGES) & 1))) { atomicExch(err, 5); tail.dead = 1; dead = true; }
                     unsigned char* v_tile = v_tiles + (j % TC_STAGES) * TC_KV_BYTES;
                     const int first_bad = len - kb * TC_BN;
@@ -542,8 +545,8 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
             if (kb * TC_BN < key_lo) {
                 // value rows before the first key that any query of the block sees: their page may not have been
                 // copied at all (given back by a window group), so the stage may hold anything there, and P = 0
-                // times a NaN is a NaN: the first tile's threads zero them, as above
-                if (t == 0) {
+                // times a NaN is a NaN: zeroed as above
+                {
                     if (!dead && !tc_mbar_wait(&tail.v_full[j % TC_STAGES], (unsigned)((j / TC_STAGES) & 1))) { atomicExch(err, 5); tail.dead = 1; dead = true; }
                     unsigned char* v_tile = v_tiles + (j % TC_STAGES) * TC_KV_BYTES;
                     const int head_bad = min(TC_BN, key_lo - kb * TC_BN);
@@ -559,7 +562,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const __grid_constant__ 
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&tail.p_ready[t][j & 1])) : "memory");
         }
         // ---- out = O / l ----------------------------------------------------------------------------------------
-        if (!dead && !tc_mbar_wait(&tail.pv_done[t][(n_blocks - 1) & 1], (unsigned)(((n_blocks - 1) >> 1) & 1))) { atomicExch(err, 5); tail.dead = 1; dead = true; }
+        if (!dead && !tc_mbar_wait(&tail.pv_done[t][(my_blocks - 1) & 1], (unsigned)(((my_blocks - 1) >> 1) & 1))) { atomicExch(err, 5); tail.dead = 1; dead = true; }
         tc_fence_after();
         const bool mine = t * TC_BM + row < rows && !dead;
         const float inv = 1.0f / l;
