@@ -1,4 +1,4 @@
-// y[M, N] = x[M, K] . W[N, K]^T in bfloat16 for 17 to 128 tokens: the decode-time linear of larger
+// y[M, N] = x[M, K] . W[N, K]^T in bfloat16 for 13 to 128 tokens: the decode-time linear of larger
 // batches, still bound by reading W once from memory, on the 5th-generation tensor cores (tcgen05).
 //
 // A block owns 128 rows of W (128 outputs) and a share of K: the blocks that share a tile of outputs form a
@@ -12,6 +12,9 @@
 // the blocks of a cluster put their partial tiles into their own shared memory, meet at the cluster's barrier,
 // and each adds a share of the tokens over all partial tiles, read through distributed shared memory in the
 // order of the shares of K: no scratch memory, no atomics, and a result that does not depend on the timing.
+//
+// With `gated` the rows of W are gate and up rows of a SwiGLU feed-forward alternating in blocks of 8 (so a tile of
+// 128 rows holds 64 channels with both their rows), and the kernel writes silu(gate) * up into y [M, N / 2].
 //
 // Rows past N and columns past K or M read as zeros (the copies fill them).  Output is bfloat16 or float32.
 // Waits on mbarriers are bounded: if one runs out the kernel sets the error word (5) and finishes (the
@@ -81,6 +84,8 @@ __device__ __forceinline__ void lt_tmem_ld16(unsigned taddr, float (&v)[16]) {
     for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
 }
 
+__device__ __forceinline__ float lt_silu(float t) { return t / (1.0f + expf(-t)); }
+
 struct LtTail {
     unsigned long long full[LT_MAX_STAGES], empty[LT_MAX_STAGES], done;
     unsigned tmem_base;
@@ -91,7 +96,7 @@ template <typename OutT>
 __global__ void __launch_bounds__(LT_THREADS)
 linear_stream_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                         OutT* __restrict__ y, int M, int Mp, int N, int K, int splits, int stages, int tmem_cols,
-                        int* __restrict__ err) {
+                        int gated, int* __restrict__ err) {
     extern __shared__ __align__(1024) unsigned char lt_smem[];
     if (smem_u32(lt_smem) & 1023u) {                               // the swizzle's period
         if (threadIdx.x == 0) atomicExch(err, 6);
@@ -179,15 +184,68 @@ linear_stream_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     const unsigned taddr = tmem + ((unsigned)(warp * 32) << 16);
     const bool row_ok = n0 + row < N;
     if (splits == 1) {
+        // gated: rows 16 i .. 16 i + 7 of the tile are gate rows and the 8 after them the up rows of the same channels,
+        // held by the lane 8 further on in the same warp
+        const bool gate_row = ((row >> 3) & 1) == 0;
+        const size_t ch = (size_t)((n0 + row) >> 4) * 8 + (row & 7);          // the channel of a gate row
         for (int c = 0; c < Mp; c += 16) {
             float v[16];
             lt_tmem_ld16(taddr + c, v);
-            if (row_ok) {
+            if (gated) {
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const float g = my_stages > 0 ? v[i] : 0.0f;
+                    const float u = __shfl_down_sync(0xffffffffu, g, 8);
+                    if (gate_row && row_ok && c + i < M) st_f(y + (size_t)(c + i) * (N / 2) + ch, lt_silu(g) * u);
+                }
+            } else if (row_ok) {
 #pragma unroll
                 for (int i = 0; i < 16; i++)
                     if (c + i < M) st_f(y + (size_t)(c + i) * N + n0 + row, my_stages > 0 ? v[i] : 0.0f);
             }
         }
+    } else if (gated) {
+        float* part = reinterpret_cast<float*>(lt_smem);
+        for (int c = 0; c < Mp; c += 16) {
+            float v[16];
+            lt_tmem_ld16(taddr + c, v);
+#pragma unroll
+            for (int i = 0; i < 16; i++) part[(size_t)(c + i) * LT_ROWS + row] = my_stages > 0 ? v[i] : 0.0f;
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+        unsigned peer[LT_MAX_SPLITS];
+#pragma unroll
+        for (int sp = 0; sp < LT_MAX_SPLITS; sp++) {
+            peer[sp] = 0;
+            if (sp < splits)
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(peer[sp]) : "r"(smem_u32(lt_smem)), "r"(sp));
+        }
+        // four channels per thread and step: their gate rows and, 8 rows on, their up rows, over the shares of K in order
+        const int o4 = (tid % (LT_ROWS / 8)) * 4;                             // channel of the tile, 0 .. 60
+        const int rg = (o4 >> 3) * 16 + (o4 & 7);                             // its gate row in the tile
+        for (int t = split + (tid / (LT_ROWS / 8)) * splits; t < M; t += (LT_THREADS / (LT_ROWS / 8)) * splits) {
+            float4 g = make_float4(0.0f, 0.0f, 0.0f, 0.0f), u = g;
+#pragma unroll
+            for (int sp = 0; sp < LT_MAX_SPLITS; sp++) {
+                if (sp < splits) {
+                    float4 a, b;
+                    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];\n"
+                                 : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w)
+                                 : "r"(peer[sp] + (unsigned)((t * LT_ROWS + rg) * 4)) : "memory");
+                    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];\n"
+                                 : "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w)
+                                 : "r"(peer[sp] + (unsigned)((t * LT_ROWS + rg + 8) * 4)) : "memory");
+                    g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+                    u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+                }
+            }
+            OutT* dst = y + (size_t)t * (N / 2) + (n0 >> 1) + o4;
+            if (n0 + rg + 8 < N) st_f(dst, lt_silu(g.x) * u.x);
+            if (n0 + rg + 9 < N) st_f(dst + 1, lt_silu(g.y) * u.y);
+            if (n0 + rg + 10 < N) st_f(dst + 2, lt_silu(g.z) * u.z);
+            if (n0 + rg + 11 < N) st_f(dst + 3, lt_silu(g.w) * u.w);
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
     } else {
         // the partial tile [token][row] of this share of K goes into this block's shared memory (the stages are
         // done with: every copy has landed and every product has read it)
@@ -284,7 +342,8 @@ static int lt_splits(int N, int K, int sms) {
 
 template <typename OutT>
 static cudaError_t lt_launch(dim3 grid, int splits, size_t smem, cudaStream_t stream, const CUtensorMap& map_w,
-                             const CUtensorMap& map_x, OutT* y, int M, int Mp, int N, int K, int stages, int tmem_cols, int* err) {
+                             const CUtensorMap& map_x, OutT* y, int M, int Mp, int N, int K, int stages, int tmem_cols, int gated,
+                             int* err) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(LT_THREADS);
@@ -299,15 +358,17 @@ static cudaError_t lt_launch(dim3 grid, int splits, size_t smem, cudaStream_t st
     attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    return cudaLaunchKernelEx(&cfg, linear_stream_tc_kernel<OutT>, map_w, map_x, y, M, Mp, N, K, splits, stages, tmem_cols, err);
+    return cudaLaunchKernelEx(&cfg, linear_stream_tc_kernel<OutT>, map_w, map_x, y, M, Mp, N, K, splits, stages, tmem_cols, gated, err);
 }
 
-extern "C" int ri_linear_stream_tc(const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int* err_flag,
-                                   cudaStream_t stream) {
+// gated != 0: W [N, K] holds gate and up rows alternating in blocks of 8 and y [M, N / 2] gets silu(gate) * up
+extern "C" int ri_linear_stream_tc(const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int gated,
+                                   int* err_flag, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
     RI_REQUIRE(M > 0 && N > 0 && K > 0, "linear_stream_tc: bad sizes M=%d N=%d K=%d", M, N, K);
     RI_REQUIRE(M <= LT_MAX_TOKENS, "linear_stream_tc: at most %d tokens, got %d", LT_MAX_TOKENS, M);
     RI_REQUIRE(K % 8 == 0, "linear_stream_tc: K=%d must be a multiple of 8", K);
+    RI_REQUIRE(!gated || N % 16 == 0, "linear_stream_tc: %d gate and up rows are not whole blocks of 8 and 8", N);
     RI_REQUIRE((((uintptr_t)x | (uintptr_t)w) & 15) == 0, "linear_stream_tc: x and w must be 16-byte aligned");
     static int sms = 0;
     if (!sms) {
@@ -337,8 +398,8 @@ extern "C" int ri_linear_stream_tc(const void* x, const void* w, void* y, int M,
         configured[out_f32 ? 1 : 0] = true;
     }
     dim3 grid(tiles, splits);
-    cudaError_t le = out_f32 ? lt_launch<float>(grid, splits, smem, stream, map_w, map_x, (float*)y, M, Mp, N, K, stages, tmem_cols, err_flag)
-                             : lt_launch<bf16>(grid, splits, smem, stream, map_w, map_x, (bf16*)y, M, Mp, N, K, stages, tmem_cols, err_flag);
+    cudaError_t le = out_f32 ? lt_launch<float>(grid, splits, smem, stream, map_w, map_x, (float*)y, M, Mp, N, K, stages, tmem_cols, gated, err_flag)
+                             : lt_launch<bf16>(grid, splits, smem, stream, map_w, map_x, (bf16*)y, M, Mp, N, K, stages, tmem_cols, gated, err_flag);
     if (le != cudaSuccess) RI_FAIL((int)le, "linear_stream_tc: %s", cudaGetErrorString(le));
     RI_CHECK_LAUNCH("linear_stream_tc");
     return 0;

@@ -35,7 +35,7 @@ _SIGNATURES = {
     ("sampling", "ri_mark_seen"): [_P, _L, _P, _P, _I, _I, _P],
     ("attention_decode", "ri_attention_decode"): [_P] * 9 + [_I] * 8 + [_F, _I, _P, _P],
     ("linear_skinny", "ri_linear_skinny"): [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
-    ("linear_stream_tc", "ri_linear_stream_tc"): [_P, _P, _P, _I, _I, _I, _I, _P, _P],
+    ("linear_stream_tc", "ri_linear_stream_tc"): [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     ("attention_prefill_tc", "ri_attention_prefill_tc"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _P],
     ("attention_prefill", "ri_attention_prefill"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _P],
 }
@@ -241,7 +241,16 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, block: int) -> torch
         _call("linear_skinny", "ri_linear_skinny", x.data_ptr(), w_gate_up.data_ptr(), y.data_ptr(), M, N, K, 0, 1,
               error_flag(x.device).data_ptr(), _stream())
         return y
+    if (x.dtype == torch.bfloat16 and M > SKINNY_MAX_TOKENS and block == 8 and N % 16 == 0 and _FUSED_SWIGLU
+            and _takes_stream_tc(M, N, K)):
+        return linear_stream_tc(x, w_gate_up, gated=True)
     return silu_mul(linear(x, w_gate_up), block)
+
+
+def _takes_stream_tc(M: int, N: int, K: int) -> bool:
+    """Whether a bfloat16 linear of M tokens (more than the mma.sync kernel takes) runs on the tcgen05 streaming kernel."""
+    return M <= STREAM_TC_MAX_TOKENS and K % 8 == 0 and (
+        _STREAM_TC == "1" or N >= STREAM_TC_WIDE or (M <= STREAM_TC_SMALL and _STREAM_TC != "0"))
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -272,26 +281,30 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         _call("linear_skinny", "ri_linear_skinny", x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K,
               1 if out_dtype == torch.float32 else 0, 0, error_flag(x.device).data_ptr(), _stream())
         return y
-    if M <= STREAM_TC_MAX_TOKENS and K % 8 == 0 and (
-            _STREAM_TC == "1" or N >= STREAM_TC_WIDE or (M <= STREAM_TC_SMALL and _STREAM_TC != "0")):
+    if _takes_stream_tc(M, N, K):
         return linear_stream_tc(x, w, out_dtype)
     if out_dtype == torch.float32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
     return torch.mm(x, w.t())
 
 
-def linear_stream_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+def linear_stream_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+                     gated: bool = False) -> torch.Tensor:
     """y = x w^T in bfloat16 for up to 128 tokens on tcgen05: weight rows as the M side of the product, tokens as N,
-    K split over a thread-block cluster whose partial tiles are added through distributed shared memory."""
+    K split over a thread-block cluster whose partial tiles are added through distributed shared memory.
+    ``gated``: w holds gate and up rows alternating in blocks of 8, and y [M, N/2] = silu(gate) * up."""
     _need(x, "x", torch.bfloat16)
     _need(w, "w", torch.bfloat16)
     M, K = x.shape
     if M > STREAM_TC_MAX_TOKENS or K % 8 or w.shape[1] != K:
         raise KernelError(f"linear_stream_tc: x {tuple(x.shape)}, w {tuple(w.shape)}: at most {STREAM_TC_MAX_TOKENS} tokens, K a multiple of 8")
     N = w.shape[0]
-    y = torch.empty((M, N), dtype=torch.float32 if out_dtype == torch.float32 else torch.bfloat16, device=x.device)
+    if gated and N % 16:
+        raise KernelError(f"linear_stream_tc: {N} gate and up rows are not whole blocks of 8 and 8")
+    y = torch.empty((M, N // 2 if gated else N), dtype=torch.float32 if out_dtype == torch.float32 else torch.bfloat16,
+                    device=x.device)
     _call("linear_stream_tc", "ri_linear_stream_tc", x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K,
-          1 if out_dtype == torch.float32 else 0, error_flag(x.device).data_ptr(), _stream())
+          1 if out_dtype == torch.float32 else 0, 1 if gated else 0, error_flag(x.device).data_ptr(), _stream())
     return y
 
 

@@ -194,6 +194,31 @@ def test_linear_stream_tc(shape):
         assert torch.equal(fewer, full[:13])
 
 
+@pytest.mark.parametrize("shape", [(13, 208, 520), (17, 4096, 1024), (32, 24576, 4096), (24, 48, 72), (64, 1040, 2048)])
+def test_linear_stream_tc_gated(shape):
+    """The tcgen05 weight-streaming linear with the SiLU gate in its epilogue (gate and up rows alternating in blocks
+    of 8): alone in its cluster and with K split, widths that end inside a tile of 128 rows."""
+    from rust_inference_b200 import ops
+    M, N, K = shape                      # N rows of gate and up together
+    rng = np.random.default_rng(N + M)
+    x = rnd(rng, M, K, dtype="bfloat16")
+    gate, up = rnd(rng, N // 2, K, scale=0.2, dtype="bfloat16"), rnd(rng, N // 2, K, scale=0.2, dtype="bfloat16")
+    nb = N // 16
+    w = np.stack([gate.reshape(nb, 8, K), up.reshape(nb, 8, K)], axis=1).reshape(N, K)
+    g, u = plain.linear(x, gate), plain.linear(x, up)
+    want = plain.silu(g) * u
+    xd, wd = dev(x, torch.bfloat16), dev(w, torch.bfloat16)
+    got = ops.linear_stream_tc(xd, wd, gated=True)
+    assert got.shape == (M, N // 2)
+    close(got, want, 5e-3, f"gated linear_stream_tc {shape}")
+    assert torch.equal(ops.linear_stream_tc(xd, wd, gated=True), got)
+    # the same through the feed-forward's entry point, against the product followed by the separate gate
+    fused = ops.linear_swiglu(xd, wd, 8)
+    apart = ops.silu_mul(ops.linear_stream_tc(xd, wd), 8)
+    close(fused, apart.float().cpu().numpy().astype(np.float64), 1e-2, "fused against product and gate apart")
+    assert int(ops.error_flag("cuda").item()) == 0
+
+
 def test_linear_takes_the_streaming_kernel_for_wide_outputs(monkeypatch):
     """`ops.linear` for 17 to 128 tokens hands matrices with many outputs (an output head) to the tcgen05
     streaming kernel and the others to the library; the threshold lowered, both ways give the same product."""
