@@ -220,7 +220,7 @@ def test_linear_stream_tc_gated(shape):
 
 
 def test_linear_takes_the_streaming_kernel_for_wide_outputs(monkeypatch):
-    """`ops.linear` for 17 to 128 tokens hands matrices with many outputs (an output head) to the tcgen05
+    """`ops.linear` for 33 to 128 tokens hands matrices with many outputs (an output head) to the tcgen05
     streaming kernel and the others to the library; the threshold lowered, both ways give the same product."""
     from rust_inference_b200 import ops
     rng = np.random.default_rng(5)

@@ -1,8 +1,9 @@
 """Schedules that the other replay tests do not reach, each against the plain model:
 
-* many sequences decoding together (24 and 64: the library products for 17 to 128 tokens, the
-  tcgen05 weight-streaming linear when it is asked for, the decode attention with several items per
-  warp), on the tiny configuration with heads of 128 and on two layers of Qwen3-8B's shapes;
+* many sequences decoding together (14, 15, 24 and 64: the tcgen05 weight-streaming linear of 13 to
+  32 tokens, the library products above that, the same linear when it is asked for there, the decode
+  attention whose runs of pages pass through several sequences), on the tiny configuration with
+  heads of 128 and on two layers of Qwen3-8B's shapes;
 * steps that are neither whole prompts nor one token each: a prompt brought in pieces, and a step
   in which one sequence brings a prompt while others go on by one token;
 * a window group whose sequence brings several tokens after pages behind the window went back.
@@ -58,7 +59,7 @@ def test_many_sequences_decode_together_tiny(tmp_path, tiny_d, dtype, seqs, stre
     steps = _together(reqs, decode)
     env = dict(os.environ)
     if stream_tc:
-        env["RUST_INFERENCE_B200_STREAM_TC_WIDE"] = "256"      # every linear of 17 to 128 tokens with 256 outputs or more
+        env["RUST_INFERENCE_B200_STREAM_TC_WIDE"] = "256"      # every linear of 13 to 128 tokens with 256 outputs or more
     out = str(tmp_path / "out")
     H.replay_subprocess(d, dtype, steps, out, env=env)
     rows = H.collect(steps, out, cfg["vocab_size"])
