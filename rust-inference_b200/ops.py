@@ -36,7 +36,7 @@ _SIGNATURES = {
     ("attention_decode", "ri_attention_decode"): [_P] * 9 + [_I] * 8 + [_F, _I, _P, _P],
     ("linear_skinny", "ri_linear_skinny"): [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     ("linear_stream_tc", "ri_linear_stream_tc"): [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
-    ("attention_prefill_tc", "ri_attention_prefill_tc"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _P],
+    ("attention_prefill_tc", "ri_attention_prefill_tc"): [_P] * 8 + [_I] * 9 + [_F, _I, _P, _P],
     ("attention_prefill", "ri_attention_prefill"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _P],
 }
 DECODE_CHUNK = 128          # keys per partial result of the decode attention kernel
@@ -446,7 +446,7 @@ def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
         # head sizes of 64 and 128: the tcgen05 / tensor-memory kernel
         _call("attention_prefill_tc", "ri_attention_prefill_tc", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
               out.data_ptr(), page_table.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seq_len.data_ptr(),
-              seqs, int(max_new), H, KV, Dh, page_table.shape[1], page_size, pages, float(scale), int(window),
+              q.shape[0], seqs, int(max_new), H, KV, Dh, page_table.shape[1], page_size, pages, float(scale), int(window),
               error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
         return out
     _call("attention_prefill", "ri_attention_prefill", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),

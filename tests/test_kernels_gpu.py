@@ -684,6 +684,43 @@ def test_attention_prefill_kernel(H, KV, Dh, window):
     assert torch.equal(one, out[starts[4]:starts[5]])
 
 
+@pytest.mark.parametrize("Dh,window", [(128, 0), (64, 0), (128, 300)])
+def test_attention_prefill_more_work_items_than_sms(Dh, window, monkeypatch):
+    """The tcgen05 prefill kernel keeps one block per SM that takes its work items (256 rows of a sequence and a
+    head) one after the other: 288 items here, of which those past a sequence's rows are empty, so every block
+    passes from one item to the next (its buffers and barriers keep their turns across items), with sequences of
+    unequal lengths, old keys in the cache and a window.  Against the plain attention for two heads and against
+    the mma.sync kernel for all."""
+    from rust_inference_b200 import ops
+    H, KV = 16, 4
+    rng = np.random.default_rng(Dh + window)
+    old = [100, 0, 33]
+    new = [700, 1300, 257]
+    lens = [a + b for a, b in zip(old, new)]
+    table, slots, k, v, k_pool, v_pool = _fill_pools(rng, lens, KV, Dh, "bfloat16", scale=0.5)
+    T = sum(new)
+    q = rnd(rng, T, H, Dh, dtype="bfloat16")
+    starts = np.concatenate([[0], np.cumsum(new)]).astype(np.int32)
+    bt = torch.bfloat16
+    args = (dev(q, bt), dev(k_pool, bt), dev(v_pool, bt), dev(table, torch.int32), dev(slots, torch.int32),
+            dev(starts, torch.int32), dev(np.array(lens), torch.int32), max(new), 1.0 / math.sqrt(Dh), window)
+    out = ops.attention_prefill(*args)
+    torch.cuda.synchronize()
+    assert int(ops.error_flag("cuda").item()) == 0
+    heads, kv_heads = [0, 13], [0, 3]
+    for b, (o, n) in enumerate(zip(old, new)):
+        qall = np.concatenate([np.zeros((o, 2, Dh)), q[starts[b]:starts[b + 1]][:, heads].astype(np.float64)])
+        want = plain.causal_attention(qall, k[b][:, kv_heads].astype(np.float64), v[b][:, kv_heads].astype(np.float64),
+                                      window=window)[o:]
+        close(out[starts[b]:starts[b + 1]][:, heads], want, 2e-2, f"prefill attention, sequence {b}")
+    again = ops.attention_prefill(*args)
+    assert torch.equal(again, out)
+    monkeypatch.setattr(ops, "_NO_TCGEN05", True)
+    other = ops.attention_prefill(*args)
+    close(out, other.float().cpu().numpy().astype(np.float64), 2e-2, "tcgen05 against mma.sync")
+    assert int(ops.error_flag("cuda").item()) == 0
+
+
 @pytest.mark.parametrize("H,KV,Dh", [(8, 2, 128), (4, 4, 64), (6, 2, 32)])
 def test_attention_prefill_unwritten_rows_are_nan(H, KV, Dh):
     """As for decoding: what the pool holds past a sequence's end, not-a-number included, changes nothing."""
