@@ -245,6 +245,7 @@ def run_workload(a) -> int:
 
 
 def main() -> int:
+    global CONTEXT, PREFILL_TOKENS, METRIC
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
@@ -254,6 +255,10 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the 36 of the configuration (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--model", default="8b", choices=sorted(SHAPES), help="layer sizes: Qwen3-8B (the default), 14B or 32B")
+    ap.add_argument("--context", type=int, default=CONTEXT,
+                    help="context length that the timed decode steps end at (the default is the configuration's; named in config)")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                    help="tokens of the timed prompt step (the default is what the line's contract names; named in config)")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--workload", choices=sorted(WORKLOADS),
@@ -268,6 +273,9 @@ def main() -> int:
     if a.gpus != 1:
         print(f"bench.py measures one GPU: this library runs on a single device, --gpus {a.gpus} is not supported")
         return 2
+    if a.context != CONTEXT:
+        METRIC = METRIC.replace(f"context {CONTEXT}", f"context {a.context}")
+    CONTEXT, PREFILL_TOKENS = a.context, a.prefill_tokens
     if a.workload:
         return run_workload(a)
     if a.warmup < 3:
