@@ -40,7 +40,11 @@
 //   o_free[t]  (4 arrivals)         the tile's threads hold the item's output: the next item's first product may overwrite O_t
 // Every barrier belongs to one buffer; a barrier waited on by parity is never two phases ahead of a
 // waiter, because its next phase needs something that waiter does after the wait.  Every wait is
-// bounded by time and ends in an error code (5), not a hang.
+// bounded by time and ends in an error code (5), not a hang: the thread that gave up says so in shared memory,
+// the copying lane starts no further copy, the issuing lanes no further product, the rows' threads run through
+// their blocks without waiting, and the block ends as usual (barrier, tensor memory given back) with a wrong
+// result for its items.  -DTC_TEST_DROP_COPY_LEN=<n> (tests only; nothing in an ordinary build) leaves out one copy
+// in sequences of exactly n keys, so that this path can be run.
 // Tensor memory (512 columns): S_t buffer b at column (2 t + b) * 64, O_0 and O_1 at 256 and 384.
 // Shared memory (224 KB at head size 128) leaves no room for slack: the dynamic shared memory must
 // start on a multiple of 1024 bytes (the swizzle's period), else the kernel reports error 6.
@@ -226,8 +230,9 @@ __device__ __forceinline__ TcPages tc_pages(const int* __restrict__ table, int k
     return r;
 }
 // starts the copies of a tile of 64 keys (or values): per page and per slab of 64 head elements one box
+// (`drop`: tests only, see TC_TEST_DROP_COPY_LEN: the first box is counted and not copied)
 __device__ __forceinline__ void tc_load_tile(unsigned char* tile, const CUtensorMap* map, const TcPages& pg, int kvh, int KV,
-                                             unsigned long long* bar) {
+                                             unsigned long long* bar, bool drop = false) {
     const int boxes = ((pg.id[0] >= 0) + (pg.id[1] >= 0)) * TC_SLABS;
     tc_expect_tx(bar, (unsigned)boxes * (TC_PAGE * 128));       // also completes the phase when there is nothing to copy
 #pragma unroll
@@ -235,8 +240,10 @@ __device__ __forceinline__ void tc_load_tile(unsigned char* tile, const CUtensor
         if (pg.id[j] < 0) continue;
         const int row = (pg.id[j] * KV + kvh) * TC_PAGE;
 #pragma unroll
-        for (int sl = 0; sl < TC_SLABS; sl++)
+        for (int sl = 0; sl < TC_SLABS; sl++) {
+            if (drop && j == 0 && sl == 0) continue;
             tc_tma_2d(tile + sl * TC_KV_SLAB + j * (TC_PAGE * 128), map, sl * 64, row, bar);
+        }
     }
 }
 
@@ -376,9 +383,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (tma_warp) {
         if (lane == 0) {
             // ---- the copying lane: queries, keys and values of one item after the other, as buffers come free ----
+            // After a wait has run out (here or anywhere in the block) this lane starts no further copy: the barrier of
+            // a copy arrives once per phase, and behind a wait that was given up nothing says that the phase before has
+            // ended (a second arrival in one phase is one more than the barrier was set up for).
             bool dead = false;
             auto wait = [&](unsigned long long* bar, unsigned parity) {
                 if (!dead && !tc_mbar_wait(bar, parity)) { atomicExch(err, 5); tail.dead = 1; dead = true; }
+                dead = dead || tail.dead != 0;
             };
             int kv_base = 0, n_it = 0;            // blocks of keys and items before the one at hand
             for (int k = 0; k < rounds && !dead; k++) {
@@ -390,6 +401,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                     for (int t = 0; t < TC_TILES; t++) {
                         if (n_it > 0) wait(&tail.q_empty[t], (unsigned)((n_it - 1) & 1));
+                        if (dead) return;
                         tc_expect_tx(&tail.q_full[t], TC_Q_TILE_BYTES);
 #pragma unroll
                         for (int sl = 0; sl < TC_SLABS; sl++)
@@ -401,14 +413,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 // the queries of a later item wait for the last product Q K^T of the item before, which is also what
                 // frees the key stage of that item's last block: they go in behind the keys that take that stage
                 const int q_after = min(TC_STAGES - 1, it.n_blocks - 1);
-                for (int j = 0; j < it.n_blocks; j++) {
+                for (int j = 0; j < it.n_blocks && !dead; j++) {
                     const int gj = kv_base + j, buf = gj % TC_STAGES;
                     const unsigned parity = (unsigned)((gj / TC_STAGES - 1) & 1);
                     const TcPages pg = tc_pages(it.table, it.kb_lo + j, it.len, it.key_lo, num_pages, err);   // under the wait below
                     if (gj >= TC_STAGES) wait(&tail.k_empty[buf], parity);
-                    tc_load_tile(k_tiles + buf * TC_KV_BYTES, &map_k, pg, it.kvh, KV, &tail.k_full[buf]);
+                    if (dead) break;
+#ifdef TC_TEST_DROP_COPY_LEN
+                    // tests only: in a sequence of exactly this many keys the first copy of an item's first block of keys
+                    // is left out, so that its barrier never completes and the waits behind it run out
+                    const bool drop = it.len == TC_TEST_DROP_COPY_LEN && j == 0;
+#else
+                    const bool drop = false;
+#endif
+                    tc_load_tile(k_tiles + buf * TC_KV_BYTES, &map_k, pg, it.kvh, KV, &tail.k_full[buf], drop);
                     if (n_it > 0 && j == q_after) load_q();
                     if (gj >= TC_STAGES) wait(&tail.v_empty[buf], parity);
+                    if (dead) break;
                     tc_load_tile(v_tiles + buf * TC_KV_BYTES, &map_v, pg, it.kvh, KV, &tail.v_full[buf]);
                 }
                 kv_base += it.n_blocks;

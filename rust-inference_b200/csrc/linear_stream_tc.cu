@@ -18,7 +18,11 @@
 //
 // Rows past N and columns past K or M read as zeros (the copies fill them).  Output is bfloat16 or float32.
 // Waits on mbarriers are bounded: if one runs out the kernel sets the error word (5) and finishes (the
-// cluster's barrier is a hardware barrier that every block reaches on every path).
+// cluster's barrier is a hardware barrier that every block reaches on every path).  -DLT_TEST_DROP_COPY_K=<k>
+// (tests only; nothing in an ordinary build) makes the first block of launches with K == k leave out the copy
+// of W of its first stage, so that this path can be run: that stage's barrier then never completes, the issuing
+// lane gives up, the copying lane gives up waiting for the stage to come back, the accumulator is read as it is,
+// the cluster's barriers are met and the tensor memory is given back.
 #include "common.cuh"
 #include "mma_helpers.cuh"
 #include <cuda.h>
@@ -142,6 +146,9 @@ linear_stream_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         const int first = my_stages < stages ? my_stages : stages;
         for (int i = 0; i < first; i++) {
             lt_expect_tx(&tail.full[i], (unsigned)stage_bytes);
+#ifdef LT_TEST_DROP_COPY_K
+            if (K == LT_TEST_DROP_COPY_K && tile == 0 && split == 0 && i == 0) continue;      // tests only: see the top
+#endif
             lt_tma_2d(lt_smem + (size_t)i * stage_bytes, &map_w, (st_lo + i) * LT_STAGE_K, n0, &tail.full[i]);
         }
         pdl_wait();
@@ -151,6 +158,10 @@ linear_stream_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         for (int i = stages; i < my_stages && !dead; i++) {
             const int s = i % stages;
             if (!ri_mbar_wait(&tail.empty[s], (unsigned)((i / stages - 1) & 1))) { atomicExch(err, 5); tail.dead = 1; dead = true; }
+            // After a wait has run out (here or in the issuing lane) no further stage is started: a stage's barrier
+            // whose copies never all came is still in its old phase, and a second arrival in that phase is one more
+            // than the barrier was set up for.
+            if (dead || *(volatile int*)&tail.dead) break;
             lt_expect_tx(&tail.full[s], (unsigned)stage_bytes);
             lt_tma_2d(lt_smem + (size_t)s * stage_bytes, &map_w, (st_lo + i) * LT_STAGE_K, n0, &tail.full[s]);
             lt_tma_2d(lt_smem + (size_t)s * stage_bytes + LT_A_BYTES, &map_x, (st_lo + i) * LT_STAGE_K, 0, &tail.full[s]);
@@ -163,6 +174,7 @@ linear_stream_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         for (int i = 0; i < my_stages && !dead; i++) {
             const int s = i % stages;
             if (!ri_mbar_wait(&tail.full[s], (unsigned)((i / stages) & 1))) { atomicExch(err, 5); tail.dead = 1; dead = true; }
+            if (dead) break;                        // the stage is not there: no product on it, and it is not handed back
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const unsigned long long off = (unsigned long long)((s * stage_bytes) >> 4);
 #pragma unroll
@@ -170,7 +182,9 @@ linear_stream_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                 lt_mma(tmem, a0 + off + (unsigned)((j * 32) >> 4), b0 + off + (unsigned)((j * 32) >> 4), idesc, (i > 0 || j > 0) ? 1u : 0u);
             lt_commit(&tail.empty[s]);
         }
-        lt_commit(&tail.done);
+        // (after a wait that ran out there may be no product at all behind this: then a plain arrival)
+        if (dead) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&tail.done)) : "memory");
+        else lt_commit(&tail.done);
     }
     // (the other threads of warps 0 and 1 wait with everybody else)
     pdl_wait();                                    // before the first write to global memory

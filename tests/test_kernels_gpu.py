@@ -875,6 +875,111 @@ print("gave up after %.1f ms" % ms)
     assert 3.0 <= ms <= 2000.0, r.stdout          # the first launch also loads the library: no tight upper bound
 
 
+def test_a_wait_that_runs_out_in_the_tcgen05_linear(tmp_path):
+    """The same for the tcgen05 weight-streaming linear, whose way out of a wait that has run out passes the
+    cluster's barriers and the release of its tensor memory: built with a test-only define, the first block of a
+    launch with K = 1536 leaves out the copy of W of its first stage.  The issuing lane and then the copying lane
+    give up (about 4 ms each), error 5 is reported, the kernel returns, the other tiles' outputs are right and
+    the next launch is right.  Nothing hangs or faults: the waits are the bounded ones."""
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import time, torch
+import rust_inference_b200
+from rust_inference_b200 import ops
+torch.manual_seed(0)
+flag = ops.error_flag("cuda")
+x = torch.randn(20, 1536, device="cuda").to(torch.bfloat16)
+w = torch.randn(300, 1536, device="cuda").to(torch.bfloat16)
+torch.cuda.synchronize()
+t0 = time.perf_counter()
+y = ops.linear_stream_tc(x, w)
+torch.cuda.synchronize()
+ms = (time.perf_counter() - t0) * 1e3
+assert int(flag.item()) == 5, int(flag.item())
+flag.zero_()
+want = x.float() @ w.float().t()
+assert torch.allclose(y.float()[:, 128:], want[:, 128:], rtol=2e-2, atol=0.5), "outputs of the other tiles"
+x2 = torch.randn(20, 2048, device="cuda").to(torch.bfloat16)
+w2 = torch.randn(300, 2048, device="cuda").to(torch.bfloat16)
+y2 = ops.linear_stream_tc(x2, w2)
+torch.cuda.synchronize()
+assert int(flag.item()) == 0
+assert torch.allclose(y2.float(), x2.float() @ w2.float().t(), rtol=2e-2, atol=0.5)
+print("gave up after %.1f ms" % ms)
+'''
+    env = dict(os.environ, RUST_INFERENCE_B200_DEFINES="LT_TEST_DROP_COPY_K=1536", PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout + r.stderr
+    ms = float(r.stdout.split("after")[1].split()[0])
+    assert 3.0 <= ms <= 2000.0, r.stdout          # the first launch also loads the library: no tight upper bound
+
+
+def test_a_wait_that_runs_out_in_the_tcgen05_attention(tmp_path):
+    """The same for the tcgen05 prefill attention (barriers between a copying lane, two issuing lanes and eight warps
+    of row threads; tensor memory to give back): built with a test-only define, a copy of the first block of keys is
+    left out in sequences of exactly 100 keys.  Error 5 is reported, the kernel returns, a sequence of another length
+    in the same launch is right, and so is the next launch."""
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import math, time, torch
+import rust_inference_b200
+from rust_inference_b200 import ops
+torch.manual_seed(0)
+flag = ops.error_flag("cuda")
+H, KV, Dh = 2, 1, 128
+bt = torch.bfloat16
+i32 = lambda a: torch.tensor(a, dtype=torch.int32, device="cuda")
+def run(new):
+    T = sum(new)
+    q = torch.randn(T, H, Dh, device="cuda").to(bt)
+    pages = sum(-(-n // 32) for n in new)
+    k_pool = (torch.randn(pages, KV, 32, Dh, device="cuda") * 0.5).to(bt)
+    v_pool = torch.randn(pages, KV, 32, Dh, device="cuda").to(bt)
+    table = torch.full((len(new), 8), -1, dtype=torch.int32)
+    p = 0
+    for b, n in enumerate(new):
+        for j in range(-(-n // 32)):
+            table[b, j] = p
+            p += 1
+    starts = [0]
+    for n in new:
+        starts.append(starts[-1] + n)
+    out = ops.attention_prefill(q, k_pool, v_pool, table.cuda(), i32(list(range(len(new)))), i32(starts), i32(new), max(new),
+                                1.0 / math.sqrt(Dh), 0)
+    torch.cuda.synchronize()
+    want = []
+    for b, n in enumerate(new):
+        ids = table[b, :-(-n // 32)].long().cuda()
+        kk = k_pool[ids][:, 0].reshape(-1, Dh)[:n].float()
+        vv = v_pool[ids][:, 0].reshape(-1, Dh)[:n].float()
+        qq = q[starts[b]:starts[b + 1]].float()
+        s = torch.einsum("thd,kd->htk", qq, kk) / math.sqrt(Dh)
+        s = s.masked_fill(torch.triu(torch.ones(n, n, dtype=torch.bool, device="cuda"), 1), float("-inf"))
+        want.append(torch.einsum("htk,kd->thd", torch.softmax(s, -1), vv))
+    return out.float(), want, starts
+t0 = time.perf_counter()
+out, want, starts = run([100, 70])
+ms = (time.perf_counter() - t0) * 1e3
+assert int(flag.item()) == 5, int(flag.item())
+flag.zero_()
+assert torch.allclose(out[starts[1]:starts[2]], want[1], rtol=2e-2, atol=2e-2), "the sequence of 70 keys"
+out, want, starts = run([101, 70])
+assert int(flag.item()) == 0
+for b in range(2):
+    assert torch.allclose(out[starts[b]:starts[b + 1]], want[b], rtol=2e-2, atol=2e-2)
+print("gave up after %.1f ms" % ms)
+'''
+    env = dict(os.environ, RUST_INFERENCE_B200_DEFINES="TC_TEST_DROP_COPY_LEN=100", PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout + r.stderr
+    ms = float(r.stdout.split("after")[1].split()[0])
+    assert 3.0 <= ms <= 5000.0, r.stdout          # the first launch also loads the library: no tight upper bound
+
+
 @pytest.mark.parametrize("Dh,window,n", [(128, 100, 450), (64, 33, 300), (32, 64, 257), (48, 1, 90)])
 def test_window_edges_stand_out(Dh, window, n):
     """The two keys at a window's edge get a score far above all others in two heads: in head 0 the last key
