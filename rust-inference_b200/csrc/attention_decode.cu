@@ -583,18 +583,28 @@ attention_decode_stream_kernel(const bf16* __restrict__ q, const __grid_constant
             const int row = (id * a.KV + ci.kvh) * AD_PAGE;
             mbar_expect_tx(&bars[slot_i], ADS_SLOT_BYTES);
 #pragma unroll
-            for (int x = 0; x < ADS_BOXES; x++)
+            for (int x = 0; x < ADS_BOXES; x++) {
+#ifdef ADS_TEST_DROP_COPY_LEN
+                // tests only: the first copy of the keys of page 0, kv head 0, of a sequence of exactly this many keys
+                // is left out, so that its barrier never completes and the wait for it runs out
+                if (ci.len == ADS_TEST_DROP_COPY_LEN && ci.p == 0 && ci.kvh == 0 && !issue_v && x == 0) continue;
+#endif
                 tma_load_2d(dst + x * ADS_BOX_BYTES, issue_v ? &map_v : &map_k, x * 64, row, &bars[slot_i]);
+            }
         }
         slot_i = slot_i + 1 == SLOTS ? 0 : slot_i + 1;
         in_flight++;
         if (issue_v) more = stream_next<true>(ci, a, tab, cut, lane);
         issue_v ^= 1;
     };
+    int gave_up_slot = 0;
+    unsigned gave_up_parity = 0;
     auto wait_tile = [&]() {
         if (!dead && !ri_mbar_wait(&bars[slot_c], (phases >> slot_c) & 1u)) {
             if (lane == 0) atomicExch(a.err, 5);
             dead = true;
+            gave_up_slot = slot_c;
+            gave_up_parity = (phases >> slot_c) & 1u;
         }
         phases ^= 1u << slot_c;
     };
@@ -769,6 +779,16 @@ attention_decode_stream_kernel(const bf16* __restrict__ q, const __grid_constant
         }
         live = stream_next<false>(cc, a, tab, cut, lane);
         if (dead) break;
+    }
+    if (dead) {
+        // A warp that gave up has started no further copy; those it had started are waited for once more, each with
+        // the same limit: a copy must not land in shared memory that the block has given back.
+        ri_mbar_wait(&bars[gave_up_slot], gave_up_parity);
+        for (; in_flight > 0; in_flight--) {
+            ri_mbar_wait(&bars[slot_c], (phases >> slot_c) & 1u);
+            phases ^= 1u << slot_c;
+            slot_c = slot_c + 1 == SLOTS ? 0 : slot_c + 1;
+        }
     }
 }
 

@@ -916,6 +916,66 @@ print("gave up after %.1f ms" % ms)
     assert 3.0 <= ms <= 2000.0, r.stdout          # the first launch also loads the library: no tight upper bound
 
 
+def test_a_wait_that_runs_out_in_the_streaming_decode_attention(tmp_path):
+    """The same for the streaming decode attention (a ring of copies per warp): built with a test-only define, a copy
+    of the first page of keys is left out in sequences of exactly 700 keys.  The warp gives up, reports error 5, starts
+    no further copy and waits (bounded) for those it had started; the kernel returns, the other sequence of the
+    launch is right, and so is the next launch."""
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import math, time, torch
+import rust_inference_b200
+from rust_inference_b200 import ops
+torch.manual_seed(0)
+flag = ops.error_flag("cuda")
+H, KV, Dh = 8, 2, 128
+bt = torch.bfloat16
+i32 = lambda a: torch.tensor(a, dtype=torch.int32, device="cuda")
+def run(lens):
+    q = torch.randn(len(lens), H, Dh, device="cuda").to(bt)
+    per = [-(-n // 32) for n in lens]
+    k_pool = (torch.randn(sum(per), KV, 32, Dh, device="cuda") * 0.5).to(bt)
+    v_pool = torch.randn(sum(per), KV, 32, Dh, device="cuda").to(bt)
+    table = torch.full((len(lens), max(per)), -1, dtype=torch.int32)
+    p = 0
+    for b, n in enumerate(per):
+        table[b, :n] = torch.arange(p, p + n, dtype=torch.int32)
+        p += n
+    out = ops.attention_decode(q, k_pool, v_pool, table.cuda(), i32(list(range(len(lens)))), i32(lens), 1.0 / math.sqrt(Dh), 0, max(lens))
+    torch.cuda.synchronize()
+    want = []
+    for b, n in enumerate(lens):
+        ids = table[b, :per[b]].long().cuda()
+        rows = []
+        for h in range(H):
+            kk = k_pool[ids][:, h // (H // KV)].reshape(-1, Dh)[:n].float()
+            vv = v_pool[ids][:, h // (H // KV)].reshape(-1, Dh)[:n].float()
+            w = torch.softmax(kk @ q[b, h].float() / math.sqrt(Dh), 0)
+            rows.append(w @ vv)
+        want.append(torch.stack(rows))
+    return out.float(), want
+t0 = time.perf_counter()
+out, want = run([700, 300])
+ms = (time.perf_counter() - t0) * 1e3
+assert int(flag.item()) == 5, int(flag.item())
+flag.zero_()
+assert torch.allclose(out[1], want[1], rtol=2e-2, atol=2e-2), "the sequence of 300 keys"
+assert torch.allclose(out[0, 4:], want[0][4:], rtol=2e-2, atol=2e-2), "the other kv head of the sequence of 700 keys"
+out, want = run([701, 300])
+assert int(flag.item()) == 0
+for b in range(2):
+    assert torch.allclose(out[b], want[b], rtol=2e-2, atol=2e-2)
+print("gave up after %.1f ms" % ms)
+'''
+    env = dict(os.environ, RUST_INFERENCE_B200_DEFINES="ADS_TEST_DROP_COPY_LEN=700", PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout + r.stderr
+    ms = float(r.stdout.split("after")[1].split()[0])
+    assert 3.0 <= ms <= 5000.0, r.stdout          # the first launch also loads the library: no tight upper bound
+
+
 def test_a_wait_that_runs_out_in_the_tcgen05_attention(tmp_path):
     """The same for the tcgen05 prefill attention (barriers between a copying lane, two issuing lanes and eight warps
     of row threads; tensor memory to give back): built with a test-only define, a copy of the first block of keys is
