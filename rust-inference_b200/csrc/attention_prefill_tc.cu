@@ -380,6 +380,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     constexpr unsigned IDESC_QK = instr_desc(TC_BM, TC_BN, 0);
     constexpr unsigned IDESC_PV = instr_desc(TC_BM, TC_DH, 1);
 
+    int k_started = 0, v_started = 0, q_started = 0;     // copies that the copying lane has started: blocks of keys, of values, items' queries
     if (tma_warp) {
         if (lane == 0) {
             // ---- the copying lane: queries, keys and values of one item after the other, as buffers come free ----
@@ -407,6 +408,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         for (int sl = 0; sl < TC_SLABS; sl++)
                             tc_tma_2d(smem + TC_OFF_Q + t * TC_Q_TILE_BYTES + sl * TC_Q_SLAB, &map_q, it.h * TC_DH + sl * 64,
                                       it.t_first + t * TC_BM, &tail.q_full[t]);
+                        q_started = n_it * TC_TILES + t + 1;
                     }
                 };
                 if (n_it == 0) load_q();
@@ -427,10 +429,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     const bool drop = false;
 #endif
                     tc_load_tile(k_tiles + buf * TC_KV_BYTES, &map_k, pg, it.kvh, KV, &tail.k_full[buf], drop);
+                    k_started = gj + 1;
                     if (n_it > 0 && j == q_after) load_q();
                     if (gj >= TC_STAGES) wait(&tail.v_empty[buf], parity);
                     if (dead) break;
                     tc_load_tile(v_tiles + buf * TC_KV_BYTES, &map_v, pg, it.kvh, KV, &tail.v_full[buf]);
+                    v_started = gj + 1;
                 }
                 kv_base += it.n_blocks;
                 n_it++;
@@ -702,6 +706,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     tc_fence_before();
     __syncthreads();
+    if (tail.dead) {
+        // Somebody gave up: before the block gives its shared memory back, the copying lane waits once more (each wait
+        // with the same limit) for the copies it has started.
+        if (tma_warp && lane == 0) {
+            for (int g = k_started > TC_STAGES ? k_started - TC_STAGES : 0; g < k_started; g++) tc_mbar_wait(&tail.k_full[g % TC_STAGES], (unsigned)((g / TC_STAGES) & 1));
+            for (int g = v_started > TC_STAGES ? v_started - TC_STAGES : 0; g < v_started; g++) tc_mbar_wait(&tail.v_full[g % TC_STAGES], (unsigned)((g / TC_STAGES) & 1));
+            for (int g = q_started > TC_TILES ? q_started - TC_TILES : 0; g < q_started; g++) tc_mbar_wait(&tail.q_full[g % TC_TILES], (unsigned)((g / TC_TILES) & 1));
+        }
+        __syncthreads();
+    }
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TC_TMEM_COLS) : "memory");
     }

@@ -138,6 +138,7 @@ linear_stream_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     // blocks that read their tables and wait) may come in right away
     pdl_trigger();
 
+    int issued = 0;                                // stages whose copies the copying lane has started
     if (warp == 0 && lane == 0) {
         // ---- the copying lane ---------------------------------------------------------------------------------
         asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_w) : "memory");
@@ -154,6 +155,7 @@ linear_stream_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         pdl_wait();
         for (int i = 0; i < first; i++)
             lt_tma_2d(lt_smem + (size_t)i * stage_bytes + LT_A_BYTES, &map_x, (st_lo + i) * LT_STAGE_K, 0, &tail.full[i]);
+        issued = first;
         bool dead = false;
         for (int i = stages; i < my_stages && !dead; i++) {
             const int s = i % stages;
@@ -165,6 +167,7 @@ linear_stream_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
             lt_expect_tx(&tail.full[s], (unsigned)stage_bytes);
             lt_tma_2d(lt_smem + (size_t)s * stage_bytes, &map_w, (st_lo + i) * LT_STAGE_K, n0, &tail.full[s]);
             lt_tma_2d(lt_smem + (size_t)s * stage_bytes + LT_A_BYTES, &map_x, (st_lo + i) * LT_STAGE_K, 0, &tail.full[s]);
+            issued = i + 1;
         }
     } else if (warp == 1 && lane == 0) {
         // ---- the issuing lane -----------------------------------------------------------------------------------
@@ -191,6 +194,12 @@ linear_stream_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     if (!ri_mbar_wait(&tail.done, 0)) {
         if (lane == 0) atomicExch(err, 5);
         tail.dead = 1;
+    }
+    if (tid == 0 && *(volatile int*)&tail.dead) {
+        // Somebody gave up: the copies that were started are waited for once more, each with the same limit, before
+        // the shared memory they land in is used for the partial tile or given back (everybody meets at a barrier
+        // further down).
+        for (int i = issued > stages ? issued - stages : 0; i < issued; i++) ri_mbar_wait(&tail.full[i % stages], (unsigned)((i / stages) & 1));
     }
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     // ---- the accumulator: thread = output row (tensor-memory lane), columns = tokens ----------------------------
