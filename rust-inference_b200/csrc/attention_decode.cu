@@ -66,10 +66,15 @@ __host__ __device__ inline size_t decode_smem_bytes(int group_rows) {
     return sizeof(DecodeSmem) + sizeof(float) * AD_WARPS * (size_t)group_rows * AD_CPITCH;
 }
 
-__device__ __forceinline__ uint4 ldg_nc16(const void* p) {
+// 16 bytes from global memory by an ordinary (coherent) load that is kept in L2 only.  Not ld.global.nc: what is read
+// with it here, the newest key and the queries, was written by the kernel before this one while this kernel was
+// already on the SMs (programmatic dependent launch), and a non-coherent load is only right for what nobody writes
+// during the kernel's life; with rows that do not fill whole cache lines (head sizes other than 64 and 128) it
+// was seen to return the line as it was before the write.
+__device__ __forceinline__ uint4 ld_cg16(const void* p) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
 __device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
@@ -137,7 +142,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
         for (int c = 0; c < AD_DH; c += 8) *(uint4*)&sm.v[warp * AD_PAGE + lane][c] = make_uint4(0, 0, 0, 0);
     }
 
-    bool waited = false;
+    bool waited = false, gave_up = false;
     for (int g0 = 0; g0 < G; g0 += AD_ROWS) {
         // ---- query fragments of this pass: rows quad and quad+8 of the group (zero past its end) ----
         uint4 qa[AD_GROUPS], qb[AD_GROUPS];
@@ -150,7 +155,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
 #pragma unroll
             for (int g = 0; g < AD_GROUPS; g++) {
                 int d = g * 32 + qc * 8;
-                kf[t][g] = (okr && d < AD_DH) ? ldg_nc16(pk + d) : make_uint4(0, 0, 0, 0);
+                kf[t][g] = (okr && d < AD_DH) ? ld_cg16(pk + d) : make_uint4(0, 0, 0, 0);
             }
         }
         if (g0 == 0 && !newest_page) pdl_wait();                   // the queries come from the kernel before
@@ -162,8 +167,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
             for (int g = 0; g < AD_GROUPS; g++) {
                 int d = g * 32 + qc * 8;
                 bool in = d < AD_DH;
-                qa[g] = (in && okA) ? *(const uint4*)(pa + d) : make_uint4(0, 0, 0, 0);
-                qb[g] = (in && okB) ? *(const uint4*)(pb + d) : make_uint4(0, 0, 0, 0);
+                qa[g] = (in && okA) ? ld_cg16(pa + d) : make_uint4(0, 0, 0, 0);
+                qb[g] = (in && okB) ? ld_cg16(pb + d) : make_uint4(0, 0, 0, 0);
             }
         }
         // ---- S[16 rows, 32 keys] = Q K^T ------------------------------------------------------------
@@ -212,7 +217,10 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
         }
         // ---- O[16, Dh] = P V: wait for the values (once), read them transposed ------------------------
         if (!waited) {
-            if (valid_rows > 0 && !mbar_wait(&sm.bar[warp], 0) && lane == 0) atomicExch(err, 5);
+            if (valid_rows > 0 && !mbar_wait(&sm.bar[warp], 0)) {
+                if (lane == 0) atomicExch(err, 5);
+                gave_up = true;
+            }
             __syncwarp();                     // also orders the zero rows written by other lanes
             waited = true;
         }
@@ -282,6 +290,9 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
             ml[1] = L;
         }
     }
+    // a warp whose wait ran out waits once more (with the same limit) for its copies before the block gives its
+    // shared memory back
+    if (gave_up) mbar_wait(&sm.bar[warp], 0);
 }
 
 // ---------------------------------------------------------------------------------------------
