@@ -37,7 +37,14 @@
 #define SK_BOX_BYTES (SK_ROWS * 128)
 #define SK_STAGE_TOTAL (SK_BOXES * SK_BOX_BYTES)
 
-__device__ __forceinline__ uint4 ld_ca16(const void* p) { return __ldg((const uint4*)p); }
+// 16 bytes of x by an ordinary (coherent, L1-cached) load.  Not __ldg: x is written by the kernel before this one while
+// this kernel is already on the SMs (programmatic dependent launch), and the non-coherent path is only right for what
+// nobody writes during the kernel's life.
+__device__ __forceinline__ uint4 ld_ca16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.ca.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ uint4 lds16(const void* p) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_u32(p)));
