@@ -77,6 +77,22 @@ __device__ __forceinline__ uint4 ld_cg16(const void* p) {
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
+// the same for 4 bytes, and for float data kept in L2 only (the merge reads every partial result once)
+__device__ __forceinline__ unsigned ld_ca32(const void* p) {
+    unsigned v;
+    asm volatile("ld.global.ca.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float ld_cg_f32(const float* p) {
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];\n" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 ld_cg_f32x4(const float* p) {
+    float4 v;
+    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
 }
@@ -653,10 +669,11 @@ attention_decode_stream_kernel(const bf16* __restrict__ q, const __grid_constant
             const bf16* pb = q + ((size_t)cc.b * H + cc.kvh * G + (quad + 8 < G ? quad + 8 : 0)) * AD_DH + qc * 2;
 #pragma unroll
             for (int ks = 0; ks < AD_DH / 16; ks++) {
-                qf[ks][0] = quad < G ? *(const unsigned*)(pa + ks * 16) : 0u;
-                qf[ks][1] = quad + 8 < G ? *(const unsigned*)(pb + ks * 16) : 0u;
-                qf[ks][2] = quad < G ? *(const unsigned*)(pa + ks * 16 + 8) : 0u;
-                qf[ks][3] = quad + 8 < G ? *(const unsigned*)(pb + ks * 16 + 8) : 0u;
+                // (ordinary loads: the queries were written while this kernel was already on the SMs)
+                qf[ks][0] = quad < G ? ld_ca32(pa + ks * 16) : 0u;
+                qf[ks][1] = quad + 8 < G ? ld_ca32(pb + ks * 16) : 0u;
+                qf[ks][2] = quad < G ? ld_ca32(pa + ks * 16 + 8) : 0u;
+                qf[ks][3] = quad + 8 < G ? ld_ca32(pb + ks * 16 + 8) : 0u;
             }
             new_item = false;
         }
@@ -917,11 +934,11 @@ attention_decode_merge_kernel(const float* __restrict__ o_part, const float* __r
 #pragma unroll
         for (int j = 0; j < PER; j++) {
             const int d = (j * 32 + lane) * 4;
-            if (lo0 + u < hi0 && d < AD_DH) first[u][j] = *(const float4*)(op + (size_t)(c_lo + lo0 + u) * AD_DH + d);
+            if (lo0 + u < hi0 && d < AD_DH) first[u][j] = ld_cg_f32x4(op + (size_t)(c_lo + lo0 + u) * AD_DH + d);
         }
     // the maximum over the visible chunks
     float M = -FLT_MAX;
-    for (int c = c_lo + (int)threadIdx.x; c < c_hi; c += AD_MERGE_THREADS) M = fmaxf(M, ml[c * 2]);
+    for (int c = c_lo + (int)threadIdx.x; c < c_hi; c += AD_MERGE_THREADS) M = fmaxf(M, ld_cg_f32(ml + c * 2));
     M = warp_max(M);
     if (lane == 0) s_red[warp] = M;
     __syncthreads();
@@ -936,13 +953,13 @@ attention_decode_merge_kernel(const float* __restrict__ o_part, const float* __r
         const int n = min(AD_MERGE_TILE, c_hi - t0);
         __syncthreads();
         for (int i = threadIdx.x; i < n; i += AD_MERGE_THREADS) {
-            float m = ml[(t0 + i) * 2];
+            float m = ld_cg_f32(ml + (t0 + i) * 2);
             s_w[i] = m == -FLT_MAX ? 0.0f : exp2f(m - M);
         }
         __syncthreads();
         // this warp's quarter of the tile
         const int lo = n * warp / MW, hi = n * (warp + 1) / MW;
-        for (int i = lo + lane; i < hi; i += 32) L += ml[(t0 + i) * 2 + 1] * s_w[i];
+        for (int i = lo + lane; i < hi; i += 32) L += ld_cg_f32(ml + (t0 + i) * 2 + 1) * s_w[i];
         // eight chunks' partial outputs are asked for before the first is added (the additions stay in rising order
         // of the chunks)
         for (int i0 = lo; i0 < hi; i0 += 8) {
@@ -954,7 +971,7 @@ attention_decode_merge_kernel(const float* __restrict__ o_part, const float* __r
                 for (int j = 0; j < PER; j++) {
                     const int d = (j * 32 + lane) * 4;
                     if (have) v[u][j] = first[u][j];
-                    else if (i0 + u < hi && d < AD_DH) v[u][j] = *(const float4*)(op + (size_t)(t0 + i0 + u) * AD_DH + d);
+                    else if (i0 + u < hi && d < AD_DH) v[u][j] = ld_cg_f32x4(op + (size_t)(t0 + i0 + u) * AD_DH + d);
                 }
 #pragma unroll
             for (int u = 0; u < 8; u++) {
