@@ -363,6 +363,10 @@ static int lt_splits(int N, int K, int sms) {
     return s;
 }
 
+// the number of shares of K that a launch for a matrix [N, K] takes on a device of `sms` SMs (for callers that choose
+// between this kernel and another by how well its grid fills the device)
+extern "C" int ri_linear_stream_tc_splits(int N, int K, int sms) { return lt_splits(N, K, sms > 0 ? sms : 148); }
+
 template <typename OutT>
 static cudaError_t lt_launch(dim3 grid, int splits, size_t smem, cudaStream_t stream, const CUtensorMap& map_w,
                              const CUtensorMap& map_x, OutT* y, int M, int Mp, int N, int K, int stages, int tmem_cols, int gated,

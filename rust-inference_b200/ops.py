@@ -233,6 +233,9 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, block: int) -> torch
     epilogue applies the gate); otherwise the product and ``silu_mul`` run one after the other."""
     M, K = x.shape
     N = w_gate_up.shape[0]
+    if (x.dtype == torch.bfloat16 and block == 8 and N % 16 == 0 and K % 8 == 0 and _FUSED_SWIGLU
+            and _gated_on_stream_tc(M, N, K, x.device)):
+        return linear_stream_tc(x, w_gate_up, gated=True)
     if (x.dtype == torch.bfloat16 and M <= SKINNY_MAX_TOKENS and K % 8 == 0 and block == 8 and N % 16 == 0
             and _FUSED_SWIGLU):
         _need(x, "x")
@@ -245,6 +248,30 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, block: int) -> torch
             and _takes_stream_tc(M, N, K)):
         return linear_stream_tc(x, w_gate_up, gated=True)
     return silu_mul(linear(x, w_gate_up), block)
+
+
+# The gate/up product of a handful of tokens is the one layer linear that the tcgen05 kernel does better than the
+# mma.sync one, where its grid fills the device: a large matrix (many waves of 16-row blocks for the mma.sync kernel,
+# whose successor can only come in with the last wave) that the tcgen05 kernel covers in one wave with at least two
+# shares of K per tile.  Measured inside the decode step at Qwen3-8B shapes (24,576 x 4,096; ms a step, tcgen05 /
+# mma.sync): 12 tokens 4.24 / 4.46, 8 tokens 3.75 / 3.90, 4 tokens 3.35 / 3.43; 2 tokens 3.16 / 3.13 and 1 token
+# 3.02 / 3.01 the other way round; at 14B and 32B shapes (one share of K: 272 and 400 blocks for 148 SMs) 6.01 / 5.93
+# and 12.52 / 12.44, so those stay where they are.  The other layer linears at 8B shapes lose 1 to 3 % on it each.
+GATED_STREAM_TC_MIN_TOKENS = 4
+GATED_STREAM_TC_MIN_ELEMENTS = 90_000_000
+_GATED_STREAM_TC = os.environ.get("RUST_INFERENCE_B200_GATED_STREAM_TC", "1") != "0"
+_splits_cache = {}
+
+
+def _gated_on_stream_tc(M: int, N: int, K: int, device) -> bool:
+    if not _GATED_STREAM_TC or M < GATED_STREAM_TC_MIN_TOKENS or M > SKINNY_MAX_TOKENS or N * K < GATED_STREAM_TC_MIN_ELEMENTS:
+        return False
+    key = (N, K, str(device))
+    if key not in _splits_cache:
+        _, lib = _fn("linear_stream_tc", "ri_linear_stream_tc")
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        _splits_cache[key] = int(lib.ri_linear_stream_tc_splits(int(N), int(K), int(sms)))
+    return _splits_cache[key] >= 2
 
 
 def _takes_stream_tc(M: int, N: int, K: int) -> bool:

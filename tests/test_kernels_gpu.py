@@ -194,6 +194,30 @@ def test_linear_stream_tc(shape):
         assert torch.equal(fewer, full[:13])
 
 
+@pytest.mark.parametrize("M,taken", [(1, False), (3, False), (4, True), (8, True), (12, True)])
+def test_gate_up_product_of_a_few_tokens_on_the_tcgen05_kernel(M, taken, monkeypatch):
+    """At Qwen3-8B's feed-forward shape (24,576 gate and up rows of 4,096) the product of 4 to 12 tokens with the SiLU
+    gate runs on the tcgen05 weight-streaming kernel, fewer tokens on the mma.sync one; both give the product and
+    the gate of the plain formulas, and a smaller matrix stays on the mma.sync kernel."""
+    from rust_inference_b200 import ops
+    N, K = 24576, 4096
+    rng = np.random.default_rng(M)
+    x = rnd(rng, M, K, dtype="bfloat16")
+    w = rnd(rng, N, K, scale=0.05, dtype="bfloat16")
+    xd, wd = dev(x, torch.bfloat16), dev(w, torch.bfloat16)
+    assert ops._gated_on_stream_tc(M, N, K, xd.device) == taken
+    assert not ops._gated_on_stream_tc(8, 6144, 4096, xd.device)
+    got = ops.linear_swiglu(xd, wd, 8)
+    v = plain.linear(x, w).reshape(M, N // 16, 2, 8)
+    want = (plain.silu(v[:, :, 0]) * v[:, :, 1]).reshape(M, N // 2)
+    close(got, want, 1e-2, f"gate/up product of {M} tokens")
+    monkeypatch.setattr(ops, "_GATED_STREAM_TC", not taken)          # the other kernel
+    if taken:
+        other = ops.linear_swiglu(xd, wd, 8)
+        close(other, got.float().cpu().numpy().astype(np.float64), 1e-2, "mma.sync against tcgen05")
+    assert int(ops.error_flag("cuda").item()) == 0
+
+
 @pytest.mark.parametrize("shape", [(13, 208, 520), (17, 4096, 1024), (32, 24576, 4096), (24, 48, 72), (64, 1040, 2048)])
 def test_linear_stream_tc_gated(shape):
     """The tcgen05 weight-streaming linear with the SiLU gate in its epilogue (gate and up rows alternating in blocks

@@ -87,7 +87,7 @@ def large_8b(tmp_path_factory):
     shutil.rmtree(d, ignore_errors=True)
 
 
-@pytest.mark.parametrize("dtype,seqs,wide", [("float32", 24, None), ("bfloat16", 24, None), ("bfloat16", 15, None), ("bfloat16", 64, None),
+@pytest.mark.parametrize("dtype,seqs,wide", [("float32", 24, None), ("bfloat16", 24, None), ("bfloat16", 15, None), ("bfloat16", 8, None), ("bfloat16", 64, None),
                                              ("bfloat16", 64, 2000), ("float32", 64, None)])
 def test_many_sequences_decode_together_at_8b_layer_shapes(tmp_path, monkeypatch, large_8b, dtype, seqs, wide):
     """Two layers of Qwen3-8B's shapes (width 4096, 32 heads over 8 kv heads of 128, feed-forward 12288) and a
