@@ -63,21 +63,26 @@ __device__ __forceinline__ void sk_tma_2d(void* dst, const CUtensorMap* map, int
 }
 __device__ __forceinline__ bool sk_wait(unsigned long long* bar, unsigned parity) { return ri_mbar_wait(bar, parity); }
 
+// STAGES: the depth of a warp's ring.  SK_STAGES (two stages, three blocks per SM) for grids of more than two
+// blocks per SM; a grid that leaves an SM two blocks at most (the matrices of 4,096 rows: 256 blocks) takes
+// SK_DEEP_STAGES, so that the blocks that are there have half as many bytes again on their way.
+#define SK_DEEP_STAGES 3
+template <int STAGES>
 struct __align__(1024) SkinnySmem {
-    unsigned char w[SK_WARPS][SK_STAGES][SK_STAGE_TOTAL];      // boxes start on multiples of 1024 bytes (the swizzle's period)
-    unsigned long long bar[SK_WARPS][SK_STAGES];
+    unsigned char w[SK_WARPS][STAGES][SK_STAGE_TOTAL];         // boxes start on multiples of 1024 bytes (the swizzle's period)
+    unsigned long long bar[SK_WARPS][STAGES];
     float part[SK_WARPS][SK_ROWS][17];
 };
-#define SK_SMEM_BYTES (sizeof(SkinnySmem) + 1024)
+#define SK_SMEM_BYTES(STAGES) (sizeof(SkinnySmem<STAGES>) + 1024)
 
 // NT: token tiles of 8 (1 or 2).  SWIGLU: the 16 rows of a block are 8 gate rows followed by their 8 up rows;
 // the block writes silu(gate) * up, 8 outputs per token, into y [M, N/2].
-template <int NT, typename OutT, bool SWIGLU>
-__global__ void __launch_bounds__(32 * SK_WARPS, SK_MIN_BLOCKS)
+template <int NT, typename OutT, bool SWIGLU, int STAGES>
+__global__ void __launch_bounds__(32 * SK_WARPS, STAGES == SK_STAGES ? SK_MIN_BLOCKS : 2)
 linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ y, int M, int N,
                      int K, int early_from, int* __restrict__ err) {
     extern __shared__ __align__(16) unsigned char sk_raw[];
-    SkinnySmem& sm = *reinterpret_cast<SkinnySmem*>(sk_raw + ((1024u - (smem_u32(sk_raw) & 1023u)) & 1023u));
+    SkinnySmem<STAGES>& sm = *reinterpret_cast<SkinnySmem<STAGES>*>(sk_raw + ((1024u - (smem_u32(sk_raw) & 1023u)) & 1023u));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int quad = lane >> 2, qc = lane & 3;
     const int rho = (quad >> 1) | ((quad & 1) << 2);          // the W row (of 8) behind MMA row `quad`
@@ -99,15 +104,15 @@ linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtenso
     if (lane == 0) {
         asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_w) : "memory");
 #pragma unroll
-        for (int s = 0; s < SK_STAGES; s++) sk_mbar_init(&bar[s]);
+        for (int s = 0; s < STAGES; s++) sk_mbar_init(&bar[s]);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncwarp();
 
-    // start the copies of stage `i` (counted from this warp's first) into ring slot i % SK_STAGES
+    // start the copies of stage `i` (counted from this warp's first) into ring slot i % STAGES
     auto issue = [&](int i) {
         if (lane == 0) {
-            const int slot = i % SK_STAGES;
+            const int slot = i % STAGES;
             const int k0 = (st_lo + i) * SK_STAGE_K;
             sk_expect_tx(&bar[slot], SK_STAGE_TOTAL);
 #pragma unroll
@@ -119,7 +124,7 @@ linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtenso
             }
         }
     };
-    const int prefill = my_stages < SK_STAGES ? my_stages : SK_STAGES;
+    const int prefill = my_stages < STAGES ? my_stages : STAGES;
     for (int i = 0; i < prefill; i++) issue(i);       // W is read-only for every kernel: no need to wait first
     pdl_wait();                                        // x comes from the kernel before
 
@@ -138,7 +143,7 @@ linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtenso
     bool dead = false;
     int started = prefill;                              // stages whose copies have been started
     for (int i = 0; i < started; i++) {
-        const int slot = i % SK_STAGES;
+        const int slot = i % STAGES;
         const int k0 = (st_lo + i) * SK_STAGE_K;
         // x for this stage (L1/L2), asked for before the wait
         uint4 xv[SK_GROUPS][NT];
@@ -151,7 +156,7 @@ linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtenso
             }
         // after a wait has run out the stages already started are still waited for (their copies must not
         // outlive the block), each with its own limit, and no further stage is started
-        if (!sk_wait(&bar[slot], (unsigned)((i / SK_STAGES) & 1))) {
+        if (!sk_wait(&bar[slot], (unsigned)((i / STAGES) & 1))) {
             if (lane == 0) atomicExch(err, 5);
             dead = true;
         }
@@ -168,9 +173,9 @@ linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtenso
             }
         }
         __syncwarp();                                   // every lane has read the slot
-        if (!dead && i + SK_STAGES < my_stages) {
-            issue(i + SK_STAGES);
-            started = i + SK_STAGES + 1;
+        if (!dead && i + STAGES < my_stages) {
+            issue(i + STAGES);
+            started = i + STAGES + 1;
         }
     }
     if (!trigger_early) pdl_trigger_late();
@@ -248,14 +253,23 @@ static int weight_tensor_map(const CUtensorMap** out, const void* w, int N, int 
     return 0;
 }
 
-template <int NT, typename OutT, bool SWIGLU>
-static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, int* err, cudaStream_t stream) {
+template <int NT, typename OutT, bool SWIGLU, int STAGES>
+static int launch_skinny_ring(const CUtensorMap* map, dim3 grid, int early_from, const void* x, void* y, int M, int N, int K, int* err,
+                              cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<NT, OutT, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<NT, OutT, SWIGLU, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)SK_SMEM_BYTES(STAGES));
         if (e != cudaSuccess) RI_FAIL((int)e, "linear_skinny: %s", cudaGetErrorString(e));
         configured = true;
     }
+    ri_launch_pdl(linear_skinny_kernel<NT, OutT, SWIGLU, STAGES>, grid, dim3(32 * SK_WARPS), SK_SMEM_BYTES(STAGES), stream, (const bf16*)x,
+                  *map, (OutT*)y, M, N, K, early_from, err);
+    return 0;
+}
+
+template <int NT, typename OutT, bool SWIGLU>
+static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, int* err, cudaStream_t stream) {
     const CUtensorMap* map = nullptr;
     int rc = weight_tensor_map(&map, w, N, K);
     if (rc) return rc;
@@ -267,11 +281,13 @@ static int launch_skinny(const void* x, const void* w, void* y, int M, int N, in
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
     }
+#ifndef SK_NO_DEEP_RING
+    // a grid of at most two blocks per SM: the deeper ring (its blocks are all on the SMs at once: early_from 0)
+    if ((long long)grid.x <= 2ll * sms) return launch_skinny_ring<NT, OutT, SWIGLU, SK_DEEP_STAGES>(map, grid, 0, x, y, M, N, K, err, stream);
+#endif
     const long long resident = (long long)sms * SK_MIN_BLOCKS;                // blocks on the device at once
     const int early_from = (long long)grid.x > resident ? (int)((long long)grid.x - resident) : 0;
-    ri_launch_pdl(linear_skinny_kernel<NT, OutT, SWIGLU>, grid, dim3(32 * SK_WARPS), SK_SMEM_BYTES, stream, (const bf16*)x,
-                  *map, (OutT*)y, M, N, K, early_from, err);
-    return 0;
+    return launch_skinny_ring<NT, OutT, SWIGLU, SK_STAGES>(map, grid, early_from, x, y, M, N, K, err, stream);
 }
 
 extern "C" int ri_linear_skinny_max_tokens() { return 16; }
