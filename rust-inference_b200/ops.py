@@ -254,17 +254,18 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, block: int) -> torch
 # mma.sync one, where its grid fills the device: a large matrix (many waves of 16-row blocks for the mma.sync kernel,
 # whose successor can only come in with the last wave) that the tcgen05 kernel covers in one wave with at least two
 # shares of K per tile.  Measured inside the decode step at Qwen3-8B shapes (24,576 x 4,096; ms a step, tcgen05 /
-# mma.sync): 12 tokens 4.24 / 4.46, 8 tokens 3.75 / 3.90, 4 tokens 3.35 / 3.43; 2 tokens 3.16 / 3.13 and 1 token
-# 3.02 / 3.01 the other way round; at 14B and 32B shapes (one share of K: 272 and 400 blocks for 148 SMs) 6.01 / 5.93
-# and 12.52 / 12.44, so those stay where they are.  The other layer linears at 8B shapes lose 1 to 3 % on it each.
-GATED_STREAM_TC_MIN_TOKENS = 4
+# mma.sync): 12 tokens 4.24 / 4.46, 8 tokens 3.75 / 3.90, 4 tokens 3.35 / 3.43, 3 tokens 3.30 / 3.33; 2 tokens
+# 3.16 / 3.13 and 1 token 3.02 / 3.01 the other way round; at 14B and 32B shapes (one share of K: 272 and 400 blocks
+# for 148 SMs) 6.01 / 5.93 and 12.52 / 12.44, so those stay where they are.  The other layer linears at 8B shapes lose
+# 1 to 3 % on it each.  Against the library product above 32 tokens: 40 tokens 7.47 / 7.58, 64 tokens 10.03 / 10.11.
+GATED_STREAM_TC_MIN_TOKENS = 3
 GATED_STREAM_TC_MIN_ELEMENTS = 90_000_000
 _GATED_STREAM_TC = os.environ.get("RUST_INFERENCE_B200_GATED_STREAM_TC", "1") != "0"
 _splits_cache = {}
 
 
 def _gated_on_stream_tc(M: int, N: int, K: int, device) -> bool:
-    if not _GATED_STREAM_TC or M < GATED_STREAM_TC_MIN_TOKENS or M > SKINNY_MAX_TOKENS or N * K < GATED_STREAM_TC_MIN_ELEMENTS:
+    if not _GATED_STREAM_TC or M < GATED_STREAM_TC_MIN_TOKENS or M > STREAM_TC_MAX_TOKENS or N * K < GATED_STREAM_TC_MIN_ELEMENTS:
         return False
     key = (N, K, str(device))
     if key not in _splits_cache:

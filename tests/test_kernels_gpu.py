@@ -194,11 +194,12 @@ def test_linear_stream_tc(shape):
         assert torch.equal(fewer, full[:13])
 
 
-@pytest.mark.parametrize("M,taken", [(1, False), (3, False), (4, True), (8, True), (12, True)])
+@pytest.mark.parametrize("M,taken", [(1, False), (2, False), (3, True), (8, True), (12, True), (40, True), (128, True)])
 def test_gate_up_product_of_a_few_tokens_on_the_tcgen05_kernel(M, taken, monkeypatch):
-    """At Qwen3-8B's feed-forward shape (24,576 gate and up rows of 4,096) the product of 4 to 12 tokens with the SiLU
-    gate runs on the tcgen05 weight-streaming kernel, fewer tokens on the mma.sync one; both give the product and
-    the gate of the plain formulas, and a smaller matrix stays on the mma.sync kernel."""
+    """At Qwen3-8B's feed-forward shape (24,576 gate and up rows of 4,096) the product of 3 to 128 tokens with the SiLU
+    gate runs on the tcgen05 weight-streaming kernel, fewer tokens on the mma.sync one; both ways (above 12 tokens
+    the other way is the product and the gate apart) give the product and the gate of the plain formulas, and a
+    smaller matrix stays where it was."""
     from rust_inference_b200 import ops
     N, K = 24576, 4096
     rng = np.random.default_rng(M)
