@@ -6,7 +6,8 @@
 // of 256 k in shared memory: per stage one lane starts four TMA tensor copies
 // (cp.async.bulk.tensor.2d, boxes of 16 rows x 64 k with the 128-byte swizzle,
 // completion counted on the stage's mbarrier), so 16 KB per warp are in flight without
-// holding a register, and three blocks share an SM.  What a box holds beyond N or K is
+// holding a register, and three blocks share an SM (a grid that leaves an SM two blocks at
+// most takes a ring of three stages: 24 KB per warp).  What a box holds beyond N or K is
 // filled with zeros by the copy.  The copies of the first stages are started before
 // the kernel waits for its predecessor (programmatic dependent launch): W is never
 // written, so they overlap the predecessor's tail.
@@ -281,7 +282,7 @@ static int launch_skinny(const void* x, const void* w, void* y, int M, int N, in
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
     }
-#ifndef SK_NO_DEEP_RING
+#ifndef SK_NO_DEEP_RING      // (-DSK_NO_DEEP_RING: two stages everywhere, for comparisons)
     // a grid of at most two blocks per SM: the deeper ring (its blocks are all on the SMs at once: early_from 0)
     if ((long long)grid.x <= 2ll * sms) return launch_skinny_ring<NT, OutT, SWIGLU, SK_DEEP_STAGES>(map, grid, 0, x, y, M, N, K, err, stream);
 #endif
