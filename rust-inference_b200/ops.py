@@ -47,11 +47,33 @@ _NO_TCGEN05 = os.environ.get("RUST_INFERENCE_B200_NO_TCGEN05") == "1"   # for co
 # Qwen3-8B shapes, 0.3 % at batch 8); RUST_INFERENCE_B200_FUSED_SWIGLU=0 takes the separate kernel, for comparisons
 _FUSED_SWIGLU = os.environ.get("RUST_INFERENCE_B200_FUSED_SWIGLU", "1") != "0"
 _WEIGHT_HINTS = os.environ.get("RUST_INFERENCE_B200_WEIGHT_HINTS", "1") != "0"
-# Up to here the bfloat16 linear is this package's mma.sync weight-streaming kernel (it takes up to 16 tokens).  From 13
-# tokens on the tcgen05 kernel below is faster inside the decode step (Qwen3-8B shapes, ms a step with 12 / 16 as the
-# limit: 13 tokens 4.65 / 4.73, 14 tokens 4.80 / 4.99, 15 tokens 4.90 / 5.27, 16 tokens 5.02 / 5.48; at 9 and 12 tokens
-# the mma.sync kernel wins by 0.5 to 1 %).  RUST_INFERENCE_B200_SKINNY_MAX=8..16 moves the limit, for comparisons.
+# Up to here the bfloat16 linear is this package's mma.sync weight-streaming kernel whatever the matrix; the kernel takes
+# up to 16 tokens, and from 13 to 16 it is taken for the matrices whose grid of 16-row blocks sits well on the SMs: all
+# blocks there at once, and either at most two per SM (they then have the ring of three stages) or nearly three
+# (with two or three blocks of the two-stage ring an SM has enough bytes on their way; a grid that leaves most SMs
+# two of them does not).  The others go to the tcgen05 kernel below.  Measured inside the decode step (ms a step;
+# everything on the mma.sync kernel / everything on the tcgen05 one / by this rule, with the gate/up product on the
+# tcgen05 kernel): Qwen3-8B shapes (grids of 384, 256 and 256 blocks for 148 SMs) 13 tokens 4.73 / 4.59 / 4.34,
+# 16 tokens 5.48 / 4.91 / 4.71; Qwen3-14B shapes (448, 320 and 320 blocks: none sits well) 16 tokens 7.87 / 7.20 / 7.20,
+# and 7.51 with the matrices of 320 blocks on the mma.sync kernel.
+# RUST_INFERENCE_B200_SKINNY_MAX=8..16 moves the first limit, for comparisons.
 SKINNY_MAX_TOKENS = min(16, max(1, int(os.environ.get("RUST_INFERENCE_B200_SKINNY_MAX", "12"))))
+SKINNY_KERNEL_TOKENS = 16          # what the kernel takes
+SKINNY_BLOCKS_PER_SM = 3           # its blocks of 16 rows that share an SM (two with the ring of three stages)
+_sm_count = {}
+
+
+def _takes_skinny(M: int, N: int, K: int, device) -> bool:
+    """Whether a bfloat16 linear of M tokens with a matrix [N, K] runs on the mma.sync weight-streaming kernel."""
+    if K % 8 or M > SKINNY_KERNEL_TOKENS:
+        return False
+    if M <= SKINNY_MAX_TOKENS:
+        return True
+    key = str(device)
+    if key not in _sm_count:
+        _sm_count[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    fill = -(-N // 16) / _sm_count[key]                  # blocks per SM
+    return fill <= 2.0 or 2.5 <= fill <= SKINNY_BLOCKS_PER_SM
 # For 13 to 128 tokens there is a tcgen05 weight-streaming kernel of this package (linear_stream_tc).  Measured inside
 # the decode step at Qwen3-8B shapes against the library product (cuBLAS): the step is 2.8 % faster with it at 24
 # tokens and 1.9 % at 32, the same at 40, and 1.5 to 2 % slower from 48 on (at 64 tokens a layer's products are
@@ -236,7 +258,7 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, block: int) -> torch
     if (x.dtype == torch.bfloat16 and block == 8 and N % 16 == 0 and K % 8 == 0 and _FUSED_SWIGLU
             and _gated_on_stream_tc(M, N, K, x.device)):
         return linear_stream_tc(x, w_gate_up, gated=True)
-    if (x.dtype == torch.bfloat16 and M <= SKINNY_MAX_TOKENS and K % 8 == 0 and block == 8 and N % 16 == 0
+    if (x.dtype == torch.bfloat16 and _takes_skinny(M, N, K, x.device) and block == 8 and N % 16 == 0
             and _FUSED_SWIGLU):
         _need(x, "x")
         _need(w_gate_up, "w_gate_up", x.dtype)
@@ -244,7 +266,7 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, block: int) -> torch
         _call("linear_skinny", "ri_linear_skinny", x.data_ptr(), w_gate_up.data_ptr(), y.data_ptr(), M, N, K, 0, 1,
               error_flag(x.device).data_ptr(), _stream())
         return y
-    if (x.dtype == torch.bfloat16 and M > SKINNY_MAX_TOKENS and block == 8 and N % 16 == 0 and _FUSED_SWIGLU
+    if (x.dtype == torch.bfloat16 and block == 8 and N % 16 == 0 and _FUSED_SWIGLU
             and _takes_stream_tc(M, N, K)):
         return linear_stream_tc(x, w_gate_up, gated=True)
     return silu_mul(linear(x, w_gate_up), block)
@@ -285,8 +307,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     """y = x w^T for x [M, K], w [N, K].
 
     float32: this package's own FMA kernel (no tensor cores, no TF32).
-    bfloat16, up to 12 tokens: this package's weight-streaming tensor-core kernel (mma.sync).
-    bfloat16, 13 to 32 tokens (and up to 128 for wide matrices such as the output head): this package's
+    bfloat16, up to 12 tokens (up to 16 for matrices of one wave of blocks): this package's weight-streaming
+    tensor-core kernel (mma.sync).
+    bfloat16, from there to 32 tokens (and up to 128 for wide matrices such as the output head): this package's
     tcgen05 weight-streaming kernel.
     bfloat16, more tokens: the library GEMM (cuBLAS through torch), as the
     reference engine uses cuBLAS for its linears (src/cuda/mod.rs:186-232 there).
@@ -303,7 +326,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         return y
     if x.dtype != torch.bfloat16:
         raise KernelError(f"linear: dtype {x.dtype}")
-    if M <= SKINNY_MAX_TOKENS and K % 8 == 0:
+    if _takes_skinny(M, N, K, x.device):
         # a handful of tokens: the weight-streaming kernel of this package
         y = torch.empty((M, N), dtype=torch.float32 if out_dtype == torch.float32 else torch.bfloat16, device=x.device)
         _call("linear_skinny", "ri_linear_skinny", x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K,
